@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the FLARE mixer forward+backward (Mtokens/s), one JSON line on stdout.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+ours      : libflare_b200.so through the public API (flare_multihead_mixer, or its
+            context-parallel form when N > 1: the token axis is sharded over the ranks,
+            total work fixed -> "scaling": "strong").
+reference : the reference project's CPU implementation of the same path (two SDPA
+            calls + autograd, README.md:37-53), timed on the host cores of the box on a
+            bounded sample of the same workload.
+
+Workload: B=1, H=8, N=1,048,576, M=256, D=32, bf16, q,k,v ~ N(0, D^-1/2), dy ~ N(0,1),
+seeded synthetic tensors (no dataset is involved).  K, V, dY, Y, dK, dV are 64 MiB per
+head-batch... 512 MiB each in total, so every pass streams far more than the 126 MB L2;
+no explicit flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(B=1, H=8, N=1 << 20, M=256, D=32)
+DTYPE = torch.bfloat16
+METRIC = "FLARE mixer fwd+bwd Mtokens/s"
+CPU_SAMPLE_TOKENS = 131072
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------------
+# clocks sampled while the timed region runs
+# ----------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return None
+        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------------
+# reference arm / CPU baseline: the two-SDPA path on the host cores
+# ----------------------------------------------------------------------------------
+def cpu_reference_step(q, k, v, dy):
+    from oracle import flare_oracle as O
+    q = q.detach().requires_grad_(True)
+    k = k.detach().requires_grad_(True)
+    v = v.detach().requires_grad_(True)
+    y = O.mixer_sdpa(q, k, v, 1.0)
+    y.backward(dy)
+    return y, q.grad, k.grad, v.grad
+
+
+def cpu_inputs(n_tokens):
+    from oracle import flare_oracle as O
+    w = WORKLOAD
+    return O.make_inputs(w["B"], w["H"], n_tokens, w["M"], w["D"], dtype=DTYPE, seed=0)
+
+
+def time_cpu(n_tokens, steps, warmup):
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, dy = cpu_inputs(n_tokens)
+    for _ in range(warmup):
+        cpu_reference_step(q, k, v, dy)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_reference_step(q, k, v, dy)
+    dt = (time.perf_counter() - t0) / steps
+    return dt, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    w = WORKLOAD
+    dt, cores = time_cpu(CPU_SAMPLE_TOKENS, args.steps, args.warmup)
+    val = w["B"] * CPU_SAMPLE_TOKENS / dt / 1e6
+    sample = (f"{CPU_SAMPLE_TOKENS} of {w['N']} tokens per step (same H, M, D, bf16), two SDPA calls + autograd "
+              f"on the host CPU, torch {torch.__version__}")
+    line = dict(
+        impl="reference", metric=METRIC, value=val, unit="Mtokens/s", n_gpus=args.gpus, steps=args.steps,
+        warmup=args.warmup, ms_per_step=dt * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None,
+        dtype="bf16", data="synthetic",
+        config=dict(workload="mixer_1M: B=1 H=8 N=1048576 M=256 D=32 bf16 fwd+bwd", sample_tokens=CPU_SAMPLE_TOKENS),
+        cpu_baseline=dict(value=val, unit="Mtokens/s", cores=cores, kind="port", sample=sample),
+        e2e=dict(value=val, unit="Mtokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+        gpu_launches=0,
+    )
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------
+def pass_table(B, H, N, M, D, e):
+    """Algorithmic work of each launch: FLOPs, exponentials, HBM bytes (W = B*H*M*N, T = B*H*N*D*e)."""
+    W, T, r = B * H * M * N, B * H * N * D * e, B * H * N * 4
+    return {
+        "gather_partial": dict(flops=4 * W * D, exps=W, bytes=2 * T),
+        "scatter":        dict(flops=4 * W * D, exps=W, bytes=2 * T + r),
+        "bwd_dz_partial": dict(flops=4 * W * D, exps=W, bytes=2 * T + r),
+        "bwd_tokens":     dict(flops=10 * W * D, exps=W, bytes=6 * T + 2 * r),
+        "bwd_dq_partial": dict(flops=2 * W * D, exps=0, bytes=3 * T + 2 * r),
+    }
+
+
+def time_passes(fb, q, k, v, dy, iters=3):
+    """CUDA-event time of every kernel of one fwd+bwd, launched one by one through the C ABI."""
+    from flare_b200 import _cabi
+    from flare_b200.mixer import make_problem
+    lib, ptr = _cabi.lib, _cabi.ptr
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    dev = k.device
+    y, dk, dv = torch.empty_like(k), torch.empty_like(k), torch.empty_like(v)
+    p = make_problem(q, k, 1.0, v=v, y=y, dy=dy, dk=dk, dv=dv)
+    p.n_splits = lib.flare_pick_splits(C.byref(p))
+    S = p.n_splits
+    rec = torch.empty(S, B, H, M, D + 2, dtype=torch.float32, device=dev)
+    part = torch.empty(S, B, H, M, D, dtype=torch.float32, device=dev)
+    z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+    dz32 = torch.empty_like(z32)
+    lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
+    lse_n = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+    delta = torch.empty_like(lse_n)
+    dq = torch.empty(H, M, D, dtype=torch.float32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+    P = C.byref(p)
+    calls = [
+        ("gather_partial", lambda: lib.flare_gather_partial(P, ptr(q), ptr(k), ptr(v), None, ptr(rec), st)),
+        ("combine", lambda: lib.flare_combine(P, ptr(rec), S, ptr(z32), None, ptr(lse_m), None, st)),
+        ("scatter", lambda: lib.flare_scatter(P, ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st)),
+        ("bwd_dz_partial", lambda: lib.flare_bwd_dz_partial(P, ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st)),
+        ("reduce_dz", lambda: lib.flare_reduce_sum(ptr(part), S, B * H * M, D, ptr(dz32), st)),
+        ("bwd_tokens", lambda: lib.flare_bwd_tokens(P, 3, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32),
+                                                   ptr(dz32), ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), st)),
+        ("bwd_dq_partial", lambda: lib.flare_bwd_dq_partial(P, 3, ptr(q), ptr(k), ptr(v), ptr(dy), None, ptr(z32),
+                                                           ptr(dz32), ptr(lse_m), ptr(lse_n), ptr(delta), ptr(part), st)),
+        ("reduce_dq", lambda: lib.flare_reduce_sum(ptr(part), S * B, H * M, D, ptr(dq), st)),
+    ]
+    times = {n: [] for n, _ in calls}
+    for it in range(iters + 1):
+        for name, fn in calls:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _cabi.check(fn(), name)
+            e1.record()
+            e1.synchronize()
+            if it > 0:
+                times[name].append(e0.elapsed_time(e1))
+    return {n: sum(v_) / len(v_) for n, v_ in times.items()}, S
+
+
+def measure_ex2_peak(dev):
+    """Gexp/s of the exponential unit, from the library's probe kernel (148 SMs x 8 blocks)."""
+    from flare_b200 import _cabi
+    out = torch.zeros(1, device=dev)
+    blocks, iters = 148 * 8, 4096
+    st = torch.cuda.current_stream().cuda_stream
+    best = 0.0
+    for i in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _cabi.check(_cabi.lib.flare_probe_ex2(blocks, iters, out.data_ptr(), st), "probe")
+        e1.record()
+        e1.synchronize()
+        if i:
+            best = max(best, blocks * 256 * 8 * iters / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    return best
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    import __graft_entry__
+    if rank == 0:
+        __graft_entry__.build()
+    if world > 1:
+        dist.barrier()
+    import flare_b200 as fb
+    from flare_b200.parallel import flare_mixer_context_parallel, shard_bounds
+
+    w = dict(WORKLOAD)
+    if args.tokens:
+        w["N"] = args.tokens
+    B, H, N, M, D = (w[x] for x in "BHNMD")
+    n0, n1 = shard_bounds(N, world, rank, multiple=128)
+    Nl = n1 - n0
+    g = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    sd = D ** -0.25
+    # host (pinned) copies feed the end-to-end measurement; device copies feed the resident one
+    hq = (torch.randn(H, M, D, generator=torch.Generator().manual_seed(7)) * sd).to(DTYPE).pin_memory()
+    hk = (torch.randn(B, H, Nl, D, generator=g) * sd).to(DTYPE).pin_memory()
+    hv = (torch.randn(B, H, Nl, D, generator=g) * sd).to(DTYPE).pin_memory()
+    hdy = torch.randn(B, H, Nl, D, generator=g).to(DTYPE).pin_memory()
+    q = hq.to(dev).requires_grad_(True)
+    k = hk.to(dev).requires_grad_(True)
+    v = hv.to(dev).requires_grad_(True)
+    dy = hdy.to(dev)
+
+    def mixer(q_, k_, v_):
+        if world > 1:
+            return flare_mixer_context_parallel(q_, k_, v_, 1.0)
+        return fb.flare_multihead_mixer(q_, k_, v_, scale=1.0)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        y = mixer(q, k, v)
+        y.backward(dy)
+        return y
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    total_ms = timed(step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    ms_step = total_ms / args.steps
+    value = B * N / (ms_step * 1e-3) / 1e6
+
+    # end to end: pinned host inputs -> device, fwd+bwd, results back to pinned host memory
+    hy = torch.empty_like(hk).pin_memory()
+    hdk = torch.empty_like(hk).pin_memory()
+    hdv = torch.empty_like(hk).pin_memory()
+    hdq = torch.empty(H, M, D, dtype=DTYPE).pin_memory()
+
+    def e2e_step():
+        q_ = hq.to(dev, non_blocking=True).requires_grad_(True)
+        k_ = hk.to(dev, non_blocking=True).requires_grad_(True)
+        v_ = hv.to(dev, non_blocking=True).requires_grad_(True)
+        dy_ = hdy.to(dev, non_blocking=True)
+        y_ = mixer(q_, k_, v_)
+        y_.backward(dy_)
+        hy.copy_(y_.detach(), non_blocking=True)
+        hdk.copy_(k_.grad, non_blocking=True)
+        hdv.copy_(v_.grad, non_blocking=True)
+        hdq.copy_(q_.grad, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdy))
+    d2h = sum(t.numel() * t.element_size() for t in (hy, hdk, hdv, hdq))
+
+    # per-kernel times and the roofline of the dominant one (rank 0's shard)
+    pk = peaks()
+    roof = None
+    passes = {}
+    if rank == 0:
+        with torch.no_grad():
+            passes, S = time_passes(fb, q.detach(), k.detach(), v.detach(), dy)
+        tab = pass_table(B, H, Nl, M, D, 2)
+        ex2 = measure_ex2_peak(dev)
+        top = max(tab, key=lambda n: passes.get(n, 0.0))
+        t_s = passes[top] * 1e-3
+        work = tab[top]
+        terms = dict(hbm_ms=work["bytes"] / (pk["hbm_gbs"] * 1e9) * 1e3,
+                     tensor_ms=work["flops"] / (pk["bf16_tflops"] * 1e12) * 1e3,
+                     mufu_ms=work["exps"] / (ex2 * 1e9) * 1e3)
+        bound = max(("hbm", terms["hbm_ms"]), ("tensor", terms["tensor_ms"]), ("mufu", terms["mufu_ms"]), key=lambda x: x[1])[0]
+        ach = {"hbm": work["bytes"] / t_s / 1e9, "tensor": work["flops"] / t_s / 1e12, "mufu": work["exps"] / t_s / 1e9}
+        peak = {"hbm": pk["hbm_gbs"], "tensor": pk["bf16_tflops"], "mufu": ex2}
+        unit = {"hbm": "GB/s", "tensor": "TFLOP/s", "mufu": "Gexp/s"}
+        traffic = None
+        tf = ROOT / "profiles" / "dram_traffic.json"
+        if tf.exists():
+            per = json.loads(tf.read_text()).get(top)
+            if per:
+                traffic = per["bytes_per_token_head"] * B * H * Nl
+        all_tab = {n: tab[n] for n in tab}
+        whole_bound_ms = max(sum(x["bytes"] for x in all_tab.values()) / (pk["hbm_gbs"] * 1e9),
+                             sum(x["flops"] for x in all_tab.values()) / (pk["bf16_tflops"] * 1e12),
+                             sum(x["exps"] for x in all_tab.values()) / (ex2 * 1e9)) * 1e3
+        roof = dict(kernel=top, bound=bound, achieved=ach[bound], peak=peak[bound], unit=unit[bound],
+                    frac=ach[bound] / peak[bound], traffic=traffic, peaks_source=pk["source"],
+                    hbm_frac=ach["hbm"] / peak["hbm"], tensor_frac=ach["tensor"] / peak["tensor"],
+                    mufu_frac=ach["mufu"] / peak["mufu"], ex2_peak_gexps=ex2, bound_terms_ms=terms,
+                    kernel_ms=passes, path_bound_ms=whole_bound_ms,
+                    path_frac=whole_bound_ms / (sum(passes.values())))
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        dt, cores = time_cpu(CPU_SAMPLE_TOKENS, 3, 1)
+        cpu = dict(value=B * CPU_SAMPLE_TOKENS / dt / 1e6, unit="Mtokens/s", cores=cores, kind="port",
+                   sample=f"{CPU_SAMPLE_TOKENS} of {N} tokens (same H, M, D, bf16), two SDPA calls + autograd, "
+                          f"1 warm-up + 3 runs, mean")
+
+    if rank == 0:
+        launches_per_step = 8 + (1 if world > 1 else 0)
+        line = dict(
+            metric=METRIC, value=value, unit="Mtokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
+            ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
+            data="synthetic",
+            config=dict(workload=f"mixer_1M: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd",
+                        parallelism=("single GPU" if world == 1 else f"context parallel, N sharded over {world} ranks"),
+                        tokens_per_rank=Nl, l2="inputs larger than L2 (K,V,dY,Y,dK,dV 64 B x tokens x heads each); no flush",
+                        kernel_path="simt+tcgen05 (auto)"),
+            clocks=clocks,
+            e2e=dict(value=B * N / (e2e_ms * 1e-3) / 1e6, unit="Mtokens/s", h2d_bytes_per_step=h2d * world,
+                     d2h_bytes_per_step=d2h * world, ms_per_step=e2e_ms),
+            gpu_launches=launches_per_step * args.steps,
+            roofline=roof, cpu_baseline=cpu,
+        )
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=0, help="override N (profiling on a smaller case)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,26 @@
+// Internal launch functions shared by the C-ABI layer and the kernel files.
+#pragma once
+#include "common.cuh"
+
+namespace flare {
+
+// fp32-arithmetic SIMT family (flare_simt.cu)
+int simt_gather_partial(const Ctx& c, int dtype, const void* q, const void* k, const void* v,
+                        const uint8_t* mask, float* rec, cudaStream_t st);
+int simt_dz_partial(const Ctx& c, int dtype, const void* q, const void* k, const void* dy,
+                    const uint8_t* mask, const float* lse_n, float* dz_part, cudaStream_t st);
+int simt_dq_partial(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const void* dy,
+                    const uint8_t* mask, const float* z32, const float* dz32, const float* lse_m,
+                    const float* lse_n, const float* delta_n, float* dq_part, cudaStream_t st);
+int simt_scatter(const Ctx& c, int dtype, const void* q, const void* k, const float* z32,
+                 const uint8_t* mask, void* y, float* lse_n, cudaStream_t st);
+int simt_bwd_tokens(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const void* dy,
+                    const void* y, const uint8_t* mask, const float* z32, const float* dz32,
+                    const float* lse_m, const float* lse_n, void* dk, void* dv, float* delta_n,
+                    cudaStream_t st);
+int launch_combine(const float* rec, int n_parts, long long rows, int D, int dtype, float* z32,
+                   void* z_out, float* lse_m, float* rec_out, cudaStream_t st);
+int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st);
+int launch_probe_ex2(int blocks, int iters, float* out, cudaStream_t st);
+
+}  // namespace flare

@@ -1,0 +1,145 @@
+"""Context-parallel FLARE mixer: the token axis N is sharded over the ranks of a process group.
+
+The reference has no such mode (its only parallelism is DDP replicas,
+mlutils/trainer.py:195-202).  FLARE's cross-token state is only the per-latent
+record (max, sum, M x D accumulator), so one small collective per direction is
+enough:
+
+  forward : local gather records -> all_gather -> log-sum-exp combine (rank
+            order, deterministic) -> every rank holds the same z and L -> the
+            scatter is local.
+  backward: local dZ partial -> all_reduce(SUM) -> local dK, dV, dQ partial ->
+            all_reduce(SUM) of dQ (the latents are replicated).
+
+The collectives are plain ``torch.distributed`` calls (NCCL on GPUs, gloo in the
+CPU tests); ``RecordExchange`` holds them so that the plumbing can be exercised
+without a GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+from ._cabi import check, lib, ptr, stream_of
+from .mixer import _need_cuda, _q3, _tok, make_problem
+
+__all__ = ["RecordExchange", "flare_mixer_context_parallel", "shard_bounds"]
+
+
+def shard_bounds(n_tokens: int, world: int, rank: int, multiple: int = 1):
+    """Token range [n0, n1) of `rank`: contiguous, sizes differ by at most `multiple`."""
+    per = -(-n_tokens // world)
+    per = -(-per // multiple) * multiple
+    n0 = min(n_tokens, rank * per)
+    return n0, min(n_tokens, n0 + per)
+
+
+class RecordExchange:
+    """The two collectives of the context-parallel mixer over one process group."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def gather_records(self, rec: torch.Tensor) -> torch.Tensor:
+        """rec [B,H,M,D+2] on every rank -> [world,B,H,M,D+2], rank-major, identical on all ranks."""
+        rec = rec.contiguous()
+        out = torch.empty((self.world,) + tuple(rec.shape), dtype=rec.dtype, device=rec.device)
+        # concatenation along dim 0 is the layout every backend accepts
+        dist.all_gather_into_tensor(out.view((self.world * rec.shape[0],) + tuple(rec.shape[1:])), rec,
+                                    group=self.group)
+        return out
+
+    def sum_(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+class _CPMixerFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, ex: RecordExchange, reduce_dq: bool):
+        _need_cuda(q, k, v)
+        q, batched = _q3(q)
+        k, v = _tok(k), _tok(v)
+        B, H, N, D = k.shape
+        M = q.shape[-2]
+        dev = k.device
+        with torch.cuda.device(dev):
+            st = stream_of(k)
+            y = torch.empty_like(k)
+            if y.stride(-1) != 1:
+                y = torch.empty(k.shape, dtype=k.dtype, device=dev)
+            p = make_problem(q, k, scale, v=v, y=y)
+            p.n_splits = lib.flare_pick_splits(C.byref(p))
+            rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
+            merged = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=dev)
+            check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), None, ptr(rec), st), "flare_gather_partial")
+            check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, None, None, None, ptr(merged), st), "flare_combine")
+            allrec = ex.gather_records(merged)
+            z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+            lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
+            lse_n = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+            check(lib.flare_combine(C.byref(p), ptr(allrec), ex.world, ptr(z32), None, ptr(lse_m), None, st), "flare_combine")
+            check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st), "flare_scatter")
+        ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n)
+        ctx.scale, ctx.ex, ctx.reduce_dq, ctx.batched = scale, ex, reduce_dq, batched
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        q, k, v, y, z32, lse_m, lse_n = ctx.saved_tensors
+        ex = ctx.ex
+        B, H, N, D = k.shape
+        M = q.shape[-2]
+        dev = k.device
+        with torch.cuda.device(dev):
+            st = stream_of(k)
+            dy = _tok(dy)
+            dk = torch.empty_like(k)
+            dv = torch.empty_like(v)
+            if dk.stride(-1) != 1:
+                dk = torch.empty(k.shape, dtype=k.dtype, device=dev)
+            if dv.stride(-1) != 1:
+                dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
+            p = make_problem(q, k, ctx.scale, v=v, y=y, dy=dy, dk=dk, dv=dv)
+            p.n_splits = lib.flare_pick_splits(C.byref(p))
+            part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=dev)
+            dz32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+            delta = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+            T = _cabi.TERM_BOTH
+            check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st), "flare_bwd_dz_partial")
+            check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
+            ex.sum_(dz32)
+            check(lib.flare_bwd_tokens(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
+                                       ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), st), "flare_bwd_tokens")
+            check(lib.flare_bwd_dq_partial(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), None, ptr(z32), ptr(dz32),
+                                           ptr(lse_m), ptr(lse_n), ptr(delta), ptr(part), st), "flare_bwd_dq_partial")
+            if ctx.batched:
+                dq = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+                check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dq), st), "flare_reduce_sum")
+            else:
+                dq = torch.empty(H, M, D, dtype=torch.float32, device=dev)
+                check(lib.flare_reduce_sum(ptr(part), p.n_splits * B, H * M, D, ptr(dq), st), "flare_reduce_sum")
+            if ctx.reduce_dq:
+                ex.sum_(dq)
+        return dq.to(q.dtype), dk, dv, None, None, None
+
+
+def flare_mixer_context_parallel(q, k_local, v_local, scale: float = 1.0,
+                                 group: Optional[dist.ProcessGroup] = None, reduce_dq: bool = True,
+                                 exchange: Optional[RecordExchange] = None):
+    """Mixer over a token axis sharded across `group`: k_local, v_local are this rank's [B,H,N/R,D] shard.
+
+    Returns this rank's y shard.  Equals ``flare_multihead_mixer`` on the concatenated
+    tokens.  With ``reduce_dq`` the latent gradient is summed over the group inside the
+    backward; pass False when a DDP-style reducer over the same group already does it.
+    """
+    ex = exchange or RecordExchange(group)
+    if q.dim() == 4 and q.stride(0) == 0:
+        q = q[0]
+    return _CPMixerFn.apply(q, k_local, v_local, float(scale), ex, reduce_dq)

@@ -1,0 +1,157 @@
+/*
+ * flare_b200 -- C ABI of the sm_100a FLARE gather-scatter token mixer.
+ *
+ * The reference project (vpuri3/FLARE.py) has no native interface: its hot
+ * path is two adjacent calls of torch's scaled_dot_product_attention inside
+ * Python modules.  The entry points below are what a binding for that path
+ * calls instead; every one cites the reference lines it replaces.
+ *
+ *   S = scale * q k^T            (M x N per (b,h); never materialised)
+ *   gather :  z = softmax_N(S) v           L_m = logsumexp_n S_mn
+ *   scatter:  y = softmax_M(S^T) z         C_n = logsumexp_m S_mn
+ *
+ * Conventions
+ *   - Plain pointers and sizes only.  All pointers are DEVICE pointers unless
+ *     a comment says otherwise.  The library never allocates, frees or keeps
+ *     device memory: the caller passes every output and the workspace.
+ *   - Token tensors k, v, y, dy, dk, dv are [B,H,N,D] with arbitrary element
+ *     strides for b, h, n and unit stride for d (the 'b n (h d) -> b h n d'
+ *     views of pdebench/models/flare.py:127-128 are passed as they are).
+ *     q is [H,M,D] (q_stride[0] == 0, shared by the batch, flare.py:126,136)
+ *     or [B,H,M,D].  Base pointers and row pitches must be 16-byte aligned.
+ *   - z32, dz32 are contiguous fp32 [B,H,M,D]; lse_m is fp32 [B,H,M]; lse_n and
+ *     delta_n are fp32 [B,H,N]; natural-log units.
+ *   - A partial record is fp32 [parts][B][H][M][D+2]: columns 0..D-1 hold
+ *     sum_n exp(S_mn - m) v_n, column D the running maximum m, column D+1 the
+ *     sum of exp(S_mn - m).  Token ranges on one GPU and the shards of a
+ *     context-parallel group use the same record and the same combine.
+ *   - key_mask is uint8 [B,N] (contiguous), non-zero = keep; NULL = keep all
+ *     (lra/models/backends.py:615-622).
+ *   - Every call is asynchronous on `stream`, re-entrant, and returns 0 when
+ *     the work was enqueued, or a negative FLARE_E* code when the request was
+ *     rejected before any launch; flare_last_error() then describes why.
+ */
+#ifndef FLARE_B200_H_
+#define FLARE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLARE_F32  0
+#define FLARE_F16  1
+#define FLARE_BF16 2
+
+#define FLARE_OK             0
+#define FLARE_EINVAL        -1   /* bad shape / dtype / null pointer            */
+#define FLARE_EALIGN        -2   /* pointer or stride not 16-byte aligned       */
+#define FLARE_EWORKSPACE    -3   /* workspace too small                         */
+#define FLARE_ECUDA         -4   /* a CUDA runtime call failed                  */
+#define FLARE_EUNSUPPORTED  -5   /* shape outside what the kernels cover        */
+
+/* which softmax terms a backward call differentiates */
+#define FLARE_TERM_GATHER   1    /* dS1 = P (dZ V^T - Delta)                    */
+#define FLARE_TERM_SCATTER  2    /* dS2 = A (Z dY^T - delta)                    */
+#define FLARE_TERM_BOTH     3
+
+/* kernel family (flare_set_path): tensor-core kernels when the shape allows, or SIMT only */
+#define FLARE_PATH_AUTO     0
+#define FLARE_PATH_SIMT     1
+
+typedef void* flare_stream_t;    /* a cudaStream_t */
+
+typedef struct FlareProblem {
+  int32_t B, H, N, M, D;
+  int32_t dtype;                 /* FLARE_F32 | FLARE_F16 | FLARE_BF16: q,k,v,y,dy,dk,dv */
+  float   scale;                 /* attn_scale of the reference (1.0 or D^-0.5)          */
+  int32_t n_splits;              /* token ranges per (b,h) in the split passes; 0 = auto  */
+  int64_t q_stride[3];           /* b (0 = shared latents), h, m                          */
+  int64_t k_stride[3];           /* b, h, n  (elements)                                   */
+  int64_t v_stride[3];
+  int64_t y_stride[3];
+  int64_t dy_stride[3];
+  int64_t dk_stride[3];
+  int64_t dv_stride[3];
+} FlareProblem;
+
+int         flare_version(void);
+const char* flare_last_error(void);          /* host string, thread-local */
+int         flare_set_path(int path);        /* returns the previous setting */
+
+/* Number of token ranges the split passes use for this problem (>= 1). */
+int    flare_pick_splits(const FlareProblem* p);
+/* Bytes of scratch the two whole-pass calls need (upper bounds, 256-byte aligned sizes). */
+size_t flare_fwd_workspace_bytes(const FlareProblem* p);
+size_t flare_bwd_workspace_bytes(const FlareProblem* p);
+
+/* ---- whole passes on one GPU ------------------------------------------------
+ * flare_mixer_fwd replaces the two SDPA calls of README.md:49-50 /
+ * pdebench/models/flare.py:137-138 / lra/models/backends.py:605-606:
+ * y = SDPA(k, q, SDPA(q, k, v)).  It also returns what the backward needs.   */
+int flare_mixer_fwd(const FlareProblem* p, const void* q, const void* k, const void* v,
+                    const uint8_t* key_mask, void* y, float* z32, float* lse_m, float* lse_n,
+                    void* workspace, size_t workspace_bytes, flare_stream_t stream);
+
+/* flare_mixer_bwd replaces autograd through those two SDPA calls (the reference
+ * has no hand-written backward; torch's SDPA backward plus the reduction that
+ * expand() of flare.py:136 adds).  dq32 is fp32 [H,M,D] (summed over the batch)
+ * when q_stride[0] == 0, else fp32 [B,H,M,D].                                  */
+int flare_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const void* v,
+                    const void* dy, const void* y, const uint8_t* key_mask,
+                    const float* z32, const float* lse_m, const float* lse_n,
+                    float* dq32, void* dk, void* dv,
+                    void* workspace, size_t workspace_bytes, flare_stream_t stream);
+
+/* ---- the passes one by one (context-parallel callers put a collective between
+ * them; BigFLARE of pdebench/models/flare_ablations.py:93-132 modifies z between
+ * gather and scatter) --------------------------------------------------------- */
+
+/* First SDPA call, per token range: rec[S][B][H][M][D+2], S = p->n_splits (must be >= 1). */
+int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, const void* v,
+                         const uint8_t* key_mask, float* rec, flare_stream_t stream);
+
+/* Log-sum-exp combine of n_parts records.  Any of z32, z_out (p->dtype, [B,H,M,D]
+ * contiguous), lse_m, rec_out (one merged, un-normalised record) may be NULL. */
+int flare_combine(const FlareProblem* p, const float* rec, int n_parts, float* z32,
+                  void* z_out, float* lse_m, float* rec_out, flare_stream_t stream);
+
+/* Second SDPA call: y = softmax_M(k q^T) z32; lse_n may be NULL. */
+int flare_scatter(const FlareProblem* p, const void* q, const void* k, const float* z32,
+                  const uint8_t* key_mask, void* y, float* lse_n, flare_stream_t stream);
+
+/* dZ = A dY per token range: dz_part[S][B][H][M][D] fp32. */
+int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, const void* dy,
+                         const uint8_t* key_mask, const float* lse_n, float* dz_part,
+                         flare_stream_t stream);
+
+/* out[rows][width] = sum over n_parts of parts[part][rows][width] (ordered, deterministic). */
+int flare_reduce_sum(const float* parts, int n_parts, int64_t rows, int width, float* out,
+                     flare_stream_t stream);
+
+/* Per-token gradients dk, dv and delta_n = dy_n . y_n.  `terms` selects which
+ * softmax is differentiated; v / dz32 / lse_m may be NULL without FLARE_TERM_GATHER,
+ * dy / y / lse_n without FLARE_TERM_SCATTER (then dk only gets the gather term). */
+int flare_bwd_tokens(const FlareProblem* p, int terms, const void* q, const void* k, const void* v,
+                     const void* dy, const void* y, const uint8_t* key_mask,
+                     const float* z32, const float* dz32, const float* lse_m, const float* lse_n,
+                     void* dk, void* dv, float* delta_n, flare_stream_t stream);
+
+/* dQ per token range: dq_part[S][B][H][M][D] fp32 (reduce with flare_reduce_sum). */
+int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const void* k,
+                         const void* v, const void* dy, const uint8_t* key_mask,
+                         const float* z32, const float* dz32, const float* lse_m,
+                         const float* lse_n, const float* delta_n, float* dq_part,
+                         flare_stream_t stream);
+
+/* Measurement aid, no counterpart in the reference: launches `blocks` x 256 threads that each
+ * issue 8*iters dependent-chain ex2 operations, so that the benchmark can time the exponential
+ * unit's peak on the device it runs on.  `out` is one device float (never written in practice). */
+int flare_probe_ex2(int blocks, int iters, float* out, flare_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* FLARE_B200_H_ */
