@@ -148,6 +148,11 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (!z32) return fail(FLARE_EINVAL, "z32 is null");
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
+  if (g_path.load() == FLARE_PATH_AUTO && tc_scatter_supported(c, p->dtype)) {
+    const int rc = tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
+    if (rc == FLARE_OK) return after_launch("scatter (tcgen05)");
+    if (rc != FLARE_EUNSUPPORTED) return fail(rc, "scatter (tcgen05): launch setup failed");
+  }
   TRY(simt_scatter(c, p->dtype, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream));
   return after_launch("scatter");
 }
@@ -223,6 +228,13 @@ int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const 
   TRY(simt_dq_partial(c, p->dtype, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part,
                       (cudaStream_t)stream));
   return after_launch("bwd_dq_partial");
+}
+
+int flare_device_status(int* out, int clear) {
+  if (!out) return fail(FLARE_EINVAL, "device_status: out is null");
+  const int rc = tc_read_status(out, clear != 0);
+  if (rc != FLARE_OK) return fail(rc, "device_status: %s", cudaGetErrorString(cudaGetLastError()));
+  return FLARE_OK;
 }
 
 int flare_probe_ex2(int blocks, int iters, float* out, flare_stream_t stream) {

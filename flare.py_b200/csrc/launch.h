@@ -23,4 +23,13 @@ int launch_combine(const float* rec, int n_parts, long long rows, int D, int dty
 int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st);
 int launch_probe_ex2(int blocks, int iters, float* out, cudaStream_t st);
 
+
+// tcgen05 tensor-core family (flare_tc_*.cu): bf16, D in {16,32,64}, M a multiple of 32 up to 256.
+// Each launcher returns FLARE_EUNSUPPORTED when the driver rejects a tensor map; the caller
+// then uses the SIMT kernel for that pass.
+bool tc_scatter_supported(const Ctx& c, int dtype);
+int tc_scatter(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
+               float* lse_n, cudaStream_t st);
+int tc_read_status(int* out, bool clear);
+
 }  // namespace flare

@@ -146,6 +146,11 @@ int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const 
                          const float* lse_n, const float* delta_n, float* dq_part,
                          flare_stream_t stream);
 
+/* Reads (and optionally clears) the device status word of the current device; synchronises.
+ * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
+ * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
+int flare_device_status(int* out, int clear);
+
 /* Measurement aid, no counterpart in the reference: launches `blocks` x 256 threads that each
  * issue 8*iters dependent-chain ex2 operations, so that the benchmark can time the exponential
  * unit's peak on the device it runs on.  `out` is one device float (never written in practice). */
