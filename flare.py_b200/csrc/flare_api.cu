@@ -126,6 +126,11 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("v", v, p->v_stride, p->dtype));
   if (!rec) return fail(FLARE_EINVAL, "rec is null");
   Ctx c = make_ctx(p);
+  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_lat_supported(c, p->dtype)) {
+    const int rc = tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
+    if (rc == FLARE_OK) return after_launch("gather_partial (tcgen05)");
+    if (rc != FLARE_EUNSUPPORTED) return fail(rc, "gather_partial (tcgen05): launch setup failed");
+  }
   TRY(simt_gather_partial(c, p->dtype, q, k, v, key_mask, rec, (cudaStream_t)stream));
   return after_launch("gather_partial");
 }
@@ -167,6 +172,11 @@ int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
   if (!lse_n || !dz_part) return fail(FLARE_EINVAL, "lse_n or dz_part is null");
   Ctx c = make_ctx(p);
+  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_lat_supported(c, p->dtype)) {
+    const int rc = tc_dz_partial(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream);
+    if (rc == FLARE_OK) return after_launch("bwd_dz_partial (tcgen05)");
+    if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_dz_partial (tcgen05): launch setup failed");
+  }
   TRY(simt_dz_partial(c, p->dtype, q, k, dy, key_mask, lse_n, dz_part, (cudaStream_t)stream));
   return after_launch("bwd_dz_partial");
 }

@@ -35,6 +35,7 @@ struct ScatterArgs {
   float* lse_n;                // [B,H,N] or null
   int tiles_per_bh;
   long long total_tiles;
+  int* status;                 // device status word
 };
 
 template <int D>
@@ -119,7 +120,7 @@ k_tc_scatter(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
       }
       fence_proxy_async();
       __syncthreads();
-      mbar_wait(bar_q, ph_q, &g_tc_status, abort_flag);
+      mbar_wait(bar_q, ph_q, a.status, abort_flag);
       ph_q ^= 1;
       cur_bh = bh;
     }
@@ -129,7 +130,7 @@ k_tc_scatter(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
       mbar_expect_tx(&bar_full[stage ^ 1], L::kK);
       tma_load_4d(sK + (stage ^ 1) * L::kK, &tmK, &bar_full[stage ^ 1], 0, ntile * 128, nbh % a.H, nbh / a.H);
     }
-    mbar_wait(&bar_full[stage], (uint32_t)(it >> 1) & 1, &g_tc_status, abort_flag);
+    mbar_wait(&bar_full[stage], (uint32_t)(it >> 1) & 1, a.status, abort_flag);
 
     if (tid == 0) {
       tc_fence_after();
@@ -139,7 +140,7 @@ k_tc_scatter(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
       for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dk + 2 * kk, dq + 2 * kk, idesc1, kk > 0);
       mma_commit(bar_mma);
     }
-    mbar_wait(bar_mma, ph_mma, &g_tc_status, abort_flag);
+    mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
     ph_mma ^= 1;
     tc_fence_after();
 
@@ -178,7 +179,7 @@ k_tc_scatter(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
         mma_ts(tmem + 128, tmem + kk * 8, dz + (uint64_t)((kk * 16 * ROWB) >> 4), idesc2, kk > 0);
       mma_commit(bar_mma);
     }
-    mbar_wait(bar_mma, ph_mma, &g_tc_status, abort_flag);
+    mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
     ph_mma ^= 1;
     tc_fence_after();
 
@@ -223,7 +224,21 @@ bool tc_scatter_supported(const Ctx& c, int dtype) {
          c.M % 32 == 0 && c.N >= 1;
 }
 
-static int num_sms() {
+// Address of the status word on the current device (looked up once per device).
+int* tc_status_ptr() {
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tc_status) != cudaSuccess) return nullptr;
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+int num_sms() {
   static int n = 0;
   if (!n) {
     int dev = 0;
@@ -255,6 +270,7 @@ static int launch_scatter_d(const Ctx& c, const void* q, const void* k, const fl
   a.lse_n = lse_n;
   a.tiles_per_bh = (c.N + 127) / 128;
   a.total_tiles = (long long)a.tiles_per_bh * c.B * c.H;
+  a.status = tc_status_ptr();
   static bool attr_done = false;
   constexpr int smem = ScatterSmem<D>::kBytes;
   if (!attr_done) {
