@@ -269,6 +269,34 @@ int flare_mixer_fwd(const FlareProblem* p, const void* q, const void* k, const v
   return FLARE_OK;
 }
 
+int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* k, const void* v,
+                   const void* dy, const void* y, const uint8_t* key_mask, const float* z32,
+                   const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                   float* delta_n, float* dq_part, flare_stream_t stream) {
+  TRY(check_problem(p));
+  if (terms < 1 || terms > 3) return fail(FLARE_EINVAL, "terms must be 1, 2 or 3");
+  if (p->n_splits < 1) return fail(FLARE_EINVAL, "flare_bwd_main needs n_splits >= 1");
+  if (!dq_part) return fail(FLARE_EINVAL, "dq_part is null");
+  Ctx c = make_ctx(p, terms);
+  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_bwd_supported(c, p->dtype)) {
+    TRY(check_tok("q", q, p->q_stride, p->dtype));
+    TRY(check_tok("k", k, p->k_stride, p->dtype));
+    TRY(check_tok("v", v, p->v_stride, p->dtype));
+    TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
+    TRY(check_tok("y", y, p->y_stride, p->dtype));
+    TRY(check_tok("dk", dk, p->dk_stride, p->dtype));
+    TRY(check_tok("dv", dv, p->dv_stride, p->dtype));
+    if (!z32 || !dz32 || !lse_m || !lse_n) return fail(FLARE_EINVAL, "bwd_main: z32, dz32, lse_m, lse_n are required");
+    const int rc = tc_bwd_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, (cudaStream_t)stream);
+    if (rc == FLARE_OK) return after_launch("bwd_main (tcgen05)");
+    if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_main (tcgen05): launch setup failed");
+  }
+  if ((terms & FLARE_TERM_SCATTER) && !delta_n) return fail(FLARE_EINVAL, "bwd_main: delta_n scratch is null");
+  TRY(flare_bwd_tokens(p, terms, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta_n, stream));
+  TRY(flare_bwd_dq_partial(p, terms, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part, stream));
+  return FLARE_OK;
+}
+
 int flare_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const void* v, const void* dy,
                     const void* y, const uint8_t* key_mask, const float* z32, const float* lse_m,
                     const float* lse_n, float* dq32, void* dk, void* dv, void* workspace,
@@ -287,8 +315,7 @@ int flare_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const v
   float* delta = reinterpret_cast<float*>(w);
   TRY(flare_bwd_dz_partial(&pp, q, k, dy, key_mask, lse_n, part, stream));
   TRY(flare_reduce_sum(part, pp.n_splits, (int64_t)rows, p->D, dz32, stream));
-  TRY(flare_bwd_tokens(&pp, FLARE_TERM_BOTH, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta, stream));
-  TRY(flare_bwd_dq_partial(&pp, FLARE_TERM_BOTH, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta, part, stream));
+  TRY(flare_bwd_main(&pp, FLARE_TERM_BOTH, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta, part, stream));
   if (p->q_stride[0] == 0) {
     TRY(flare_reduce_sum(part, pp.n_splits * p->B, (int64_t)p->H * p->M, p->D, dq32, stream));
   } else {

@@ -112,6 +112,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -141,6 +146,19 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   d |= (uint64_t)((8 * ROWB) >> 4) << 32;
   d |= (uint64_t)1 << 46;                 // descriptor version for sm_100
   d |= SwizzleCode<ROWB>::v << 61;
+  return d;
+}
+
+// Descriptor of an MN-major operand whose M/N extent spans several 128-byte swizzle rows:
+// blocks of 64 elements (128 bytes) are `lbo` bytes apart, groups of 8 contraction rows `sbo`
+// bytes apart (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc_mn128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= SwizzleCode<128>::v << 61;
   return d;
 }
 

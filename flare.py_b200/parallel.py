@@ -115,10 +115,9 @@ class _CPMixerFn(torch.autograd.Function):
             check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st), "flare_bwd_dz_partial")
             check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
             ex.sum_(dz32)
-            check(lib.flare_bwd_tokens(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
-                                       ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), st), "flare_bwd_tokens")
-            check(lib.flare_bwd_dq_partial(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), None, ptr(z32), ptr(dz32),
-                                           ptr(lse_m), ptr(lse_n), ptr(delta), ptr(part), st), "flare_bwd_dq_partial")
+            check(lib.flare_bwd_main(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
+                                     ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), ptr(part), st),
+                  "flare_bwd_main")
             if ctx.batched:
                 dq = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
                 check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dq), st), "flare_reduce_sum")

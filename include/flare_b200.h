@@ -146,6 +146,15 @@ int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const 
                          const float* lse_n, const float* delta_n, float* dq_part,
                          flare_stream_t stream);
 
+/* flare_bwd_tokens and flare_bwd_dq_partial in one call: dk, dv and dq_part[S][B][H][M][D] from a
+ * single sweep over k, v, dy, y where the fused tensor-core kernel covers the shape, else the two
+ * launches above (delta_n [B,H,N] fp32 is their scratch; it may be left unwritten).  Replaces the
+ * bulk of autograd through the two SDPA calls of pdebench/models/flare.py:137-138. */
+int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* k, const void* v,
+                   const void* dy, const void* y, const uint8_t* key_mask, const float* z32,
+                   const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                   float* delta_n, float* dq_part, flare_stream_t stream);
+
 /* Reads (and optionally clears) the device status word of the current device; synchronises.
  * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
