@@ -11,9 +11,8 @@ reference : the reference project's CPU implementation of the same path (two SDP
             bounded sample of the same workload.
 
 Workload: B=1, H=8, N=1,048,576, M=256, D=32, bf16, q,k,v ~ N(0, D^-1/2), dy ~ N(0,1),
-seeded synthetic tensors (no dataset is involved).  K, V, dY, Y, dK, dV are 64 MiB per
-head-batch... 512 MiB each in total, so every pass streams far more than the 126 MB L2;
-no explicit flush is needed between iterations.
+seeded synthetic tensors (no dataset is involved).  K, V, dY, Y, dK, dV are 512 MiB each, so
+every pass streams far more than the 126 MB L2; no explicit flush is needed between iterations.
 """
 from __future__ import annotations
 
@@ -162,8 +161,7 @@ def pass_table(B, H, N, M, D, e):
         "gather_partial": dict(flops=4 * W * D, exps=W, bytes=2 * T),
         "scatter":        dict(flops=4 * W * D, exps=W, bytes=2 * T + r),
         "bwd_dz_partial": dict(flops=4 * W * D, exps=W, bytes=2 * T + r),
-        "bwd_tokens":     dict(flops=10 * W * D, exps=W, bytes=6 * T + 2 * r),
-        "bwd_dq_partial": dict(flops=2 * W * D, exps=0, bytes=3 * T + 2 * r),
+        "bwd_main":       dict(flops=12 * W * D, exps=W, bytes=6 * T + r),
     }
 
 
@@ -195,10 +193,8 @@ def time_passes(fb, q, k, v, dy, iters=3):
         ("scatter", lambda: lib.flare_scatter(P, ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st)),
         ("bwd_dz_partial", lambda: lib.flare_bwd_dz_partial(P, ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st)),
         ("reduce_dz", lambda: lib.flare_reduce_sum(ptr(part), S, B * H * M, D, ptr(dz32), st)),
-        ("bwd_tokens", lambda: lib.flare_bwd_tokens(P, 3, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32),
-                                                   ptr(dz32), ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), st)),
-        ("bwd_dq_partial", lambda: lib.flare_bwd_dq_partial(P, 3, ptr(q), ptr(k), ptr(v), ptr(dy), None, ptr(z32),
-                                                           ptr(dz32), ptr(lse_m), ptr(lse_n), ptr(delta), ptr(part), st)),
+        ("bwd_main", lambda: lib.flare_bwd_main(P, 3, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
+                                               ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), ptr(part), st)),
         ("reduce_dq", lambda: lib.flare_reduce_sum(ptr(part), S * B, H * M, D, ptr(dq), st)),
     ]
     times = {n: [] for n, _ in calls}
@@ -377,7 +373,7 @@ def run_ours(args):
                           f"1 warm-up + 3 runs, mean")
 
     if rank == 0:
-        launches_per_step = 8 + (1 if world > 1 else 0)
+        launches_per_step = 7 + (1 if world > 1 else 0)
         line = dict(
             metric=METRIC, value=value, unit="Mtokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
             ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
