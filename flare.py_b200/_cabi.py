@@ -50,6 +50,7 @@ SIGNATURES = {
     "flare_reduce_sum": (_i, [_vp, _i, _i64, _i, _vp, _vp]),
     "flare_bwd_tokens": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_bwd_main": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_gather_noalloc": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_device_status": (_i, [C.POINTER(C.c_int), _i]),
     "flare_probe_ex2": (_i, [_i, _i, _vp, _vp]),
     "flare_bwd_dq_partial": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),

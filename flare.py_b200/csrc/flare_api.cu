@@ -89,6 +89,11 @@ int after_launch(const char* what) {
 
 }  // namespace
 
+namespace flare {
+// Lets entry points defined in other files of the library report through flare_last_error().
+void set_last_error(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg ? msg : ""); }
+}  // namespace flare
+
 extern "C" {
 
 int flare_version(void) { return 100; }

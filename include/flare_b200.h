@@ -155,6 +155,22 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
                    const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* delta_n, float* dq_part, flare_stream_t stream);
 
+/* Gather (first SDPA call) that allocates nothing and needs no workspace.  It has no counterpart
+ * in the reference.  It exists for callers that may not allocate device memory at the point of
+ * the call: plugins running inside a host framework's fixed memory plan, latency-critical service
+ * threads that must stay out of the allocator, callers that own nothing but the tensors passed in.
+ * The split-N partial records go to a FLARE_NOALLOC_SCRATCH_BYTES array built into the library
+ * (resident on every GPU that loads it, until exit).  Refused with FLARE_EWORKSPACE when one record
+ * set, B*H*M*(D+2) floats, does not fit; with fewer token ranges than usual when only those fit.
+ * Outputs as flare_combine: z32 fp32 [B,H,M,D], z_out in p->dtype, lse_m fp32 [B,H,M]; any may be
+ * NULL but not all.  All calls share the array: calls that overlap on the GPU (other streams,
+ * other host threads) race and must be serialised by the caller.  The first call on a device
+ * resolves the array's device address and should be made outside any stream capture. */
+#define FLARE_NOALLOC_SCRATCH_BYTES (16u << 20)
+int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, const void* v,
+                         const uint8_t* key_mask, float* z32, void* z_out, float* lse_m,
+                         flare_stream_t stream);
+
 /* Reads (and optionally clears) the device status word of the current device; synchronises.
  * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
