@@ -129,6 +129,21 @@ def pde_model_case(ref, name, seed):
     print(name, "params", sum(v.size for v in sd.values()))
 
 
+def lra_block_case(lra, name, seed):
+    """lra FLAREBlock (lra/models/backends.py:624-672) with a key-padding mask, eval mode."""
+    torch.manual_seed(seed)
+    blk = lra.FLAREBlock(channel_dim=64, num_heads=4, num_latents=16, kv_proj_hidden_dim=64,
+                         ffn_hidden_dim=64).eval()
+    x = torch.randn(3, 24, 64)
+    mask = torch.arange(24)[None, :] < torch.tensor([24, 17, 9])[:, None]
+    with torch.no_grad():
+        y = blk(x, attention_mask=mask)
+    sd = {k: np32(v) for k, v in blk.state_dict().items()}
+    np.savez_compressed(HERE / f"{name}.npz", x=np32(x), y=np32(y), mask=mask.numpy(),
+                        **{"sd::" + k: v for k, v in sd.items()})
+    print(name, "params", sum(v.size for v in sd.values()))
+
+
 def triton_ref_cases(root: Path):
     """Einsum references of the two Triton operators (triple.py:846-860, causal_linear.py:317-336).
 
@@ -164,6 +179,7 @@ def main():
     pde_mixer_case(ref, "pde_mixer_sqrt", B=1, N=80, C=64, H=4, M=24, scale=16 ** -0.5, seed=1)
     lra_mixer_case(lra, "lra_mixer_mask", B=3, N=40, C=32, H=4, M=16, scale=1.0, seed=2)
     pde_model_case(ref, "pde_model_contract", seed=0)
+    lra_block_case(lra, "lra_block_contract", seed=3)
     try:
         triton_ref_cases(root)
     except Exception as e:  # triton import without a GPU may fail on some images

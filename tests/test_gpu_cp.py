@@ -1,0 +1,84 @@
+"""Context-parallel mixer on GPUs: equals the unsharded mixer and the CPU oracle.
+
+With one GPU the group has a single rank (the collectives are trivial but the whole record ->
+merge -> gather -> combine -> scatter chain and its backward run on the device); with two or more
+GPUs the token axis is really sharded over NCCL ranks.
+"""
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q_out):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import flare_b200 as fb
+        from flare_b200.parallel import flare_mixer_context_parallel, shard_bounds
+        from oracle import flare_oracle as O
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            B, H, N, M, D, scale = 2, 4, 1500, 64, 32, 0.9
+            q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=7)
+            n0, n1 = shard_bounds(N, world, rank, multiple=128)
+            qd = q.to(dev).requires_grad_(True)
+            kd = k[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
+            vd = v[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
+            y = flare_mixer_context_parallel(qd, kd, vd, scale)
+            y.backward(dy[:, :, n0:n1].contiguous().to(dev))
+            torch.cuda.synchronize()
+            qf, kf, vf, dyf = (t.float() for t in (q, k, v, dy))
+            y_ref = O.mixer_sdpa(qf, kf, vf, scale)
+            dq_ref, dk_ref, dv_ref = O.mixer_bwd_closed_form(qf, kf, vf, dyf, scale)
+            errs = dict(y=O.rel_l2(y.float().cpu(), y_ref[:, :, n0:n1]), dq=O.rel_l2(qd.grad.float().cpu(), dq_ref),
+                        dk=O.rel_l2(kd.grad.float().cpu(), dk_ref[:, :, n0:n1]),
+                        dv=O.rel_l2(vd.grad.float().cpu(), dv_ref[:, :, n0:n1]))
+            bad = {n: e for n, e in errs.items() if not e <= tol}
+            assert not bad, (str(dtype), bad)
+        q_out.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        q_out.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world):
+    import __graft_entry__
+    __graft_entry__.build()
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q_out.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results
+
+
+def test_single_rank_group(cuda_dev):
+    _run(1)
+
+
+def test_two_ranks_shard_the_tokens(cuda_dev):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2)
