@@ -131,7 +131,7 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("v", v, p->v_stride, p->dtype));
   if (!rec) return fail(FLARE_EINVAL, "rec is null");
   Ctx c = make_ctx(p);
-  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_lat_supported(c, p->dtype)) {
+  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
     const int rc = tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("gather_partial (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "gather_partial (tcgen05): launch setup failed");
@@ -158,7 +158,7 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (!z32) return fail(FLARE_EINVAL, "z32 is null");
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
-  if (g_path.load() == FLARE_PATH_AUTO && tc_scatter_supported(c, p->dtype)) {
+  if (g_path.load() != FLARE_PATH_SIMT && tc_scatter_supported(c, p->dtype)) {
     const int rc = tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("scatter (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "scatter (tcgen05): launch setup failed");
@@ -177,7 +177,7 @@ int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
   if (!lse_n || !dz_part) return fail(FLARE_EINVAL, "lse_n or dz_part is null");
   Ctx c = make_ctx(p);
-  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_lat_supported(c, p->dtype)) {
+  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
     const int rc = tc_dz_partial(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("bwd_dz_partial (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_dz_partial (tcgen05): launch setup failed");
@@ -283,7 +283,7 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
   if (p->n_splits < 1) return fail(FLARE_EINVAL, "flare_bwd_main needs n_splits >= 1");
   if (!dq_part) return fail(FLARE_EINVAL, "dq_part is null");
   Ctx c = make_ctx(p, terms);
-  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && tc_bwd_supported(c, p->dtype)) {
+  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_bwd_supported(c, p->dtype)) {
     TRY(check_tok("q", q, p->q_stride, p->dtype));
     TRY(check_tok("k", k, p->k_stride, p->dtype));
     TRY(check_tok("v", v, p->v_stride, p->dtype));
@@ -292,7 +292,15 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
     TRY(check_tok("dk", dk, p->dk_stride, p->dtype));
     TRY(check_tok("dv", dv, p->dv_stride, p->dtype));
     if (!z32 || !dz32 || !lse_m || !lse_n) return fail(FLARE_EINVAL, "bwd_main: z32, dz32, lse_m, lse_n are required");
-    const int rc = tc_bwd_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, (cudaStream_t)stream);
+    // delta_n ([B,H,N] floats) is not needed by the fused kernels; it doubles as the scratch of the
+    // range check that picks, per (b, h), the one-exponential kernel or the exact one
+    const int* flag = nullptr;
+    int rc = FLARE_OK;
+    const size_t have = (size_t)p->B * p->H * (size_t)p->N * sizeof(float);
+    if (g_path.load() != FLARE_PATH_TC_EXACT && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
+        have >= tc_bwd2_scratch_bytes(c))
+      rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
+    if (rc == FLARE_OK) rc = tc_bwd_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("bwd_main (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_main (tcgen05): launch setup failed");
   }

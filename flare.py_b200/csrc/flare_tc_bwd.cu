@@ -40,6 +40,7 @@ struct BwdArgs {
   long long dks[3], dvs[3];
   float* dq_part;              // [S,B,H,M,D]
   int* status;
+  const int* flag;             // [B*H] or null: run only the (b, h) whose flag is 1
 };
 
 template <int D>
@@ -81,6 +82,7 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
   const int row = (warp & 3) * 32 + lane;          // token within the tile = tensor-memory lane
   const int split = blockIdx.x % a.n_splits;
   const int bh = blockIdx.x / a.n_splits;
+  if (a.flag && a.flag[bh] != 1) return;           // the one-exponential kernel owns this (b, h)
   const int b = bh / a.H, h = bh % a.H;
   const int M = a.M;
   const int n_mblk = (M + 127) / 128;
@@ -333,7 +335,7 @@ bool tc_bwd_supported(const Ctx& c, int dtype) {
 template <int D>
 static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                       const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk,
-                      void* dv, float* dq_part, cudaStream_t st) {
+                      void* dv, float* dq_part, const int* flag, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmV, tmG, tmY;
   const uint64_t e = 2;
   const bool qb = c.qs[0] != 0;
@@ -355,6 +357,7 @@ static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v,
   for (int i = 0; i < 3; ++i) { a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
+  a.flag = flag;
   static bool attr_done = false;
   constexpr int smem = BwdSmem<D>::kBytes;
   if (!attr_done) {
@@ -370,10 +373,10 @@ static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v,
 
 int tc_bwd_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                 const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                float* dq_part, cudaStream_t st) {
+                float* dq_part, const int* flag, cudaStream_t st) {
   switch (c.D) {
-    case 16: return launch_bwd<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, st);
-    case 32: return launch_bwd<32>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, st);
+    case 16: return launch_bwd<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
+    case 32: return launch_bwd<32>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
   }
   return FLARE_EUNSUPPORTED;
 }

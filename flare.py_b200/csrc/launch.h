@@ -37,7 +37,13 @@ int tc_dz_partial(const Ctx& c, const void* q, const void* k, const void* dy, co
 bool tc_bwd_supported(const Ctx& c, int dtype);
 int tc_bwd_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                 const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                float* dq_part, cudaStream_t st);
+                float* dq_part, const int* flag, cudaStream_t st);
+// One-exponential form of the same pass plus the on-device range check that selects, per (b, h),
+// between it (flag 0) and the exact kernel above (flag 1).
+size_t tc_bwd2_scratch_bytes(const Ctx& c);
+int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                 const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                 float* dq_part, void* scratch, const int** flag_out, cudaStream_t st);
 int tc_read_status(int* out, bool clear);
 int* tc_status_ptr();
 int num_sms();

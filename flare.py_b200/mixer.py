@@ -29,9 +29,9 @@ __all__ = [
 
 def set_kernel_path(path: str) -> str:
     """'auto' (tensor-core kernels where the shape allows) or 'simt'; returns the previous one."""
-    code = {"auto": _cabi.PATH_AUTO, "simt": _cabi.PATH_SIMT}[path]
+    code = {"auto": 0, "simt": 1, "tc_exact": 2}[path]
     prev = lib.flare_set_path(code)
-    return {v: k for k, v in {"auto": 0, "simt": 1}.items()}[prev]
+    return {0: "auto", 1: "simt", 2: "tc_exact"}[prev]
 
 
 def _need_cuda(*ts):

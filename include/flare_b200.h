@@ -60,6 +60,7 @@ extern "C" {
 /* kernel family (flare_set_path): tensor-core kernels when the shape allows, or SIMT only */
 #define FLARE_PATH_AUTO     0
 #define FLARE_PATH_SIMT     1
+#define FLARE_PATH_TC_EXACT 2    /* tensor-core kernels, but always the two-exponential backward */
 
 typedef void* flare_stream_t;    /* a cudaStream_t */
 
