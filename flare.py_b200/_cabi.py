@@ -52,6 +52,7 @@ SIGNATURES = {
     "flare_bwd_main": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_gather_noalloc": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_device_status": (_i, [C.POINTER(C.c_int), _i]),
+    "flare_debug_phase_counters": (_i, [_vp]),
     "flare_probe_ex2": (_i, [_i, _i, _vp, _vp]),
     "flare_bwd_dq_partial": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
 }

@@ -2,6 +2,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include "common.cuh"
 #include "launch.h"
@@ -47,6 +48,11 @@ int check_tok(const char* name, const void* ptr, const int64_t* st, int dtype) {
 }
 
 int auto_splits(const FlareProblem* p) {
+  // FLARE_SPLITS=<n> overrides the choice (tuning and experiments)
+  if (const char* env = getenv("FLARE_SPLITS")) {
+    const int v = atoi(env);
+    if (v >= 1) return v;
+  }
   const int tpt = p->D <= 32 ? 1 : p->D / 32;
   const int lpb = 128 / tpt;
   const long long base = (long long)p->B * p->H * ((p->M + lpb - 1) / lpb);
@@ -249,6 +255,11 @@ int flare_device_status(int* out, int clear) {
   if (!out) return fail(FLARE_EINVAL, "device_status: out is null");
   const int rc = tc_read_status(out, clear != 0);
   if (rc != FLARE_OK) return fail(rc, "device_status: %s", cudaGetErrorString(cudaGetLastError()));
+  return FLARE_OK;
+}
+
+int flare_debug_phase_counters(long long* dev_counters) {
+  tc_set_phase_counters(dev_counters);
   return FLARE_OK;
 }
 

@@ -21,6 +21,7 @@
 // One CTA of 512 threads per SM: thread (row, g) owns token row `row` (tensor-memory lane) and the
 // 32 latent columns [32g, 32g+32) of the current 128-latent block.  Tensor memory: S^T [0,128),
 // T' [128,256), dV 256, dK 288, dQ_j 320+32j.  Requires bf16, D in {16,32}, M <= 256.
+#include <cstdlib>
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -113,6 +114,7 @@ struct Bwd2Args {
   long long dks[3], dvs[3];
   float* dq_part;              // [S,B,H,M,D]
   int* status;
+  long long* prof;             // optional phase counters (clock cycles seen by thread 0), or null
 };
 
 template <int D>
@@ -191,7 +193,7 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-  constexpr uint32_t cS = 0, cT = 128, cDV = 256, cDK = 288, cDQ = 320;
+  constexpr uint32_t cS = 0, cT = 128, cDV = 256, cDK = 288, cDQ = 320, cP = 384, cDSp = 448;
 
   auto load_tile = [&](int stage, int tok0) {
     uint8_t* dst = sTok + stage * L::kStage;
@@ -262,21 +264,19 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   uint32_t ph_mma = 0;
   bool aborted = false;
 
-  for (int t = 0; t < n_tiles && !aborted; ++t) {
+  // Per-token operands of tile `t` (must have landed in stage t&1): eC_n, g_n = eC_n delta_n, the A'
+  // extension columns and the eC_n * dY_n tile.  Called by all threads; ends with the writes fenced
+  // for the tensor core but NOT with a CTA barrier (the caller's next barrier covers it).
+  auto prep_tile = [&](int t) {
     const int st = t & 1;
     const int tok0 = n0 + t * 128;
-    uint8_t* tK = sTok + st * L::kStage;
-    uint8_t* tV = tK + L::kT;
-    uint8_t* tG = tK + 2 * L::kT;
-    uint8_t* tY = tK + 3 * L::kT;
-    if (tid == 0 && t + 1 < n_tiles) load_tile(st ^ 1, tok0 + 128);   // every MMA of tile t-1 is complete
-    mbar_wait(&bar_full[st], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
-
-    // per-token scalars eC_n and g_n = eC_n delta_n, and the A' extension columns
+    const uint8_t* tG = sTok + st * L::kStage + 2 * L::kT;
+    const uint8_t* tY = sTok + st * L::kStage + 3 * L::kT;
     if (tid < 128) {
       const int n = tok0 + tid;
       float dl = 0.f, ec = 0.f;
       if (n < n1) {
+        const float c2 = cb[n] * kLog2e;
 #pragma unroll
         for (int c = 0; c < CPR; ++c) {
           const uint4 g4 = *reinterpret_cast<const uint4*>(tG + swz_off<ROWB>(tid, c));
@@ -289,10 +289,10 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
             dl = fmaf(gf.x, yf.x, dl); dl = fmaf(gf.y, yf.y, dl);
           }
         }
-        ec = ex2(mu - cb[n] * kLog2e);
+        ec = ex2(mu - c2);
       }
       const float gg = ec * dl;
-      sCD[st * 128 + tid] = make_float2(ec, gg);
+      sCD[tid] = make_float2(ec, gg);
       __nv_bfloat16 e[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) e[i] = __float2bfloat16_rn(0.f);
@@ -305,10 +305,9 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       *reinterpret_cast<uint4*>(sXA + swz_off<32>(tid, 1)) = src[1];
     }
     __syncthreads();
-    // eC_n * dY_n tile: one 16-byte chunk per thread
     for (int i = tid; i < 128 * CPR; i += 512) {
       const int r = i / CPR, c = i % CPR;
-      const float ec = sCD[st * 128 + r].x;
+      const float ec = sCD[r].x;
       const uint4 g4 = *reinterpret_cast<const uint4*>(tG + swz_off<ROWB>(r, c));
       const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
       uint4 o;
@@ -321,29 +320,96 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       *reinterpret_cast<uint4*>(sGe + swz_off<ROWB>(r, c)) = o;
     }
     fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
+  };
 
-    for (int j = 0; j < n_mblk; ++j) {
-      if (tid == 0) {
-        tc_fence_after();
-        const uint32_t lo = (uint32_t)(j * 128 * ROWB);
-        const uint64_t aK = smem_desc<ROWB>(smem_u32(tK)), aV = smem_desc<ROWB>(smem_u32(tV)),
-                       aG = smem_desc<ROWB>(smem_u32(sGe)), aX = smem_desc<32>(smem_u32(sXA));
-        const uint64_t bQ = smem_desc<ROWB>(smem_u32(sQ) + lo), bDZ = smem_desc<ROWB>(smem_u32(sDZ) + lo),
-                       bZe = smem_desc<ROWB>(smem_u32(sZe) + lo), bX = smem_desc<32>(smem_u32(sXB) + j * 128 * 32);
+  // S^T and T' of (tile in stage st, latent block j)
+  auto issue_p1 = [&](int st, int j) {
+    const uint8_t* tK = sTok + st * L::kStage;
+    const uint32_t lo = (uint32_t)(j * 128 * ROWB);
+    const uint64_t aK = smem_desc<ROWB>(smem_u32(tK)), aV = smem_desc<ROWB>(smem_u32(tK + L::kT)),
+                   aG = smem_desc<ROWB>(smem_u32(sGe)), aX = smem_desc<32>(smem_u32(sXA));
+    const uint64_t bQ = smem_desc<ROWB>(smem_u32(sQ) + lo), bDZ = smem_desc<ROWB>(smem_u32(sDZ) + lo),
+                   bZe = smem_desc<ROWB>(smem_u32(sZe) + lo), bX = smem_desc<32>(smem_u32(sXB) + j * 128 * 32);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cS, aK + 2 * kk, bQ + 2 * kk, id_st, kk > 0);
+    for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cS, aK + 2 * kk, bQ + 2 * kk, id_st, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT, aV + 2 * kk, bDZ + 2 * kk, id_st, kk > 0);
+    for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT, aV + 2 * kk, bDZ + 2 * kk, id_st, kk > 0);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT, aG + 2 * kk, bZe + 2 * kk, id_st, true);
-        mma_ss(tmem + cT, aX, bX, id_st, true);
-        mma_commit(bar_mma);
+    for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT, aG + 2 * kk, bZe + 2 * kk, id_st, true);
+    mma_ss(tmem + cT, aX, bX, id_st, true);
+  };
+
+  // dV += P^T dZ_j, dK += dS^T Q_j, dQ_j += dS K_t
+  auto issue_p2 = [&](int st, int j, bool first_tile) {
+    const uint8_t* tK = sTok + st * L::kStage;
+    const uint32_t lo = (uint32_t)(j * 128 * ROWB);
+    const uint64_t bDZ = smem_desc<ROWB>(smem_u32(sDZ) + lo), bQ = smem_desc<ROWB>(smem_u32(sQ) + lo);
+    const uint64_t bK = smem_desc<ROWB>(smem_u32(tK));
+    const uint64_t aDS = smem_desc_mn128(smem_u32(sDS), 128 * 128, 1024);
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {             // three independent accumulation chains, interleaved
+      const uint64_t boff = (uint64_t)((kk * 16 * ROWB) >> 4);
+      mma_ts(tmem + cDV, tmem + cP + 8 * kk, bDZ + boff, id_tv, (j > 0) || (kk > 0));      // over latents
+      mma_ts(tmem + cDK, tmem + cDSp + 8 * kk, bQ + boff, id_tv, (j > 0) || (kk > 0));     // over latents
+      mma_ss(tmem + cDQ + 32 * j, aDS + (uint64_t)((kk * 2048) >> 4), bK + boff, id_dq,    // over tokens
+             !first_tile || (kk > 0));
+    }
+  };
+
+  // dV (groups 0,1) and dK (groups 2,3) of tile t -> global, 16 columns per thread
+  auto store_tile = [&](int t) {
+    constexpr int HALVES = D / 16;
+    const int which = g >> 1, piece = g & 1;
+    if (piece < HALVES) {
+      uint32_t r[16];
+      tmem_ld16(lane_base + (which ? cDK : cDV) + 16 * piece, r);
+      tmem_wait_ld();
+      const int n = n0 + t * 128 + row;
+      if (n < n1) {
+        const float f = which ? a.scale : 1.f;
+        __nv_bfloat16* op = which ? a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
+                                  : a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
+        op += 16 * piece;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(r[8 * c]) * f, __uint_as_float(r[8 * c + 1]) * f);
+          o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
+          o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
+          o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
+          reinterpret_cast<uint4*>(op)[c] = o;
+        }
       }
+    }
+  };
+
+  // ---- prologue: operands of tile 0, then its first S^T / T' ------------------------------------
+  mbar_wait(&bar_full[0], 0, a.status, abort_flag);
+  prep_tile(0);
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    tc_fence_after();
+    issue_p1(0, 0);
+    mma_commit(bar_mma);
+  }
+
+  // One step = (tile t, latent block j).  The single commit of a step covers the dV/dK/dQ products of
+  // that step and the S^T/T' products of the next one, so there is one wait per step and the packed
+  // P and dS live in their own columns (never overwritten by an S^T/T' product that is in flight).
+  for (int t = 0; t < n_tiles && !aborted; ++t) {
+    const int st = t & 1;
+    for (int j = 0; j < n_mblk; ++j) {
+      long long c0 = a.prof ? clock64() : 0;
       mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
       ph_mma ^= 1;
       tc_fence_after();
+      long long c1 = a.prof ? clock64() : 0;
+      if (j == 0) {
+        // every product that read stage st^1 (tile t-1) is complete: refill it, and write out tile t-1
+        if (tid == 0 && t + 1 < n_tiles) load_tile(st ^ 1, n0 + (t + 1) * 128);
+        if (t > 0) store_tile(t - 1);
+      }
 
       // ---- P and dS = P * T' for this thread's token and its 32 latents of block j -------------
       {
@@ -367,78 +433,59 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           pd[2 * e] = pack_bf16(p0 * __uint_as_float(rt[4 * e]), p1 * __uint_as_float(rt[4 * e + 1]));
           pd[2 * e + 1] = pack_bf16(p2 * __uint_as_float(rt[4 * e + 2]), p3 * __uint_as_float(rt[4 * e + 3]));
         }
-        tmem_st16(lane_base + cS + colb, pp);
-        tmem_st16(lane_base + cT + colb, pd);
+        tmem_st16(lane_base + cP + 16 * g, pp);
+        tmem_st16(lane_base + cDSp + 16 * g, pd);
         const int cb0 = 4 * (g & 1);                           // first 16-byte chunk within the 128-byte row
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           *reinterpret_cast<uint4*>(ds_row + swz_off<128>(row, cb0 + c)) =
               make_uint4(pd[4 * c], pd[4 * c + 1], pd[4 * c + 2], pd[4 * c + 3]);
       }
+      const bool last_blk = (j + 1 == n_mblk);
+      const bool has_next_tile = (t + 1 < n_tiles);
+      long long c2 = a.prof ? clock64() : 0;
+      if (last_blk && has_next_tile) {            // operands of the next tile, while this step's stores drain
+        mbar_wait(&bar_full[st ^ 1], (uint32_t)((t + 1) >> 1) & 1, a.status, abort_flag);
+        prep_tile(t + 1);
+      }
+      long long c3 = a.prof ? clock64() : 0;
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       __syncthreads();
+      long long c4 = a.prof ? clock64() : 0;
       aborted = *reinterpret_cast<volatile int*>(abort_flag) != 0;
       if (aborted) break;
 
       if (tid == 0) {
         tc_fence_after();
-        const uint32_t lo = (uint32_t)(j * 128 * ROWB);
-        const uint64_t bDZ = smem_desc<ROWB>(smem_u32(sDZ) + lo), bQ = smem_desc<ROWB>(smem_u32(sQ) + lo);
-        const uint64_t bK = smem_desc<ROWB>(smem_u32(tK));
-        const uint64_t aDS = smem_desc_mn128(smem_u32(sDS), 128 * 128, 1024);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {           // contraction over the 128 latents of block j
-          const uint32_t acol = 32 * (kk >> 1) + 8 * (kk & 1);
-          const uint64_t boff = (uint64_t)((kk * 16 * ROWB) >> 4);
-          mma_ts(tmem + cDV, tmem + cS + acol, bDZ + boff, id_tv, (j > 0) || (kk > 0));
-          mma_ts(tmem + cDK, tmem + cT + acol, bQ + boff, id_tv, (j > 0) || (kk > 0));
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)             // contraction over the 128 tokens of the tile
-          mma_ss(tmem + cDQ + 32 * j, aDS + (uint64_t)((kk * 2048) >> 4), bK + (uint64_t)((kk * 16 * ROWB) >> 4),
-                 id_dq, (t > 0) || (kk > 0));
+        issue_p2(st, j, t == 0);
+        const long long c45 = a.prof ? clock64() : 0;
+        if (a.prof) atomicAdd((unsigned long long*)&a.prof[6], (unsigned long long)(c45 - c4));
+        if (!last_blk) issue_p1(st, j + 1);
+        else if (has_next_tile) issue_p1(st ^ 1, 0);
         mma_commit(bar_mma);
-      }
-      mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
-      ph_mma ^= 1;
-      tc_fence_after();
-    }
-    if (aborted) break;
-
-    // ---- dV (groups 0,1) and dK (groups 2,3) of this tile -> global, 16 columns per thread ------
-    {
-      constexpr int HALVES = D / 16;               // 16-column pieces per output row
-      const int which = g >> 1, piece = g & 1;
-      if (piece < HALVES) {
-        uint32_t r[16];
-        tmem_ld16(lane_base + (which ? cDK : cDV) + 16 * piece, r);
-        tmem_wait_ld();
-        const int n = tok0 + row;
-        if (n < n1) {
-          const float f = which ? a.scale : 1.f;
-          __nv_bfloat16* op = which ? a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
-                                    : a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
-          op += 16 * piece;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[8 * c]) * f, __uint_as_float(r[8 * c + 1]) * f);
-            o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
-            o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
-            o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
-            reinterpret_cast<uint4*>(op)[c] = o;
-          }
+        if (a.prof) {
+          const long long c5 = clock64();
+          atomicAdd((unsigned long long*)&a.prof[0], (unsigned long long)(c1 - c0));   // wait for the products
+          atomicAdd((unsigned long long*)&a.prof[1], (unsigned long long)(c2 - c1));   // stores + softmax math
+          atomicAdd((unsigned long long*)&a.prof[2], (unsigned long long)(c3 - c2));   // next tile's operands
+          atomicAdd((unsigned long long*)&a.prof[3], (unsigned long long)(c4 - c3));   // drain + CTA barrier
+          atomicAdd((unsigned long long*)&a.prof[4], (unsigned long long)(c5 - c4));   // issue
+          atomicAdd((unsigned long long*)&a.prof[5], 1ull);                             // steps
         }
       }
+      // the issuing lane's warp-mates wait here instead of racing ahead into the next barrier wait,
+      // where their polling would share the warp's issue slots with the lane that feeds the tensor core
+      if (warp == 0) __syncwarp();
     }
-    tc_fence_before();
-    __syncthreads();
   }
 
-  // ---- dQ partial of this range: block g/2, 16-column piece g%2 ---------------------------------
   if (!aborted) {
+    mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
+    tc_fence_after();
+    store_tile(n_tiles - 1);
+    // ---- dQ partial of this range: block g/2, 16-column piece g%2 -------------------------------
     const int j = g >> 1, piece = g & 1;
     if (j < n_mblk && piece < D / 16) {
       uint32_t r[16];
@@ -492,6 +539,7 @@ static int launch_bwd2(const Ctx& c, const void* q, const void* k, const void* v
   for (int i = 0; i < 3; ++i) { a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
+  a.prof = tc_phase_counters();
   static bool attr_done = false;
   constexpr int smem = Bwd2Smem<D>::kBytes;
   if (!attr_done) {
@@ -518,6 +566,10 @@ int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, cons
   k_bwd_range_c<<<dim3(kRangeParts, (unsigned)bh), 256, 0, st>>>(lse_n, c.N, part);
   k_bwd_range_final<<<(unsigned)bh, 256, 0, st>>>(lse_m, c.M, part, mu, flag);
   *flag_out = flag;
+  // the software-pipelined kernel (D = 32, 128 < M <= 256) is opt-in (FLARE_PIPELINE=1) until it beats
+  // the step-serial one
+  if (tc_bwd3_supported(c, FLARE_BF16) && getenv("FLARE_PIPELINE"))
+    return tc_bwd3_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
   switch (c.D) {
     case 16: return launch_bwd2<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
     case 32: return launch_bwd2<32>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);

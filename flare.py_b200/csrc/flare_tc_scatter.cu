@@ -238,6 +238,11 @@ int* tc_status_ptr() {
   return ptrs[dev];
 }
 
+// Optional phase counters for the tensor-core kernels (8 x int64 on the device), off by default.
+static long long* g_phase_counters = nullptr;
+void tc_set_phase_counters(long long* dev_ptr) { g_phase_counters = dev_ptr; }
+long long* tc_phase_counters() { return g_phase_counters; }
+
 int num_sms() {
   static int n = 0;
   if (!n) {

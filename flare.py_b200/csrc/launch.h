@@ -44,8 +44,14 @@ size_t tc_bwd2_scratch_bytes(const Ctx& c);
 int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                  const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                  float* dq_part, void* scratch, const int** flag_out, cudaStream_t st);
+bool tc_bwd3_supported(const Ctx& c, int dtype);
+int tc_bwd3_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                   const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                   float* dq_part, const float* mu, const int* flag, cudaStream_t st);
 int tc_read_status(int* out, bool clear);
 int* tc_status_ptr();
+void tc_set_phase_counters(long long* dev_ptr);
+long long* tc_phase_counters();
 int num_sms();
 
 }  // namespace flare

@@ -49,6 +49,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(64);      // waiting warps must not take issue slots from the warp that feeds the tensor core
     if (clock64() - t0 > (1LL << 31)) {
       if (status) atomicOr(status, kErrWaitTimeout);
       *reinterpret_cast<volatile int*>(abort_flag) = 1;

@@ -177,6 +177,13 @@ int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, co
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
 int flare_device_status(int* out, int clear);
 
+/* Tracing aid, no counterpart in the reference: when given a device array of 8 int64 (zeroed by
+ * the caller), the fused backward kernel adds the clock cycles its issuing thread spends in each
+ * phase of a step: [0] waiting for tensor-core products, [1] softmax math and stores, [2] preparing
+ * the next tile's operands, [3] draining stores + CTA barrier, [4] issuing products, [5] step count.
+ * NULL (the default) switches the counters off. */
+int flare_debug_phase_counters(long long* dev_counters);
+
 /* Measurement aid, no counterpart in the reference: launches `blocks` x 256 threads that each
  * issue 8*iters dependent-chain ex2 operations, so that the benchmark can time the exponential
  * unit's peak on the device it runs on.  `out` is one device float (never written in practice). */
