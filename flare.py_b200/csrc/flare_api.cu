@@ -138,7 +138,9 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
   if (!rec) return fail(FLARE_EINVAL, "rec is null");
   Ctx c = make_ctx(p);
   if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
-    const int rc = tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
+    const int rc = (tc_lat2_supported(c, p->dtype) && !getenv("FLARE_LAT_V1"))
+                       ? tc_gather_partial2(c, q, k, v, rec, (cudaStream_t)stream)
+                       : tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("gather_partial (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "gather_partial (tcgen05): launch setup failed");
   }
@@ -184,7 +186,9 @@ int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, co
   if (!lse_n || !dz_part) return fail(FLARE_EINVAL, "lse_n or dz_part is null");
   Ctx c = make_ctx(p);
   if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
-    const int rc = tc_dz_partial(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream);
+    const int rc = (tc_lat2_supported(c, p->dtype) && !getenv("FLARE_LAT_V1"))
+                       ? tc_dz_partial2(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream)
+                       : tc_dz_partial(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("bwd_dz_partial (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_dz_partial (tcgen05): launch setup failed");
   }

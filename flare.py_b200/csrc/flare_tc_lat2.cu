@@ -1,0 +1,406 @@
+// Latent-major split-N passes on tcgen05 tensor cores, decoupled schedule (D <= 32).
+//
+//   MODE 0  gather : record (acc, m, l) of z = softmax_N(S) v over one token range
+//   MODE 1  dZ     : dz_part = sum_n exp(S_mn - C_n) dY_n over one token range
+//
+// Same mathematics and tiling as flare_tc_lat.cu (one CTA = 128 latents x one token range, 128-token
+// tiles, S = Q K^T and acc += P V on the tensor core, P packed over S in tensor memory).  Differences:
+//   * A dedicated issuer warp feeds the tensor core; the 256 softmax threads (two per latent row, 64
+//     score columns each) never issue and never wait for more than the S product of their tile:
+//     S(t+1) is committed on its own mbarrier ahead of P(t) V(t).
+//   * No separate row-max pass in steady state.  The running maximum m_run only has to stay within
+//     2^60 of the true one; a Cauchy-Schwarz bound |q_m| max_n |k_n| on the tile's scores (row norms of
+//     the K tile, computed while the S product runs) tells when that is guaranteed.  Only the first
+//     tile and tiles whose bound exceeds m_run + 60 take the exact max pass (two halves of a row meet
+//     through shared memory) and rescale the accumulator.
+//   * Tensor-memory columns: S of even tiles [0,128), of odd tiles [96,224); P of even tiles
+//     {[0,32), [64,96)}, of odd tiles {[128,160), [192,224)}; accumulator [224,256).  Every thread
+//     packs P inside its own score columns, S(t+1) never touches P(t), and S(t+2) is issued only after
+//     P(t) V(t) has completed.
+//   * K/V tiles arrive in a three-stage TMA ring (two tiles of prefetch distance).
+// Two CTAs (288 threads each) share an SM.
+#include "common.cuh"
+#include "launch.h"
+#include "tc_common.cuh"
+#include "tma_host.h"
+
+namespace flare {
+
+using namespace tc;
+
+struct Lat2Args {
+  int B, H, N, M;
+  float scale_log2;
+  int q_batched;
+  int n_splits, chunk, n_mblk;
+  const float* lse_n;          // MODE 1: [B,H,N]
+  float* out;                  // MODE 0: rec [S,B,H,M,D+2]; MODE 1: dz_part [S,B,H,M,D]
+  int* status;
+};
+
+template <int D>
+struct Lat2Smem {
+  static constexpr int ROWB = 2 * D;
+  static constexpr int kQ = 128 * ROWB;
+  static constexpr int kT = 128 * ROWB;            // one K or V tile
+  static constexpr int kBytes = kQ + 6 * kT + 3 * 128 * 4 /*C*/ + 2 * 128 * 4 /*max*/ + 128 * 4 /*l*/ + 64 /*kmax*/ + 1024 + 256;
+};
+
+__device__ __forceinline__ void mbar_arrive_l2(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+constexpr int kLat2Softmax = 256;
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(kLat2Softmax + 32, 2)
+k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+          const __grid_constant__ CUtensorMap tmV, Lat2Args a) {
+  constexpr int ROWB = 2 * D;
+  constexpr int CPR = ROWB / 16;
+  using L = Lat2Smem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + L::kQ;                        // [3]
+  uint8_t* sV = sK + 3 * L::kT;                    // [3]
+  float* sC2 = reinterpret_cast<float*>(sV + 3 * L::kT);   // [3][128]  C_n in log2 units (MODE 1)
+  float* sMax = sC2 + 3 * 128;                     // [2][128] half-row maxima (exact pass)
+  float* sLsum = sMax + 2 * 128;                   // [128]
+  float* sKmax = sLsum + 128;                      // [8] per-warp max of |k_n|^2
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKmax + 16);
+  uint64_t* bar_full = bars;                       // [3]
+  uint64_t* bar_s = bars + 3;                      // [2] S(t) complete
+  uint64_t* bar_pv = bars + 5;                     // [2] P(t) V(t) complete
+  uint64_t* bar_sm = bars + 7;                     // [2] softmax(t) done (256 arrivals)
+  uint64_t* bar_q = bars + 9;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  int* abort_flag = reinterpret_cast<int*>(bars + 11);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool is_issuer = warp == kLat2Softmax / 32;
+  const int half = (warp >> 2) & 1;                // which 64 of the tile's 128 score columns
+  const int row = (warp & 3) * 32 + lane;          // latent within the block = tensor-memory lane
+  const int mblk = blockIdx.x % a.n_mblk;
+  const int split = (blockIdx.x / a.n_mblk) % a.n_splits;
+  const int bh = blockIdx.x / (a.n_splits * a.n_mblk);
+  const int b = bh / a.H, h = bh % a.H;
+  const int n0 = split * a.chunk, n1 = min(a.N, n0 + a.chunk);
+  const int T = n1 > n0 ? (n1 - n0 + 127) / 128 : 0;
+  const int lat = mblk * 128 + row;
+
+  constexpr int W = (MODE == 0) ? D + 2 : D;
+  float* orow = a.out + ((((long long)split * a.B + b) * a.H + h) * a.M + lat) * W;
+
+  if (T == 0) {                                    // empty range: the neutral record
+    if (!is_issuer && half == 0 && lat < a.M) {
+      for (int i = 0; i < D; ++i) orow[i] = 0.f;
+      if (MODE == 0) { orow[D] = -INFINITY; orow[D + 1] = 0.f; }
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&bar_s[i], 1); mbar_init(&bar_pv[i], 1); mbar_init(&bar_sm[i], kLat2Softmax); }
+    mbar_init(bar_q, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+  constexpr uint32_t kAcc = 224;
+
+  auto load_tile = [&](int t) {
+    const int st = t % 3;
+    mbar_expect_tx(&bar_full[st], 2 * L::kT);
+    tma_load_4d(sK + st * L::kT, &tmK, &bar_full[st], 0, n0 + t * 128, h, b);
+    tma_load_4d(sV + st * L::kT, &tmV, &bar_full[st], 0, n0 + t * 128, h, b);
+  };
+
+  if (is_issuer) {
+    // ================================ issuer warp ================================
+    if (lane == 0) {
+      const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
+      const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
+      const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
+      mbar_expect_tx(bar_q, L::kQ);
+      tma_load_4d(sQ, &tmQ, bar_q, 0, mblk * 128, h, a.q_batched ? b : 0);
+      load_tile(0);
+      if (T > 1) load_tile(1);
+      mbar_wait(bar_q, 0, a.status, abort_flag);
+      mbar_wait(&bar_full[0], 0, a.status, abort_flag);
+      tc_fence_after();
+      {
+        const uint64_t dk = smem_desc<ROWB>(smem_u32(sK));
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+        mma_commit(&bar_s[0]);
+      }
+      for (int t = 0; t < T; ++t) {
+        const int p = t & 1;
+        mbar_wait(&bar_sm[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);       // P(t) written, S(t) consumed
+        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+        if (t >= 1) {
+          // P(t-1) V(t-1) complete: its packed P columns may be overwritten by S(t+1), and the
+          // stage of tile t-1 may take tile t+2
+          mbar_wait(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
+        }
+        if (t + 2 < T) load_tile(t + 2);
+        tc_fence_after();
+        if (t + 1 < T) {
+          mbar_wait(&bar_full[(t + 1) % 3], (uint32_t)((t + 1) / 3) & 1, a.status, abort_flag);
+          const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + ((t + 1) % 3) * L::kT));
+          const uint32_t sb = tmem + (p ? 0 : 96);                                  // region of tile t+1
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+          mma_commit(&bar_s[p ^ 1]);
+        }
+        {
+          const uint64_t dv = smem_desc<ROWB>(smem_u32(sV + (t % 3) * L::kT));
+          const uint32_t p0 = tmem + (p ? 128 : 0), p1 = tmem + (p ? 192 : 64);     // packed P of the two halves
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem + kAcc, (kk < 4 ? p0 + 8 * kk : p1 + 8 * (kk - 4)), dv + (uint64_t)((kk * 16 * ROWB) >> 4),
+                   idesc_pv, (t > 0) || (kk > 0));
+          mma_commit(&bar_pv[p]);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ================================ softmax threads ================================
+    const float sl = a.scale_log2;
+    const float* cb = (MODE == 1) ? a.lse_n + ((long long)b * a.H + h) * a.N : nullptr;
+    float m_run = -INFINITY, l_run = 0.f, qn = 0.f;
+    if (MODE == 0) {
+      // |q_m| of this thread's latent row (both halves compute the same value)
+      mbar_wait(bar_q, 0, a.status, abort_flag);
+      float s2 = 0.f;
+#pragma unroll
+      for (int c = 0; c < CPR; ++c) {
+        const uint4 q4 = *reinterpret_cast<const uint4*>(sQ + swz_off<ROWB>(row, c));
+        const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&q4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(qp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
+      }
+      qn = sqrtf(s2) * sl * 1.0001f;
+    }
+
+    for (int t = 0; t < T; ++t) {
+      const int p = t & 1, st = t % 3;
+      const int tile0 = n0 + t * 128;
+      const int cnt = min(128, n1 - tile0);
+      // ---- per-tile scalars, computed while the S product runs -------------------------------
+      mbar_wait(&bar_full[st], (uint32_t)(t / 3) & 1, a.status, abort_flag);
+      if (MODE == 1) {
+        if (tid < 128) sC2[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] * kLog2e : INFINITY;
+      } else {
+        // max_n |k_n|^2 of the tile: thread (n, part) reads half a row
+        const int n = tid >> 1, part = tid & 1;
+        float s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CPR / 2; ++c) {
+          const uint4 k4 = *reinterpret_cast<const uint4*>(sK + st * L::kT + swz_off<ROWB>(n, part * (CPR / 2) + c));
+          const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&k4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(kp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
+        }
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+#pragma unroll
+        for (int o = 2; o < 32; o <<= 1) s2 = fmaxf(s2, __shfl_xor_sync(0xffffffffu, s2, o));
+        if (lane == 0) sKmax[(p << 3) + warp] = s2;
+      }
+      named_bar_sync(2, kLat2Softmax);
+      float bound = 0.f;
+      if (MODE == 0) {
+        float k2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) k2 = fmaxf(k2, sKmax[(p << 3) + i]);
+        bound = qn * sqrtf(k2);                    // >= every score of this row in the tile, log2 units
+      }
+
+      mbar_wait(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
+      tc_fence_after();
+
+      // this thread's 64 score columns: two chunks of 32, the one that hosts P second-to-last
+      const uint32_t s_cols = lane_base + (p ? 96 : 0) + 64 * half;
+      uint32_t r0[32], r1[32];                     // r0 = columns [0,32) of the half, r1 = [32,64)
+      tmem_ld32(s_cols, r0);
+      tmem_ld32(s_cols + 32, r1);
+      tmem_wait_ld();
+
+      if (MODE == 0) {
+        const bool need = (t == 0) || (bound > m_run + 60.f);
+        if (__any_sync(0xffffffffu, need)) {       // the partner warp holds the same rows: same vote
+          float mx = -INFINITY;
+          const int c0 = 64 * half;
+          if (cnt == 128) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              mx = fmaxf(mx, (c0 + j < cnt) ? __uint_as_float(r0[j]) : -INFINITY);
+              mx = fmaxf(mx, (c0 + 32 + j < cnt) ? __uint_as_float(r1[j]) : -INFINITY);
+            }
+          }
+          sMax[half * 128 + row] = mx;
+          named_bar_sync(3 + (warp & 3), 64);      // the two warps of this lane quarter
+          const float tmax = fmaxf(mx, sMax[(half ^ 1) * 128 + row]) * sl;
+          const bool grow = tmax > m_run + 8.f;
+          if (t > 0 && __any_sync(0xffffffffu, grow)) {
+            const float f = grow ? ex2(m_run - tmax) : 1.f;
+            if (half == 0) {                       // one thread per row rescales the accumulator
+              mbar_wait(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
+              tc_fence_after();
+              uint32_t r[D];
+              if constexpr (D == 16) tmem_ld16(lane_base + kAcc, r); else tmem_ld32(lane_base + kAcc, r);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < D; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * f);
+              if constexpr (D == 16) tmem_st16(lane_base + kAcc, r); else tmem_st32(lane_base + kAcc, r);
+            }
+            l_run *= f;
+          }
+          if (grow) m_run = tmax;
+          named_bar_sync(3 + (warp & 3), 64);      // sMax may be rewritten next time only after both read it
+        }
+      }
+
+      // ---- one exponential per score; P packed inside this thread's own columns ----------------
+      float lsum = 0.f;
+      const float* c2p = (MODE == 1) ? sC2 + st * 128 + 64 * half : nullptr;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = p ? 1 - cc : cc;             // odd tiles: upper chunk first (P lives in the upper chunk)
+        const uint32_t* r = c ? r1 : r0;
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          float x0, x1;
+          if (MODE == 0) {
+            x0 = fmaf(__uint_as_float(r[2 * j]), sl, -m_run);
+            x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -m_run);
+          } else {
+            const float2 cc2 = *reinterpret_cast<const float2*>(c2p + 32 * c + 2 * j);
+            x0 = fmaf(__uint_as_float(r[2 * j]), sl, -cc2.x);
+            x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -cc2.y);
+          }
+          float e0 = ex2(x0), e1 = ex2(x1);
+          if (MODE == 0 && cnt < 128) {
+            if (64 * half + 32 * c + 2 * j >= cnt) e0 = 0.f;
+            if (64 * half + 32 * c + 2 * j + 1 >= cnt) e1 = 0.f;
+          }
+          lsum += e0 + e1;
+          pk[j] = pack_bf16(e0, e1);
+        }
+        // even tiles: P at [0,32) of the half's 64 columns; odd tiles: at [32,64)
+        tmem_st16(s_cols + (p ? 32 : 0) + 16 * c, pk);
+      }
+      l_run += lsum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_l2(&bar_sm[p]);
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+    }
+
+    // ---- epilogue ---------------------------------------------------------------------------
+    if (!*reinterpret_cast<volatile int*>(abort_flag)) {
+      if (MODE == 0) {
+        if (half == 1) sLsum[row] = l_run;
+        named_bar_sync(2, kLat2Softmax);
+        if (half == 0) l_run += sLsum[row];
+      }
+      mbar_wait(&bar_pv[(T - 1) & 1], (uint32_t)((T - 1) >> 1) & 1, a.status, abort_flag);
+      tc_fence_after();
+      if (half == 0) {
+        uint32_t r[D];
+        if constexpr (D == 16) tmem_ld16(lane_base + kAcc, r); else tmem_ld32(lane_base + kAcc, r);
+        tmem_wait_ld();
+        if (lat < a.M) {
+#pragma unroll
+          for (int j = 0; j < D / 4; ++j) {
+            if constexpr (MODE == 1) {
+              reinterpret_cast<float4*>(orow)[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                               __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            } else {
+              reinterpret_cast<float2*>(orow)[2 * j] = make_float2(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]));
+              reinterpret_cast<float2*>(orow)[2 * j + 1] = make_float2(__uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+            }
+          }
+          if (MODE == 0) { orow[D] = m_run * kLn2; orow[D + 1] = l_run; }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc<256>(tmem);
+}
+
+// ------------------------------------------------------------------------------------------
+bool tc_lat2_supported(const Ctx& c, int dtype) {
+  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.N >= 1 && c.M >= 1;
+}
+
+template <int D, int MODE>
+static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v, const float* lse_n, float* out,
+                       cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t e = 2;
+  const bool qb = c.qs[0] != 0;
+  const long long* vs = (MODE == 0) ? c.vs : c.dys;
+  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
+                     (qb ? c.qs[0] : c.qs[1] * c.H) * e, 128) ||
+      !make_tile_map(&tmK, k, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
+                     (c.B > 1 ? c.ks[0] : c.ks[1] * c.H) * e, 128) ||
+      !make_tile_map(&tmV, v, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, vs[2] * e, vs[1] * e,
+                     (c.B > 1 ? vs[0] : vs[1] * c.H) * e, 128))
+    return FLARE_EUNSUPPORTED;
+  Lat2Args a;
+  a.B = c.B; a.H = c.H; a.N = c.N; a.M = c.M;
+  a.scale_log2 = c.scale * kLog2e;
+  a.q_batched = qb ? 1 : 0;
+  a.n_splits = c.n_splits; a.chunk = c.chunk; a.n_mblk = (c.M + 127) / 128;
+  a.lse_n = lse_n; a.out = out;
+  a.status = tc_status_ptr();
+  static bool attr_done = false;
+  constexpr int smem = Lat2Smem<D>::kBytes;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(k_tc_lat2<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return FLARE_ECUDA;
+    attr_done = true;
+  }
+  const long long grid = (long long)c.n_splits * a.n_mblk * c.B * c.H;
+  if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
+  k_tc_lat2<D, MODE><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
+  return FLARE_OK;
+}
+
+int tc_gather_partial2(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st) {
+  switch (c.D) {
+    case 16: return launch_lat2<16, 0>(c, q, k, v, nullptr, rec, st);
+    case 32: return launch_lat2<32, 0>(c, q, k, v, nullptr, rec, st);
+  }
+  return FLARE_EUNSUPPORTED;
+}
+
+int tc_dz_partial2(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,
+                   cudaStream_t st) {
+  switch (c.D) {
+    case 16: return launch_lat2<16, 1>(c, q, k, dy, lse_n, dz_part, st);
+    case 32: return launch_lat2<32, 1>(c, q, k, dy, lse_n, dz_part, st);
+  }
+  return FLARE_EUNSUPPORTED;
+}
+
+}  // namespace flare

@@ -34,6 +34,11 @@ bool tc_lat_supported(const Ctx& c, int dtype);
 int tc_gather_partial(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st);
 int tc_dz_partial(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,
                   cudaStream_t st);
+// decoupled-schedule versions of the two latent-major passes (D <= 32)
+bool tc_lat2_supported(const Ctx& c, int dtype);
+int tc_gather_partial2(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st);
+int tc_dz_partial2(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,
+                   cudaStream_t st);
 bool tc_bwd_supported(const Ctx& c, int dtype);
 int tc_bwd_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                 const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
