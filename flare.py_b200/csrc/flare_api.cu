@@ -167,7 +167,9 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
   if (g_path.load() != FLARE_PATH_SIMT && tc_scatter_supported(c, p->dtype)) {
-    const int rc = tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
+    const int rc = (tc_scatter2_supported(c, p->dtype) && !getenv("FLARE_SCATTER_V1"))
+                       ? tc_scatter2(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream)
+                       : tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("scatter (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "scatter (tcgen05): launch setup failed");
   }

@@ -388,10 +388,13 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   prep_tile(0);
   tc_fence_before();
   __syncthreads();
-  if (tid == 0) {
+  if (warp == 0) {                                // whole warp converged, one elected lane issues
     tc_fence_after();
-    issue_p1(0, 0);
-    mma_commit(bar_mma);
+    if (elect_one()) {
+      issue_p1(0, 0);
+      mma_commit(bar_mma);
+    }
+    __syncwarp();
   }
 
   // One step = (tile t, latent block j).  The single commit of a step covers the dV/dK/dQ products of
@@ -457,15 +460,16 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       aborted = *reinterpret_cast<volatile int*>(abort_flag) != 0;
       if (aborted) break;
 
-      if (tid == 0) {
+      if (warp == 0) {                            // whole warp converged, one elected lane issues
         tc_fence_after();
-        issue_p2(st, j, t == 0);
-        const long long c45 = a.prof ? clock64() : 0;
-        if (a.prof) atomicAdd((unsigned long long*)&a.prof[6], (unsigned long long)(c45 - c4));
-        if (!last_blk) issue_p1(st, j + 1);
-        else if (has_next_tile) issue_p1(st ^ 1, 0);
-        mma_commit(bar_mma);
-        if (a.prof) {
+        if (elect_one()) {
+          issue_p2(st, j, t == 0);
+          if (!last_blk) issue_p1(st, j + 1);
+          else if (has_next_tile) issue_p1(st ^ 1, 0);
+          mma_commit(bar_mma);
+        }
+        __syncwarp();
+        if (a.prof && tid == 0) {
           const long long c5 = clock64();
           atomicAdd((unsigned long long*)&a.prof[0], (unsigned long long)(c1 - c0));   // wait for the products
           atomicAdd((unsigned long long*)&a.prof[1], (unsigned long long)(c2 - c1));   // stores + softmax math
@@ -475,9 +479,6 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           atomicAdd((unsigned long long*)&a.prof[5], 1ull);                             // steps
         }
       }
-      // the issuing lane's warp-mates wait here instead of racing ahead into the next barrier wait,
-      // where their polling would share the warp's issue slots with the lane that feeds the tensor core
-      if (warp == 0) __syncwarp();
     }
   }
 
@@ -566,9 +567,9 @@ int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, cons
   k_bwd_range_c<<<dim3(kRangeParts, (unsigned)bh), 256, 0, st>>>(lse_n, c.N, part);
   k_bwd_range_final<<<(unsigned)bh, 256, 0, st>>>(lse_m, c.M, part, mu, flag);
   *flag_out = flag;
-  // the software-pipelined kernel (D = 32, 128 < M <= 256) is opt-in (FLARE_PIPELINE=1) until it beats
-  // the step-serial one
-  if (tc_bwd3_supported(c, FLARE_BF16) && getenv("FLARE_PIPELINE"))
+  // the software-pipelined kernel where it applies (D = 32, 128 < M <= 256), else the step-serial one;
+  // FLARE_NO_PIPELINE=1 forces the latter
+  if (tc_bwd3_supported(c, FLARE_BF16) && !getenv("FLARE_NO_PIPELINE"))
     return tc_bwd3_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
   switch (c.D) {
     case 16: return launch_bwd2<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);

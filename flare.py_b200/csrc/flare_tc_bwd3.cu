@@ -309,10 +309,11 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   tc_fence_before();
   __syncthreads();
   if (is_issuer) {
-    if (lane == 0) {
-      mbar_wait(bar_q, 0, a.status, abort_flag);
-      mbar_wait(&bar_full[0], 0, a.status, abort_flag);
-      tc_fence_after();
+    // the whole warp runs the issue code; one elected lane executes each TMA / MMA / commit
+    mbar_wait(bar_q, 0, a.status, abort_flag);
+    mbar_wait(&bar_full[0], 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
       issue_p1(0);
       if (U > 1) issue_p1(1);
       mma_commit(bar_pro);
@@ -322,37 +323,30 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   if (is_issuer) {
     // ================= issuer warp =================
-    if (lane == 0) {
-      for (int u = 0; u < U; ++u) {
-        const int xb = u & 1;
-        // token tile tau may be (re)loaded once every product that read its stage (tile tau-3) is complete
-        {
-          const int num = u - 1;
-          if (num >= 0 && num % n_sub == 0) {
-            const int tau = num / n_sub + 2;
-            if (tau >= 2 && tau < n_tiles) {
-              if (u >= 2) mbar_wait(&bar_c[xb], (uint32_t)((u >> 1) - 1) & 1, a.status, abort_flag);
-              load_tile(tau);
-            }
+    for (int u = 0; u < U; ++u) {
+      const int xb = u & 1;
+      // token tile tau may be (re)loaded once every product that read its stage (tile tau-3) is complete
+      {
+        const int num = u - 1;
+        if (num >= 0 && num % n_sub == 0) {
+          const int tau = num / n_sub + 2;
+          if (tau >= 2 && tau < n_tiles) {
+            if (u >= 2) mbar_wait(&bar_c[xb], (uint32_t)((u >> 1) - 1) & 1, a.status, abort_flag);
+            if (elect_one()) load_tile(tau);
+            __syncwarp();
           }
         }
-        const long long i0 = a.prof ? clock64() : 0;
-        mbar_wait(&bar_simt[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
-        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
-        tc_fence_after();
-        const long long i1 = a.prof ? clock64() : 0;
+      }
+      mbar_wait(&bar_simt[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      tc_fence_after();
+      if (elect_one()) {
         issue_p2(u);
         if (u + 2 < U) issue_p1(u + 2);
         mma_commit(&bar_c[xb]);
-        if (a.prof) {
-          const long long i2 = clock64();
-          atomicAdd((unsigned long long*)&a.prof[0], (unsigned long long)(i1 - i0));   // issuer waits for softmax
-          atomicAdd((unsigned long long*)&a.prof[4], (unsigned long long)(i2 - i1));   // issue
-          atomicAdd((unsigned long long*)&a.prof[5], 1ull);
-        }
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ================= softmax threads =================
     for (int u = 0; u < U; ++u) {

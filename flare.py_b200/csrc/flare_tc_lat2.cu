@@ -128,22 +128,29 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   if (is_issuer) {
     // ================================ issuer warp ================================
-    if (lane == 0) {
+    // The whole warp runs this code; one elected lane executes each TMA / MMA / commit.
+    {
       const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
       const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
       const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
-      mbar_expect_tx(bar_q, L::kQ);
-      tma_load_4d(sQ, &tmQ, bar_q, 0, mblk * 128, h, a.q_batched ? b : 0);
-      load_tile(0);
-      if (T > 1) load_tile(1);
+      if (elect_one()) {
+        mbar_expect_tx(bar_q, L::kQ);
+        tma_load_4d(sQ, &tmQ, bar_q, 0, mblk * 128, h, a.q_batched ? b : 0);
+        load_tile(0);
+        if (T > 1) load_tile(1);
+      }
+      __syncwarp();
       mbar_wait(bar_q, 0, a.status, abort_flag);
       mbar_wait(&bar_full[0], 0, a.status, abort_flag);
       tc_fence_after();
       {
         const uint64_t dk = smem_desc<ROWB>(smem_u32(sK));
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-        mma_commit(&bar_s[0]);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+          mma_commit(&bar_s[0]);
+        }
+        __syncwarp();
       }
       for (int t = 0; t < T; ++t) {
         const int p = t & 1;
@@ -154,24 +161,31 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           // stage of tile t-1 may take tile t+2
           mbar_wait(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
         }
-        if (t + 2 < T) load_tile(t + 2);
+        if (t + 2 < T && elect_one()) load_tile(t + 2);
+        __syncwarp();
         tc_fence_after();
         if (t + 1 < T) {
           mbar_wait(&bar_full[(t + 1) % 3], (uint32_t)((t + 1) / 3) & 1, a.status, abort_flag);
           const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + ((t + 1) % 3) * L::kT));
           const uint32_t sb = tmem + (p ? 0 : 96);                                  // region of tile t+1
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-          mma_commit(&bar_s[p ^ 1]);
+            for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+            mma_commit(&bar_s[p ^ 1]);
+          }
+          __syncwarp();
         }
         {
           const uint64_t dv = smem_desc<ROWB>(smem_u32(sV + (t % 3) * L::kT));
           const uint32_t p0 = tmem + (p ? 128 : 0), p1 = tmem + (p ? 192 : 64);     // packed P of the two halves
+          if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem + kAcc, (kk < 4 ? p0 + 8 * kk : p1 + 8 * (kk - 4)), dv + (uint64_t)((kk * 16 * ROWB) >> 4),
-                   idesc_pv, (t > 0) || (kk > 0));
-          mma_commit(&bar_pv[p]);
+            for (int kk = 0; kk < 8; ++kk)
+              mma_ts(tmem + kAcc, (kk < 4 ? p0 + 8 * kk : p1 + 8 * (kk - 4)), dv + (uint64_t)((kk * 16 * ROWB) >> 4),
+                     idesc_pv, (t > 0) || (kk > 0));
+            mma_commit(&bar_pv[p]);
+          }
+          __syncwarp();
         }
       }
     }

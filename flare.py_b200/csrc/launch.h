@@ -30,6 +30,10 @@ int launch_probe_ex2(int blocks, int iters, float* out, cudaStream_t st);
 bool tc_scatter_supported(const Ctx& c, int dtype);
 int tc_scatter(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
                float* lse_n, cudaStream_t st);
+// decoupled-schedule scatter (one CTA per SM, two tiles in flight; D <= 32)
+bool tc_scatter2_supported(const Ctx& c, int dtype);
+int tc_scatter2(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
+                float* lse_n, cudaStream_t st);
 bool tc_lat_supported(const Ctx& c, int dtype);
 int tc_gather_partial(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st);
 int tc_dz_partial(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,

@@ -21,6 +21,16 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// One lane of a fully converged warp.  TMA and tcgen05.mma/commit must be issued this way (whole warp
+// runs the surrounding code, one elected lane executes the instruction): the operands then stay in
+// the warp-uniform datapath and a 128x32x16 product issues every ~16 clocks; from a divergent single
+// lane (if (lane == 0) ...) the same instruction stream was measured at ~45-90 clocks per product.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
