@@ -154,6 +154,8 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     if (n_tiles > 1) load_tile(1);
   }
   const float mu = a.mu[bh];
+  long long k_c0 = 0; unsigned long long k_t0 = 0;
+  if (a.prof && tid == 0 && blockIdx.x == 0) { k_c0 = clock64(); asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(k_t0)); }
   // resident latent operands of B': dZ, eL*Z and the extension columns
   {
     const long long lrow = ((long long)b * a.H + h) * M;
@@ -256,8 +258,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   };
 
   // S^T and T' of step u2 into buffer (u2 & 1)
-  auto issue_p1 = [&](int u2) {
-    const int tau = u2 / n_sub, s = u2 % n_sub;
+  auto issue_p1 = [&](int u2, int tau, int s) {
     const uint8_t* tK = sTok + (tau % 3) * L::kStage;
     const uint32_t lo = (uint32_t)(s * 64 * ROWB);
     const uint32_t cx = tmem + cX + 128 * (u2 & 1);
@@ -275,8 +276,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     mma_ss(cx + 64, aX, bX, id_st, true);
   };
   // dV += P^T dZ_s, dK += dS^T Q_s, and after the last slice of a 128-latent block dQ_j += dS K_t
-  auto issue_p2 = [&](int u) {
-    const int t = u / n_sub, s = u % n_sub;
+  auto issue_p2 = [&](int u, int t, int s) {
     const uint8_t* tK = sTok + (t % 3) * L::kStage;
     const uint32_t lo = (uint32_t)(s * 64 * ROWB);
     const uint32_t cpd = tmem + cPD + 64 * (u & 1);
@@ -298,6 +298,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     }
   };
 
+  if (a.prof && tid == 0 && blockIdx.x == 0) a.prof[11] = clock64() - k_c0;   // resident operands built
   // ---- prologue --------------------------------------------------------------------------------
   if (!is_issuer) {
     uint4 yv; float cbv;
@@ -314,51 +315,56 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     mbar_wait(&bar_full[0], 0, a.status, abort_flag);
     tc_fence_after();
     if (elect_one()) {
-      issue_p1(0);
-      if (U > 1) issue_p1(1);
+      issue_p1(0, 0, 0);
+      if (U > 1) issue_p1(1, 0, 1);
       mma_commit(bar_pro);
     }
     __syncwarp();
   }
 
+  if (a.prof && tid == 0 && blockIdx.x == 0) a.prof[12] = clock64() - k_c0;   // loop starts
   if (is_issuer) {
     // ================= issuer warp =================
+    int t = 0, s = 0;                              // step u = (tile t, slice s), tracked without divisions
     for (int u = 0; u < U; ++u) {
       const int xb = u & 1;
-      // token tile tau may be (re)loaded once every product that read its stage (tile tau-3) is complete
-      {
-        const int num = u - 1;
-        if (num >= 0 && num % n_sub == 0) {
-          const int tau = num / n_sub + 2;
-          if (tau >= 2 && tau < n_tiles) {
-            if (u >= 2) mbar_wait(&bar_c[xb], (uint32_t)((u >> 1) - 1) & 1, a.status, abort_flag);
-            if (elect_one()) load_tile(tau);
-            __syncwarp();
-          }
-        }
+      // token tile t+2 may be (re)loaded at slice 1 of tile t: every product that read its stage
+      // (tile t-1) is complete once the commit of step u-2 has arrived
+      if (s == 1 && t + 2 < n_tiles) {
+        if (u >= 2) mbar_wait(&bar_c[xb], (uint32_t)((u >> 1) - 1) & 1, a.status, abort_flag);
+        if (elect_one()) load_tile(t + 2);
+        __syncwarp();
       }
       mbar_wait(&bar_simt[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       tc_fence_after();
+      int t2 = t, s2 = s + 2;                      // (tile, slice) of step u+2
+      if (s2 >= n_sub) { s2 -= n_sub; ++t2; }
       if (elect_one()) {
-        issue_p2(u);
-        if (u + 2 < U) issue_p1(u + 2);
+        issue_p2(u, t, s);
+        if (u + 2 < U) issue_p1(u + 2, t2, s2);
         mma_commit(&bar_c[xb]);
       }
       __syncwarp();
+      if (++s == n_sub) { s = 0; ++t; }
     }
   } else {
     // ================= softmax threads =================
-    for (int u = 0; u < U; ++u) {
+    long long s_prev = 0;
+    int t = 0, s = 0;                              // step u = (tile t, slice s), tracked without divisions
+    for (int u = 0; u < U; ++u, s = (s + 1 == n_sub ? 0 : s + 1), t += (s == 0)) {
       const int xb = u & 1;
-      const int t = u / n_sub, s = u % n_sub;
-      // operands of a later tile are due when the product two steps ahead first belongs to it
-      const int tau_p = (u + 2) / n_sub;
-      const bool do_prep = ((u + 2) % n_sub == 0) && tau_p < n_tiles;
+      // operands of the next tile are due when the product two steps ahead first belongs to it
+      const int tau_p = t + 1;
+      const bool do_prep = (s == n_sub - 2) && tau_p < n_tiles;
       uint4 yv = make_uint4(0, 0, 0, 0); float cbv = 0.f;
       if (do_prep) fetch_y(tau_p, yv, cbv);
 
       const long long s0 = (a.prof && tid == 0) ? clock64() : 0;
+      if (a.prof && tid == 0 && u > 0) atomicAdd((unsigned long long*)&a.prof[15], (unsigned long long)(s0 - s_prev));
+      s_prev = s0;
+      const long long sA = s0;
+      (void)sA;
       if (u >= 2) mbar_wait(&bar_c[xb], (uint32_t)((u >> 1) - 1) & 1, a.status, abort_flag);
       else mbar_wait(bar_pro, 0, a.status, abort_flag);
       tc_fence_after();
@@ -438,6 +444,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
     }
 
+    if (a.prof && tid == 0 && blockIdx.x == 0) a.prof[10] = clock64() - k_c0;   // loop ends
     // ---- tail: last tile's dV/dK and the dQ partial ------------------------------------------------
     if (!*reinterpret_cast<volatile int*>(abort_flag)) {
       if (U >= 2) mbar_wait(&bar_c[(U - 2) & 1], (uint32_t)((U - 2) >> 1) & 1, a.status, abort_flag);
@@ -481,6 +488,10 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc<512>(tmem);
+  if (a.prof && tid == 0 && blockIdx.x == 0) {
+    unsigned long long k_t1; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(k_t1));
+    a.prof[13] = clock64() - k_c0; a.prof[14] = (long long)(k_t1 - k_t0);
+  }
 }
 
 // ------------------------------------------------------------------------------------------
