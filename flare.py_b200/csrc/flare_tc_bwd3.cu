@@ -70,9 +70,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int kSoftmaxThreads = 512;
+constexpr int kSoftmaxThreads = 512, kStoreThreads = 128;
 
-__global__ void __launch_bounds__(kSoftmaxThreads + 32, 1)
+__global__ void __launch_bounds__(kSoftmaxThreads + kStoreThreads + 32, 1)
 k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, Bwd3Args a) {
   constexpr int D = 32, ROWB = 64, CPR = 4;
@@ -98,11 +98,14 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   uint64_t* bar_simt = bars + 5;                   // [2] softmax threads done with step u
   uint64_t* bar_pro = bars + 7;                    // first two S^T/T' products
   uint64_t* bar_q = bars + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
-  int* abort_flag = reinterpret_cast<int*>(bars + 10);
+  uint64_t* bar_free = bars + 9;                   // dV/dK of a finished tile have been read (128 arrivals)
+  uint64_t* bar_tile = bars + 10;                  // every product of a tile is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  int* abort_flag = reinterpret_cast<int*>(bars + 12);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool is_issuer = warp == kSoftmaxThreads / 32;
+  const bool is_issuer = warp == (kSoftmaxThreads + kStoreThreads) / 32;
+  const bool is_store = !is_issuer && warp >= kSoftmaxThreads / 32;   // four warps that write dV/dK of finished tiles
   const int g = (warp >> 2) & 3;                   // column group 0..3 (16 latent columns of a slice)
   const int row = (warp & 3) * 32 + lane;          // token within the tile = tensor-memory lane
   const int b = bh / a.H, h = bh % a.H;
@@ -122,7 +125,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
     mbar_init(&bar_c[0], 1); mbar_init(&bar_c[1], 1);
     mbar_init(&bar_simt[0], kSoftmaxThreads); mbar_init(&bar_simt[1], kSoftmaxThreads);
-    mbar_init(bar_pro, 1); mbar_init(bar_q, 1);
+    mbar_init(bar_pro, 1); mbar_init(bar_q, 1); mbar_init(bar_free, kStoreThreads); mbar_init(bar_tile, 1);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmG);
@@ -300,11 +303,15 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   if (a.prof && tid == 0 && blockIdx.x == 0) a.prof[11] = clock64() - k_c0;   // resident operands built
   // ---- prologue --------------------------------------------------------------------------------
-  if (!is_issuer) {
-    uint4 yv; float cbv;
-    fetch_y(0, yv, cbv);
+  // Y rows and C_n of the tile whose operands are prepared next; loaded a whole tile ahead so that the
+  // DRAM latency never sits on the softmax threads' critical path
+  uint4 yv_next = make_uint4(0, 0, 0, 0);
+  float cb_next = 0.f;
+  if (!is_issuer && !is_store) {
+    fetch_y(0, yv_next, cb_next);
     mbar_wait(&bar_full[0], 0, a.status, abort_flag);
-    prep_tile(0, yv, cbv);
+    prep_tile(0, yv_next, cb_next);
+    if (n_tiles > 1) fetch_y(1, yv_next, cb_next);
   }
   fence_proxy_async();
   tc_fence_before();
@@ -335,18 +342,72 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         if (elect_one()) load_tile(t + 2);
         __syncwarp();
       }
+      const long long i0 = (a.prof && lane == 0) ? clock64() : 0;
       mbar_wait(&bar_simt[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       tc_fence_after();
+      const long long i1 = (a.prof && lane == 0) ? clock64() : 0;
       int t2 = t, s2 = s + 2;                      // (tile, slice) of step u+2
       if (s2 >= n_sub) { s2 -= n_sub; ++t2; }
-      if (elect_one()) {
+      if (s == 0 && t > 0) {
+        // the dV/dK accumulators still hold tile t-1 until the store warps have read them: run the
+        // independent S^T/T' product first, then wait, then start this tile's accumulation
+        if (elect_one() && u + 2 < U) issue_p1(u + 2, t2, s2);
+        __syncwarp();
+        mbar_wait(bar_free, (uint32_t)(t - 1) & 1, a.status, abort_flag);
+        tc_fence_after();
+        if (elect_one()) {
+          issue_p2(u, t, s);
+          mma_commit(&bar_c[xb]);
+        }
+      } else if (elect_one()) {
         issue_p2(u, t, s);
         if (u + 2 < U) issue_p1(u + 2, t2, s2);
         mma_commit(&bar_c[xb]);
+        if (s == n_sub - 1) mma_commit(bar_tile);  // one phase per tile: the store warps follow it in order
       }
       __syncwarp();
+      if (a.prof && lane == 0) {
+        const long long i2 = clock64();
+        atomicAdd((unsigned long long*)&a.prof[0], (unsigned long long)(i1 - i0));   // issuer waits for softmax
+        atomicAdd((unsigned long long*)&a.prof[4], (unsigned long long)(i2 - i1));   // issue
+      }
       if (++s == n_sub) { s = 0; ++t; }
+    }
+  } else if (is_store) {
+    // ================= store warps: dV/dK of every finished tile -> global =================
+    for (int t = 0; t < n_tiles; ++t) {
+      mbar_wait(bar_tile, (uint32_t)t & 1, a.status, abort_flag);
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      tc_fence_after();
+      // four 16-column pieces (dV low/high, dK low/high) keep this role's register use small
+      uint32_t r[4][16];
+      tmem_ld16(lane_base + cDV, r[0]);
+      tmem_ld16(lane_base + cDV + 16, r[1]);
+      tmem_ld16(lane_base + cDK, r[2]);
+      tmem_ld16(lane_base + cDK + 16, r[3]);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar_free);
+      const int n = n0 + t * 128 + row;
+      if (n < n1) {
+        __nv_bfloat16* pv = a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
+        __nv_bfloat16* pk = a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2];
+#pragma unroll
+        for (int pc = 0; pc < 4; ++pc) {
+          const float f = pc >= 2 ? a.scale : 1.f;
+          __nv_bfloat16* op = (pc >= 2 ? pk : pv) + 16 * (pc & 1);
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[pc][8 * c]) * f, __uint_as_float(r[pc][8 * c + 1]) * f);
+            o.y = pack_bf16(__uint_as_float(r[pc][8 * c + 2]) * f, __uint_as_float(r[pc][8 * c + 3]) * f);
+            o.z = pack_bf16(__uint_as_float(r[pc][8 * c + 4]) * f, __uint_as_float(r[pc][8 * c + 5]) * f);
+            o.w = pack_bf16(__uint_as_float(r[pc][8 * c + 6]) * f, __uint_as_float(r[pc][8 * c + 7]) * f);
+            reinterpret_cast<uint4*>(op)[c] = o;
+          }
+        }
+      }
     }
   } else {
     // ================= softmax threads =================
@@ -357,8 +418,6 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       // operands of the next tile are due when the product two steps ahead first belongs to it
       const int tau_p = t + 1;
       const bool do_prep = (s == n_sub - 2) && tau_p < n_tiles;
-      uint4 yv = make_uint4(0, 0, 0, 0); float cbv = 0.f;
-      if (do_prep) fetch_y(tau_p, yv, cbv);
 
       const long long s0 = (a.prof && tid == 0) ? clock64() : 0;
       if (a.prof && tid == 0 && u > 0) atomicAdd((unsigned long long*)&a.prof[15], (unsigned long long)(s0 - s_prev));
@@ -401,35 +460,10 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       const long long s2 = (a.prof && tid == 0) ? clock64() : 0;
       if (do_prep) {
         mbar_wait(&bar_full[tau_p % 3], (uint32_t)(tau_p / 3) & 1, a.status, abort_flag);
-        prep_tile(tau_p, yv, cbv);
+        prep_tile(tau_p, yv_next, cb_next);
+        if (tau_p + 1 < n_tiles) fetch_y(tau_p + 1, yv_next, cb_next);
       }
       const long long s3 = (a.prof && tid == 0) ? clock64() : 0;
-      if (s == 0 && t > 0) {
-        // dV/dK of the previous tile: its last products were committed by step u-1; write them out
-        // before the issuer starts this tile's accumulation
-        mbar_wait(&bar_c[xb ^ 1], (uint32_t)((u - 1) >> 1) & 1, a.status, abort_flag);
-        tc_fence_after();
-        const int which = g >> 1, piece = g & 1;
-        uint32_t r[16];
-        tmem_ld16(lane_base + (which ? cDK : cDV) + 16 * piece, r);
-        tmem_wait_ld();
-        const int n = n0 + (t - 1) * 128 + row;
-        if (n < n1) {
-          const float f = which ? a.scale : 1.f;
-          __nv_bfloat16* op = which ? a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
-                                    : a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
-          op += 16 * piece;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[8 * c]) * f, __uint_as_float(r[8 * c + 1]) * f);
-            o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
-            o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
-            o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
-            reinterpret_cast<uint4*>(op)[c] = o;
-          }
-        }
-      }
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
@@ -450,26 +484,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       if (U >= 2) mbar_wait(&bar_c[(U - 2) & 1], (uint32_t)((U - 2) >> 1) & 1, a.status, abort_flag);
       mbar_wait(&bar_c[(U - 1) & 1], (uint32_t)((U - 1) >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
-      const int which = g >> 1, piece = g & 1;
-      uint32_t r[16];
-      tmem_ld16(lane_base + (which ? cDK : cDV) + 16 * piece, r);
-      tmem_wait_ld();
-      const int n = n0 + (n_tiles - 1) * 128 + row;
-      if (n < n1) {
-        const float f = which ? a.scale : 1.f;
-        __nv_bfloat16* op = which ? a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
-                                  : a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
-        op += 16 * piece;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint4 o;
-          o.x = pack_bf16(__uint_as_float(r[8 * c]) * f, __uint_as_float(r[8 * c + 1]) * f);
-          o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
-          o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
-          o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
-          reinterpret_cast<uint4*>(op)[c] = o;
-        }
-      }
+      const int piece = g & 1;
       // dQ partial: latent block g/2, 16-column piece g%2
       const int j = g >> 1;
       uint32_t q[16];
@@ -536,7 +551,7 @@ int tc_bwd3_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   }
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_bwd3<<<(unsigned)grid, kSoftmaxThreads + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+  k_tc_bwd3<<<(unsigned)grid, kSoftmaxThreads + kStoreThreads + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
   return FLARE_OK;
 }
 
