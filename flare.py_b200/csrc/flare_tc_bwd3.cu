@@ -70,7 +70,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int kSoftmaxThreads = 512, kStoreThreads = 128;
+constexpr int kSoftmaxThreads = 512, kStoreThreads = 96;   // the issuer warp stores the fourth lane quarter
 
 __global__ void __launch_bounds__(kSoftmaxThreads + kStoreThreads + 32, 1)
 k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -105,7 +105,7 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_issuer = warp == (kSoftmaxThreads + kStoreThreads) / 32;
-  const bool is_store = !is_issuer && warp >= kSoftmaxThreads / 32;   // four warps that write dV/dK of finished tiles
+  const bool is_store = !is_issuer && warp >= kSoftmaxThreads / 32;   // three warps that write dV/dK of finished tiles
   const int g = (warp >> 2) & 3;                   // column group 0..3 (16 latent columns of a slice)
   const int row = (warp & 3) * 32 + lane;          // token within the tile = tensor-memory lane
   const int b = bh / a.H, h = bh % a.H;
@@ -302,6 +302,37 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   };
 
   if (a.prof && tid == 0 && blockIdx.x == 0) a.prof[11] = clock64() - k_c0;   // resident operands built
+  // dV/dK rows of tile t for this warp's lane quarter: tensor memory -> registers, then -> global
+  auto read_dvdk = [&](uint32_t (&r)[4][16]) {
+    tmem_ld16(lane_base + cDV, r[0]);
+    tmem_ld16(lane_base + cDV + 16, r[1]);
+    tmem_ld16(lane_base + cDK, r[2]);
+    tmem_ld16(lane_base + cDK + 16, r[3]);
+    tmem_wait_ld();
+    tc_fence_before();
+  };
+  auto write_dvdk = [&](int t, const uint32_t (&r)[4][16]) {
+    const int n = n0 + t * 128 + row;
+    if (n < n1) {
+      __nv_bfloat16* pv = a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
+      __nv_bfloat16* pk = a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2];
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        const float f = pc >= 2 ? a.scale : 1.f;
+        __nv_bfloat16* op = (pc >= 2 ? pk : pv) + 16 * (pc & 1);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(r[pc][8 * c]) * f, __uint_as_float(r[pc][8 * c + 1]) * f);
+          o.y = pack_bf16(__uint_as_float(r[pc][8 * c + 2]) * f, __uint_as_float(r[pc][8 * c + 3]) * f);
+          o.z = pack_bf16(__uint_as_float(r[pc][8 * c + 4]) * f, __uint_as_float(r[pc][8 * c + 5]) * f);
+          o.w = pack_bf16(__uint_as_float(r[pc][8 * c + 6]) * f, __uint_as_float(r[pc][8 * c + 7]) * f);
+          reinterpret_cast<uint4*>(op)[c] = o;
+        }
+      }
+    }
+  };
+
   // ---- prologue --------------------------------------------------------------------------------
   // Y rows and C_n of the tile whose operands are prepared next; loaded a whole tile ahead so that the
   // DRAM latency never sits on the softmax threads' critical path
@@ -350,16 +381,23 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       int t2 = t, s2 = s + 2;                      // (tile, slice) of step u+2
       if (s2 >= n_sub) { s2 -= n_sub; ++t2; }
       if (s == 0 && t > 0) {
-        // the dV/dK accumulators still hold tile t-1 until the store warps have read them: run the
-        // independent S^T/T' product first, then wait, then start this tile's accumulation
+        // the dV/dK accumulators still hold tile t-1 until they have been read: run the independent
+        // S^T/T' product first, read this warp's own lane quarter, wait for the three store warps,
+        // then start this tile's accumulation and write the quarter out
         if (elect_one() && u + 2 < U) issue_p1(u + 2, t2, s2);
         __syncwarp();
+        mbar_wait(bar_tile, (uint32_t)(t - 1) & 1, a.status, abort_flag);
+        tc_fence_after();
+        uint32_t r[4][16];
+        read_dvdk(r);
         mbar_wait(bar_free, (uint32_t)(t - 1) & 1, a.status, abort_flag);
         tc_fence_after();
         if (elect_one()) {
           issue_p2(u, t, s);
           mma_commit(&bar_c[xb]);
         }
+        __syncwarp();
+        write_dvdk(t - 1, r);
       } else if (elect_one()) {
         issue_p2(u, t, s);
         if (u + 2 < U) issue_p1(u + 2, t2, s2);
@@ -374,40 +412,23 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       }
       if (++s == n_sub) { s = 0; ++t; }
     }
+    if (!*reinterpret_cast<volatile int*>(abort_flag)) {   // this warp's quarter of the last tile
+      mbar_wait(bar_tile, (uint32_t)(n_tiles - 1) & 1, a.status, abort_flag);
+      tc_fence_after();
+      uint32_t r[4][16];
+      read_dvdk(r);
+      write_dvdk(n_tiles - 1, r);
+    }
   } else if (is_store) {
     // ================= store warps: dV/dK of every finished tile -> global =================
     for (int t = 0; t < n_tiles; ++t) {
       mbar_wait(bar_tile, (uint32_t)t & 1, a.status, abort_flag);
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       tc_fence_after();
-      // four 16-column pieces (dV low/high, dK low/high) keep this role's register use small
       uint32_t r[4][16];
-      tmem_ld16(lane_base + cDV, r[0]);
-      tmem_ld16(lane_base + cDV + 16, r[1]);
-      tmem_ld16(lane_base + cDK, r[2]);
-      tmem_ld16(lane_base + cDK + 16, r[3]);
-      tmem_wait_ld();
-      tc_fence_before();
+      read_dvdk(r);
       mbar_arrive(bar_free);
-      const int n = n0 + t * 128 + row;
-      if (n < n1) {
-        __nv_bfloat16* pv = a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
-        __nv_bfloat16* pk = a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2];
-#pragma unroll
-        for (int pc = 0; pc < 4; ++pc) {
-          const float f = pc >= 2 ? a.scale : 1.f;
-          __nv_bfloat16* op = (pc >= 2 ? pk : pv) + 16 * (pc & 1);
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[pc][8 * c]) * f, __uint_as_float(r[pc][8 * c + 1]) * f);
-            o.y = pack_bf16(__uint_as_float(r[pc][8 * c + 2]) * f, __uint_as_float(r[pc][8 * c + 3]) * f);
-            o.z = pack_bf16(__uint_as_float(r[pc][8 * c + 4]) * f, __uint_as_float(r[pc][8 * c + 5]) * f);
-            o.w = pack_bf16(__uint_as_float(r[pc][8 * c + 6]) * f, __uint_as_float(r[pc][8 * c + 7]) * f);
-            reinterpret_cast<uint4*>(op)[c] = o;
-          }
-        }
-      }
+      write_dvdk(t, r);
     }
   } else {
     // ================= softmax threads =================
@@ -436,11 +457,14 @@ k_tc_bwd3(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         uint32_t rs[16], rt[16];
         tmem_ld16(cx, rs);
         tmem_ld16(cx + 64, rt);
+        float4 l4s[4];                             // L_m of the 16 latents: fetched while the loads are in flight
+#pragma unroll
+        for (int e = 0; e < 4; ++e) l4s[e] = *reinterpret_cast<const float4*>(l2p + 4 * e);
         tmem_wait_ld();
         uint32_t pp[8], pd[8];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float4 l4 = *reinterpret_cast<const float4*>(l2p + 4 * e);
+          const float4 l4 = l4s[e];
           const float p0 = ex2(fmaf(__uint_as_float(rs[4 * e]), sl, -l4.x));
           const float p1 = ex2(fmaf(__uint_as_float(rs[4 * e + 1]), sl, -l4.y));
           const float p2 = ex2(fmaf(__uint_as_float(rs[4 * e + 2]), sl, -l4.z));
