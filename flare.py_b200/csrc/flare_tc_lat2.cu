@@ -10,14 +10,17 @@
 //     S(t+1) is committed on its own mbarrier ahead of P(t) V(t).
 //   * No separate row-max pass in steady state.  The running maximum m_run only has to stay within
 //     2^60 of the true one; a Cauchy-Schwarz bound |q_m| max_n |k_n| on the tile's scores (row norms of
-//     the K tile, computed while the S product runs) tells when that is guaranteed.  Only the first
+//     the K tile, computed by the issuer warp two tiles ahead) tells when that is guaranteed.  Only the first
 //     tile and tiles whose bound exceeds m_run + 60 take the exact max pass (two halves of a row meet
 //     through shared memory) and rescale the accumulator.
 //   * Tensor-memory columns: S of even tiles [0,128), of odd tiles [96,224); P of even tiles
 //     {[0,32), [64,96)}, of odd tiles {[128,160), [192,224)}; accumulator [224,256).  Every thread
 //     packs P inside its own score columns, S(t+1) never touches P(t), and S(t+2) is issued only after
 //     P(t) V(t) has completed.
-//   * K/V tiles arrive in a three-stage TMA ring (two tiles of prefetch distance).
+//   * K/V tiles arrive in a four-stage TMA ring (three tiles of prefetch distance); in MODE 1 the
+//     tile's C_n row rides on the same mbarrier as an untiled bulk copy.
+//   * The softmax threads read their 64 columns in four chunks of 16, one chunk ahead of the
+//     arithmetic, so that few registers are live and the MUFU stays fed.
 // Two CTAs (288 threads each) share an SM.
 #include "common.cuh"
 #include "launch.h"
@@ -36,14 +39,18 @@ struct Lat2Args {
   const float* lse_n;          // MODE 1: [B,H,N]
   float* out;                  // MODE 0: rec [S,B,H,M,D+2]; MODE 1: dz_part [S,B,H,M,D]
   int* status;
+  int c_bulk;                  // MODE 1: C_n rows may be fetched with 16-byte-aligned bulk copies
 };
+
+constexpr int kLat2Stages = 4;
 
 template <int D>
 struct Lat2Smem {
   static constexpr int ROWB = 2 * D;
   static constexpr int kQ = 128 * ROWB;
   static constexpr int kT = 128 * ROWB;            // one K or V tile
-  static constexpr int kBytes = kQ + 6 * kT + 3 * 128 * 4 /*C*/ + 2 * 128 * 4 /*max*/ + 128 * 4 /*l*/ + 64 /*kmax*/ + 1024 + 256;
+  static constexpr int kBytes = kQ + 2 * kLat2Stages * kT + kLat2Stages * 128 * 4 /*C*/ + 2 * 128 * 4 /*max*/ +
+                                128 * 4 /*l*/ + 64 /*kmax*/ + 1024 + 256;
 };
 
 __device__ __forceinline__ void mbar_arrive_l2(uint64_t* bar) {
@@ -52,8 +59,77 @@ __device__ __forceinline__ void mbar_arrive_l2(uint64_t* bar) {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// Untiled bulk copy global -> shared, completing on an mbarrier.  Both addresses 16-byte aligned,
+// size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
 
 constexpr int kLat2Softmax = 256;
+
+// One chunk of 16 score columns of one row: P = 2^(S sl - m) (MODE 0) or 2^(S sl - C log2e) (MODE 1),
+// packed to bf16 pairs; the two running sums take alternate columns.
+template <int MODE, bool MASKED>
+__device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_run, const float* c16, int col0,
+                                           int cnt, uint32_t* pk, float& s0, float& s1) {
+  float cv[16];
+  if (MODE == 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 c4 = *reinterpret_cast<const float4*>(c16 + 4 * j);
+      cv[4 * j] = c4.x; cv[4 * j + 1] = c4.y; cv[4 * j + 2] = c4.z; cv[4 * j + 3] = c4.w;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float x0, x1;
+    if (MODE == 0) {
+      x0 = fmaf(__uint_as_float(r[2 * j]), sl, -m_run);
+      x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -m_run);
+    } else {
+      x0 = fmaf(__uint_as_float(r[2 * j]), sl, -cv[2 * j] * kLog2e);
+      x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -cv[2 * j + 1] * kLog2e);
+    }
+    float e0 = ex2(x0), e1 = ex2(x1);
+    if (MASKED) {
+      if (col0 + 2 * j >= cnt) e0 = 0.f;
+      if (col0 + 2 * j + 1 >= cnt) e1 = 0.f;
+    }
+    s0 += e0; s1 += e1;
+    pk[j] = pack_bf16(e0, e1);
+  }
+}
+
+// The four chunks of this thread's 64 score columns, loads one chunk ahead of the arithmetic.
+// Even tiles walk the chunks upwards and odd tiles downwards, so that the packed P of a chunk
+// never lands on score columns that are still to be loaded (P sits in the lower half of the 64
+// columns on even tiles, in the upper half on odd ones).  Registers are indexed statically; only
+// addresses depend on the direction.
+template <int MODE, bool MASKED>
+__device__ __forceinline__ float lat2_row(uint32_t s_cols, uint32_t p_cols, int p, float sl, float m_run,
+                                          const float* c64, int col_half, int cnt) {
+  uint32_t ra[16], rb[16], pk[8];
+  float s0 = 0.f, s1 = 0.f;
+  const int c0 = p ? 3 : 0, dc = p ? -1 : 1;
+  tmem_ld16(s_cols + 16 * c0, ra);
+  tmem_wait_ld();
+  tmem_ld16(s_cols + 16 * (c0 + dc), rb);
+  lat2_chunk<MODE, MASKED>(ra, sl, m_run, c64 + 16 * c0, col_half + 16 * c0, cnt, pk, s0, s1);
+  tmem_st8(p_cols + 8 * c0, pk);
+  tmem_wait_ld();
+  tmem_ld16(s_cols + 16 * (c0 + 2 * dc), ra);
+  lat2_chunk<MODE, MASKED>(rb, sl, m_run, c64 + 16 * (c0 + dc), col_half + 16 * (c0 + dc), cnt, pk, s0, s1);
+  tmem_st8(p_cols + 8 * (c0 + dc), pk);
+  tmem_wait_ld();
+  tmem_ld16(s_cols + 16 * (c0 + 3 * dc), rb);
+  lat2_chunk<MODE, MASKED>(ra, sl, m_run, c64 + 16 * (c0 + 2 * dc), col_half + 16 * (c0 + 2 * dc), cnt, pk, s0, s1);
+  tmem_st8(p_cols + 8 * (c0 + 2 * dc), pk);
+  tmem_wait_ld();
+  lat2_chunk<MODE, MASKED>(rb, sl, m_run, c64 + 16 * (c0 + 3 * dc), col_half + 16 * (c0 + 3 * dc), cnt, pk, s0, s1);
+  tmem_st8(p_cols + 8 * (c0 + 3 * dc), pk);
+  return s0 + s1;
+}
 
 template <int D, int MODE>
 __global__ void __launch_bounds__(kLat2Softmax + 32, 2)
@@ -61,24 +137,26 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           const __grid_constant__ CUtensorMap tmV, Lat2Args a) {
   constexpr int ROWB = 2 * D;
   constexpr int CPR = ROWB / 16;
+  constexpr int NS = kLat2Stages;
   using L = Lat2Smem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + L::kQ;                        // [3]
-  uint8_t* sV = sK + 3 * L::kT;                    // [3]
-  float* sC2 = reinterpret_cast<float*>(sV + 3 * L::kT);   // [3][128]  C_n in log2 units (MODE 1)
-  float* sMax = sC2 + 3 * 128;                     // [2][128] half-row maxima (exact pass)
+  uint8_t* sK = sQ + L::kQ;                        // [NS]
+  uint8_t* sV = sK + NS * L::kT;                   // [NS]
+  float* sC = reinterpret_cast<float*>(sV + NS * L::kT);   // [NS][128]  C_n of the tile (MODE 1)
+  float* sMax = sC + NS * 128;                     // [2][128] half-row maxima (exact pass)
   float* sLsum = sMax + 2 * 128;                   // [128]
-  float* sKmax = sLsum + 128;                      // [8] per-warp max of |k_n|^2
+  float* sKmax = sLsum + 128;                      // [NS] max_n |k_n|^2 of the tile in each stage
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKmax + 16);
-  uint64_t* bar_full = bars;                       // [3]
-  uint64_t* bar_s = bars + 3;                      // [2] S(t) complete
-  uint64_t* bar_pv = bars + 5;                     // [2] P(t) V(t) complete
-  uint64_t* bar_sm = bars + 7;                     // [2] softmax(t) done (256 arrivals)
-  uint64_t* bar_q = bars + 9;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-  int* abort_flag = reinterpret_cast<int*>(bars + 11);
+  uint64_t* bar_full = bars;                       // [NS]
+  uint64_t* bar_s = bars + NS;                     // [2] S(t) complete
+  uint64_t* bar_pv = bar_s + 2;                    // [2] P(t) V(t) complete
+  uint64_t* bar_sm = bar_pv + 2;                   // [2] softmax(t) done (256 arrivals)
+  uint64_t* bar_k = bar_sm + 2;                    // [2] tile norm bound of tile t written (MODE 0)
+  uint64_t* bar_q = bar_k + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_q + 1);
+  int* abort_flag = reinterpret_cast<int*>(bar_q + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const bool is_issuer = warp == kLat2Softmax / 32;
@@ -104,8 +182,10 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   }
 
   if (tid == 0) {
-    for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(&bar_s[i], 1); mbar_init(&bar_pv[i], 1); mbar_init(&bar_sm[i], kLat2Softmax); }
+    for (int i = 0; i < NS; ++i) mbar_init(&bar_full[i], 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_s[i], 1); mbar_init(&bar_pv[i], 1); mbar_init(&bar_sm[i], kLat2Softmax); mbar_init(&bar_k[i], 1);
+    }
     mbar_init(bar_q, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -118,83 +198,115 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   const uint32_t tmem = *tmem_slot;
   const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t kAcc = 224;
-
-  auto load_tile = [&](int t) {
-    const int st = t % 3;
-    mbar_expect_tx(&bar_full[st], 2 * L::kT);
-    tma_load_4d(sK + st * L::kT, &tmK, &bar_full[st], 0, n0 + t * 128, h, b);
-    tma_load_4d(sV + st * L::kT, &tmV, &bar_full[st], 0, n0 + t * 128, h, b);
-  };
+  const float* cb = (MODE == 1) ? a.lse_n + ((long long)b * a.H + h) * a.N : nullptr;
+  const bool c_bulk = (MODE == 1) && a.c_bulk;
 
   if (is_issuer) {
     // ================================ issuer warp ================================
     // The whole warp runs this code; one elected lane executes each TMA / MMA / commit.
+    auto load_tile = [&](int t) {
+      const int st = t % NS;
+      const int tile0 = n0 + t * 128;
+      const uint32_t cbytes = c_bulk ? (uint32_t)min(128, n1 - tile0) * 4u : 0u;
+      mbar_expect_tx(&bar_full[st], 2 * L::kT + cbytes);
+      tma_load_4d(sK + st * L::kT, &tmK, &bar_full[st], 0, tile0, h, b);
+      tma_load_4d(sV + st * L::kT, &tmV, &bar_full[st], 0, tile0, h, b);
+      if (c_bulk) bulk_load(sC + st * 128, cb + tile0, cbytes, &bar_full[st]);
+    };
+    // max_n |k_n|^2 of a landed tile (rows past the end are zero-filled), published to the softmax
+    // threads through bar_k; lane l takes rows l, l+32, l+64, l+96
+    auto tile_kmax = [&](int t) {
+      const int st = t % NS;
+      float mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float s2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < CPR; ++c) {
+          const uint4 k4 = *reinterpret_cast<const uint4*>(sK + st * L::kT + swz_off<ROWB>(lane + 32 * i, c));
+          const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&k4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(kp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
+        }
+        mx = fmaxf(mx, s2);
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) { sKmax[st] = mx; mbar_arrive_l2(&bar_k[t & 1]); }
+      __syncwarp();
+    };
+
+    const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
+    const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
+    const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
+    if (elect_one()) {
+      mbar_expect_tx(bar_q, L::kQ);
+      tma_load_4d(sQ, &tmQ, bar_q, 0, mblk * 128, h, a.q_batched ? b : 0);
+      for (int t = 0; t < NS - 1 && t < T; ++t) load_tile(t);
+    }
+    __syncwarp();
+    mbar_wait(bar_q, 0, a.status, abort_flag);
+    mbar_wait(&bar_full[0], 0, a.status, abort_flag);
+    tc_fence_after();
     {
-      const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
-      const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
-      const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
+      const uint64_t dk = smem_desc<ROWB>(smem_u32(sK));
       if (elect_one()) {
-        mbar_expect_tx(bar_q, L::kQ);
-        tma_load_4d(sQ, &tmQ, bar_q, 0, mblk * 128, h, a.q_batched ? b : 0);
-        load_tile(0);
-        if (T > 1) load_tile(1);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+        mma_commit(&bar_s[0]);
       }
       __syncwarp();
-      mbar_wait(bar_q, 0, a.status, abort_flag);
-      mbar_wait(&bar_full[0], 0, a.status, abort_flag);
+    }
+    if (MODE == 0) {
+      tile_kmax(0);
+      if (T > 1) { mbar_wait(&bar_full[1], 0, a.status, abort_flag); tile_kmax(1); }
+    }
+    for (int t = 0; t < T; ++t) {
+      const int p = t & 1;
+      mbar_wait_hot(&bar_sm[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);     // P(t) written, S(t) consumed
+      if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      if (t >= 1) {
+        // P(t-1) V(t-1) complete: its packed P columns may be overwritten by S(t+1), and the
+        // stage of tile t-1 may take tile t+3
+        mbar_wait_hot(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
+      }
+      if (t + NS - 1 < T && elect_one()) load_tile(t + NS - 1);
+      __syncwarp();
       tc_fence_after();
-      {
-        const uint64_t dk = smem_desc<ROWB>(smem_u32(sK));
+      if (t + 1 < T) {
+        mbar_wait_hot(&bar_full[(t + 1) % NS], (uint32_t)((t + 1) / NS) & 1, a.status, abort_flag);
+        const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + ((t + 1) % NS) * L::kT));
+        const uint32_t sb = tmem + (p ? 0 : 96);                                    // region of tile t+1
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-          mma_commit(&bar_s[0]);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
+          mma_commit(&bar_s[p ^ 1]);
         }
         __syncwarp();
       }
-      for (int t = 0; t < T; ++t) {
-        const int p = t & 1;
-        mbar_wait(&bar_sm[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);       // P(t) written, S(t) consumed
-        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
-        if (t >= 1) {
-          // P(t-1) V(t-1) complete: its packed P columns may be overwritten by S(t+1), and the
-          // stage of tile t-1 may take tile t+2
-          mbar_wait(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
+      {
+        const uint64_t dv = smem_desc<ROWB>(smem_u32(sV + (t % NS) * L::kT));
+        const uint32_t p0 = tmem + (p ? 128 : 0), p1 = tmem + (p ? 192 : 64);       // packed P of the two halves
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem + kAcc, (kk < 4 ? p0 + 8 * kk : p1 + 8 * (kk - 4)), dv + (uint64_t)((kk * 16 * ROWB) >> 4),
+                   idesc_pv, (t > 0) || (kk > 0));
+          mma_commit(&bar_pv[p]);
         }
-        if (t + 2 < T && elect_one()) load_tile(t + 2);
         __syncwarp();
-        tc_fence_after();
-        if (t + 1 < T) {
-          mbar_wait(&bar_full[(t + 1) % 3], (uint32_t)((t + 1) / 3) & 1, a.status, abort_flag);
-          const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + ((t + 1) % 3) * L::kT));
-          const uint32_t sb = tmem + (p ? 0 : 96);                                  // region of tile t+1
-          if (elect_one()) {
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-            mma_commit(&bar_s[p ^ 1]);
-          }
-          __syncwarp();
-        }
-        {
-          const uint64_t dv = smem_desc<ROWB>(smem_u32(sV + (t % 3) * L::kT));
-          const uint32_t p0 = tmem + (p ? 128 : 0), p1 = tmem + (p ? 192 : 64);     // packed P of the two halves
-          if (elect_one()) {
-#pragma unroll
-            for (int kk = 0; kk < 8; ++kk)
-              mma_ts(tmem + kAcc, (kk < 4 ? p0 + 8 * kk : p1 + 8 * (kk - 4)), dv + (uint64_t)((kk * 16 * ROWB) >> 4),
-                     idesc_pv, (t > 0) || (kk > 0));
-            mma_commit(&bar_pv[p]);
-          }
-          __syncwarp();
-        }
+      }
+      if (MODE == 0 && t + 2 < T) {
+        // the bound of tile t+2, while the softmax threads work on tile t+1
+        mbar_wait(&bar_full[(t + 2) % NS], (uint32_t)((t + 2) / NS) & 1, a.status, abort_flag);
+        tile_kmax(t + 2);
       }
     }
     __syncwarp();
   } else {
     // ================================ softmax threads ================================
     const float sl = a.scale_log2;
-    const float* cb = (MODE == 1) ? a.lse_n + ((long long)b * a.H + h) * a.N : nullptr;
-    float m_run = -INFINITY, l_run = 0.f, qn = 0.f;
+    float m_run = (MODE == 0) ? -INFINITY : 0.f, l_run = 0.f, qn = 0.f;
     if (MODE == 0) {
       // |q_m| of this thread's latent row (both halves compute the same value)
       mbar_wait(bar_q, 0, a.status, abort_flag);
@@ -210,62 +322,38 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     }
 
     for (int t = 0; t < T; ++t) {
-      const int p = t & 1, st = t % 3;
+      const int p = t & 1, st = t % NS;
       const int tile0 = n0 + t * 128;
       const int cnt = min(128, n1 - tile0);
-      // ---- per-tile scalars, computed while the S product runs -------------------------------
-      mbar_wait(&bar_full[st], (uint32_t)(t / 3) & 1, a.status, abort_flag);
-      if (MODE == 1) {
-        if (tid < 128) sC2[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] * kLog2e : INFINITY;
-      } else {
-        // max_n |k_n|^2 of the tile: thread (n, part) reads half a row
-        const int n = tid >> 1, part = tid & 1;
-        float s2 = 0.f;
-#pragma unroll
-        for (int c = 0; c < CPR / 2; ++c) {
-          const uint4 k4 = *reinterpret_cast<const uint4*>(sK + st * L::kT + swz_off<ROWB>(n, part * (CPR / 2) + c));
-          const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&k4);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(kp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
-        }
-        s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-#pragma unroll
-        for (int o = 2; o < 32; o <<= 1) s2 = fmaxf(s2, __shfl_xor_sync(0xffffffffu, s2, o));
-        if (lane == 0) sKmax[(p << 3) + warp] = s2;
-      }
-      named_bar_sync(2, kLat2Softmax);
       float bound = 0.f;
-      if (MODE == 0) {
-        float k2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) k2 = fmaxf(k2, sKmax[(p << 3) + i]);
-        bound = qn * sqrtf(k2);                    // >= every score of this row in the tile, log2 units
+      if (MODE == 1) {
+        // C_n of the tile: landed with K and dY, or (unaligned rows) fetched by the first 128 threads
+        mbar_wait(&bar_full[st], (uint32_t)(t / NS) & 1, a.status, abort_flag);
+        if (!c_bulk) {
+          if (tid < 128) sC[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] : 0.f;
+          named_bar_sync(2, kLat2Softmax);
+        }
+      } else {
+        mbar_wait(&bar_k[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
+        bound = qn * sqrtf(sKmax[st]);             // >= every score of this row in the tile, log2 units
       }
 
-      mbar_wait(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
+      mbar_wait_hot(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
-
-      // this thread's 64 score columns: two chunks of 32, the one that hosts P second-to-last
-      const uint32_t s_cols = lane_base + (p ? 96 : 0) + 64 * half;
-      uint32_t r0[32], r1[32];                     // r0 = columns [0,32) of the half, r1 = [32,64)
-      tmem_ld32(s_cols, r0);
-      tmem_ld32(s_cols + 32, r1);
-      tmem_wait_ld();
+      const uint32_t s_cols = lane_base + (p ? 96 : 0) + 64 * half;   // this thread's 64 score columns
+      const uint32_t p_cols = s_cols + (p ? 32 : 0);                  // where their packed P goes
 
       if (MODE == 0) {
         const bool need = (t == 0) || (bound > m_run + 60.f);
         if (__any_sync(0xffffffffu, need)) {       // the partner warp holds the same rows: same vote
           float mx = -INFINITY;
-          const int c0 = 64 * half;
-          if (cnt == 128) {
+          for (int i = 0; i < 4; ++i) {
+            uint32_t r[16];
+            tmem_ld16(s_cols + 16 * i, r);
+            tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, fmaxf(__uint_as_float(r0[j]), __uint_as_float(r1[j])));
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              mx = fmaxf(mx, (c0 + j < cnt) ? __uint_as_float(r0[j]) : -INFINITY);
-              mx = fmaxf(mx, (c0 + 32 + j < cnt) ? __uint_as_float(r1[j]) : -INFINITY);
-            }
+            for (int j = 0; j < 16; ++j)
+              mx = fmaxf(mx, (64 * half + 16 * i + j < cnt) ? __uint_as_float(r[j]) : -INFINITY);
           }
           sMax[half * 128 + row] = mx;
           named_bar_sync(3 + (warp & 3), 64);      // the two warps of this lane quarter
@@ -291,36 +379,9 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       }
 
       // ---- one exponential per score; P packed inside this thread's own columns ----------------
-      float lsum = 0.f;
-      const float* c2p = (MODE == 1) ? sC2 + st * 128 + 64 * half : nullptr;
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = p ? 1 - cc : cc;             // odd tiles: upper chunk first (P lives in the upper chunk)
-        const uint32_t* r = c ? r1 : r0;
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          float x0, x1;
-          if (MODE == 0) {
-            x0 = fmaf(__uint_as_float(r[2 * j]), sl, -m_run);
-            x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -m_run);
-          } else {
-            const float2 cc2 = *reinterpret_cast<const float2*>(c2p + 32 * c + 2 * j);
-            x0 = fmaf(__uint_as_float(r[2 * j]), sl, -cc2.x);
-            x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -cc2.y);
-          }
-          float e0 = ex2(x0), e1 = ex2(x1);
-          if (MODE == 0 && cnt < 128) {
-            if (64 * half + 32 * c + 2 * j >= cnt) e0 = 0.f;
-            if (64 * half + 32 * c + 2 * j + 1 >= cnt) e1 = 0.f;
-          }
-          lsum += e0 + e1;
-          pk[j] = pack_bf16(e0, e1);
-        }
-        // even tiles: P at [0,32) of the half's 64 columns; odd tiles: at [32,64)
-        tmem_st16(s_cols + (p ? 32 : 0) + 16 * c, pk);
-      }
-      l_run += lsum;
+      const float* c64 = sC + st * 128 + 64 * half;
+      if (cnt == 128) l_run += lat2_row<MODE, false>(s_cols, p_cols, p, sl, m_run, c64, 64 * half, cnt);
+      else            l_run += lat2_row<MODE, true>(s_cols, p_cols, p, sl, m_run, c64, 64 * half, cnt);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_l2(&bar_sm[p]);
@@ -387,6 +448,7 @@ static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v
   a.n_splits = c.n_splits; a.chunk = c.chunk; a.n_mblk = (c.M + 127) / 128;
   a.lse_n = lse_n; a.out = out;
   a.status = tc_status_ptr();
+  a.c_bulk = (MODE == 1 && lse_n && (reinterpret_cast<uintptr_t>(lse_n) & 15) == 0 && (c.N & 3) == 0) ? 1 : 0;
   static bool attr_done = false;
   constexpr int smem = Lat2Smem<D>::kBytes;
   if (!attr_done) {

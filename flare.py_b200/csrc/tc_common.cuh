@@ -68,6 +68,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
   return true;
 }
+// The same bounded wait without the sleep, for the waits that sit on a kernel's critical chain
+// (a hand-off seen 64 ns late is a stall of every unit behind it).  try_wait itself suspends the
+// warp for a hardware-defined time, so the spin stays cheap.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, int* status, int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > (1LL << 31)) {
+      if (status) atomicOr(status, kErrWaitTimeout);
+      *reinterpret_cast<volatile int*>(abort_flag) = 1;
+      return false;
+    }
+  }
+  return true;
+}
 
 // ---------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar,
