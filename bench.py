@@ -373,7 +373,10 @@ def run_ours(args):
                           f"1 warm-up + 3 runs, mean")
 
     if rank == 0:
-        launches_per_step = 7 + (1 if world > 1 else 0)
+        # forward: gather, combine, scatter; backward: dZ partial, reduce, range check (2 kernels),
+        # one-exponential main kernel, flag-gated exact kernel, dQ reduce; the context-parallel
+        # forward has a second combine over the ranks' records
+        launches_per_step = 10 + (1 if world > 1 else 0)
         line = dict(
             metric=METRIC, value=value, unit="Mtokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
             ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
@@ -381,7 +384,7 @@ def run_ours(args):
             config=dict(workload=f"mixer_1M: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd",
                         parallelism=("single GPU" if world == 1 else f"context parallel, N sharded over {world} ranks"),
                         tokens_per_rank=Nl, l2="inputs larger than L2 (K,V,dY,Y,dK,dV 64 B x tokens x heads each); no flush",
-                        kernel_path="simt+tcgen05 (auto)"),
+                        kernel_path="tcgen05 (decoupled gather/scatter/dZ, pipelined one-exponential backward behind an on-device range check); fp32 SIMT reductions"),
             clocks=clocks,
             e2e=dict(value=B * N / (e2e_ms * 1e-3) / 1e6, unit="Mtokens/s", h2d_bytes_per_step=h2d * world,
                      d2h_bytes_per_step=d2h * world, ms_per_step=e2e_ms),
