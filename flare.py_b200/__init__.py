@@ -4,11 +4,12 @@ The directory is named after the project it accelerates (``flare.py_b200``); the
 importable name is ``flare_b200`` (see ``flare_b200.py`` at the repository root,
 which registers this directory under that name).
 """
+from .causal import causal_state_init, flare_causal_decode, flare_causal_prefill
 from .mixer import (flare_gather, flare_multihead_mixer, flare_scatter, mixer_backward, mixer_forward,
                     set_kernel_path)
 from .modules import FLARE, FLAREBlock, FLAREModel, ResidualMLP
 
 __all__ = [
     "flare_multihead_mixer", "flare_gather", "flare_scatter", "mixer_forward", "mixer_backward",
-    "set_kernel_path", "FLARE", "FLAREBlock", "FLAREModel", "ResidualMLP",
+    "set_kernel_path", "flare_causal_prefill", "flare_causal_decode", "causal_state_init", "FLARE", "FLAREBlock", "FLAREModel", "ResidualMLP",
 ]

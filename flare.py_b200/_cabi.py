@@ -51,6 +51,9 @@ SIGNATURES = {
     "flare_bwd_tokens": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_bwd_main": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_gather_noalloc": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_causal_workspace_bytes": (_sz, [_P]),
+    "flare_causal_prefill": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_causal_decode": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_device_status": (_i, [C.POINTER(C.c_int), _i]),
     "flare_debug_phase_counters": (_i, [_vp]),
     "flare_probe_ex2": (_i, [_i, _i, _vp, _vp]),

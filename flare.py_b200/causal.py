@@ -1,0 +1,63 @@
+"""Causal FLARE: prefill over a whole sequence and recurrent decode on a per-(b, h) state.
+
+The reference links this path (README.md:60) without shipping code; the semantics are those of
+figs/flare_decoder.py:211-250.  ``y_t = softmax_M(S[:, t]) . z_t`` with
+``z_t = softmax_{n <= t}(S) v`` and ``S = scale * q k^T``.  The state is one record per latent,
+``[B, H, M, D + 2] = (acc[D], m, l)`` in fp32, the same record the non-causal gather writes per token
+range; ``causal_state_init`` gives the empty one.  Forward only (serving path).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._cabi import check, lib, ptr, stream_of
+from .mixer import _need_cuda, _q3, _tok, make_problem
+
+__all__ = ["causal_state_init", "flare_causal_prefill", "flare_causal_decode"]
+
+
+def causal_state_init(B: int, H: int, M: int, D: int, device) -> torch.Tensor:
+    """The record of an empty prefix: acc = 0, m = -inf, l = 0."""
+    st = torch.zeros(B, H, M, D + 2, dtype=torch.float32, device=device)
+    st[..., D] = float("-inf")
+    return st
+
+
+def flare_causal_prefill(q, k, v, scale: float = 1.0, state=None):
+    """All tokens of k, v [B,H,N,D] at once.  Returns (y [B,H,N,D], state after the last token)."""
+    _need_cuda(q, k, v)
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError("q, k, v must share a dtype")
+    q, _ = _q3(q)
+    k, v = _tok(k), _tok(v)
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    with torch.cuda.device(k.device):
+        y = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        out = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=k.device)
+        p = make_problem(q, k, scale, v=v, y=y)
+        ws = torch.empty(lib.flare_causal_workspace_bytes(C.byref(p)), dtype=torch.uint8, device=k.device)
+        if state is not None:
+            state = state.contiguous()
+        check(lib.flare_causal_prefill(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(y), ptr(state), ptr(out), ptr(ws),
+                                       stream_of(k)), "flare_causal_prefill")
+    return y, out
+
+
+def flare_causal_decode(q, k, v, state, scale: float = 1.0):
+    """The tokens of k, v [B,H,T,D] (T is usually 1) one after the other; `state` is updated in place."""
+    _need_cuda(q, k, v, state)
+    q, _ = _q3(q)
+    k, v = _tok(k), _tok(v)
+    B, H, T, D = k.shape
+    M = q.shape[-2]
+    if tuple(state.shape) != (B, H, M, D + 2) or state.dtype != torch.float32 or not state.is_contiguous():
+        raise ValueError(f"state must be a contiguous fp32 [B,H,M,D+2] = {(B, H, M, D + 2)} tensor")
+    with torch.cuda.device(k.device):
+        y = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        p = make_problem(q, k, scale, v=v, y=y)
+        check(lib.flare_causal_decode(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(y), ptr(state), stream_of(k)),
+              "flare_causal_decode")
+    return y

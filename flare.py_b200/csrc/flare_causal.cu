@@ -1,0 +1,319 @@
+// Causal FLARE: y_t = softmax_M(S[:, t]) . z_t with z_t = softmax_{n <= t}(S) v   (S = scale q k^T).
+//
+// The reference ships no code for this path, only its semantics (figs/flare_decoder.py:211-250: a
+// per-(b, h) state (m[M], l[M], acc[M, D]) updated with each (k_t, v_t)).  Here the state is the same
+// split-N record the non-causal gather produces, so prefill is three passes:
+//
+//   1. flare_gather_partial with 128-token ranges: one record per chunk           (existing kernels)
+//   2. k_causal_scan: exclusive log-sum-exp prefix of the records along the chunk axis, in place;
+//      the inclusive total is the state after the last token
+//   3. k_causal_walk: per (b, h, chunk), start from the chunk's prefix record and walk its tokens:
+//      acc_m += e^{s_mt - mu_m} v_t,  y_t = sum_m softmax_M(s_:t)_m / l_mt * acc_m
+//
+// and decode is one launch of the same kernel per token on the caller's record.  Pass 3 and decode are fp32
+// SIMT kernels: thread (d, g) keeps acc[m][d] of its latents m = g, g + G, ... in registers, scores and
+// weights of a 64-token sub-chunk sit in shared memory.  Scores are computed once per token; the
+// sequential part is O(T M D) fused multiply-adds per chunk, the minimum for this recurrence.
+#include <cstdarg>
+#include <cstdio>
+#include <cuda_runtime.h>
+#include "common.cuh"
+
+namespace flare { void set_last_error(const char* msg); }
+
+namespace {
+
+using namespace flare;
+
+constexpr int kThreads = 256;
+constexpr int kSub = 64;          // tokens per sub-chunk
+constexpr int kChunk = 128;       // tokens per record (pass 1 range length)
+constexpr int kMaxLat = 32;       // latents per thread
+
+int refuse(int code, const char* fmt, ...) {
+  char msg[400];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(msg, sizeof(msg), fmt, ap);
+  va_end(ap);
+  flare::set_last_error(msg);
+  return code;
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 2: exclusive prefix of records along the chunk axis.  rec[c][row][D+2]; one warp per row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, const float* __restrict__ state_in,
+              float* __restrict__ state_out) {
+  const long long row = (long long)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  if (row >= rows) return;
+  const int W = D + 2;
+  const long long cs = rows * W;
+  float m = -INFINITY, l = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};             // D <= 128: four columns per lane
+  if (state_in) {
+    m = state_in[row * W + D]; l = state_in[row * W + D + 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) acc[i] = state_in[row * W + lane + 32 * i];
+  }
+  for (int c = 0; c < n_chunks; ++c) {
+    float* r = rec + c * cs + row * W;
+    const float mc = r[D], lc = r[D + 1];
+    float ac[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ac[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+    __syncwarp();
+    // the record of everything before chunk c
+#pragma unroll
+    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[i];
+    if (lane == 0) { r[D] = m; r[D + 1] = l; }
+    const float mn = fmaxf(m, mc);
+    const float wa = (m == -INFINITY) ? 0.f : __expf(m - mn);
+    const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
+    l = wa * l + wc * lc;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = wa * acc[i] + wc * ac[i];
+    m = mn;
+  }
+  if (state_out) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) state_out[row * W + lane + 32 * i] = acc[i];
+    if (lane == 0) { state_out[row * W + D] = m; state_out[row * W + D + 1] = l; }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// pass 3 / decode: walk `cnt` tokens starting from a record.
+// Shared memory: q [M][D] fp32, k/v sub-chunk [kSub][D] fp32, S->G [kSub][M], E [kSub][M],
+// mu/l/a [M], cmax/csum [kSub], ypart [2][G][D] (rows padded by one float).
+// ---------------------------------------------------------------------------------------------
+struct CausalArgs {
+  int B, H, N, M, D;
+  float scale;
+  long long qs[3], ks[3], vs[3], ys[3];
+  const void* q; const void* k; const void* v; void* y;
+  const float* prefix;         // [n_chunks][B][H][M][D+2]: the record before each chunk
+  float* state;                // decode: [B][H][M][D+2], updated in place (prefix == nullptr)
+  int tokens_per_cta;          // kChunk in prefill, N (usually 1) in decode
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads)
+k_causal_walk(CausalArgs a) {
+  constexpr int G = kThreads / D;                  // latent groups
+  extern __shared__ float sm[];
+  const int M = a.M;
+  constexpr int DP = D + 1;                        // padded rows: no bank conflicts when a warp walks rows
+  const int MP = M + 1;
+  float* sQ = sm;                                  // [M][DP]
+  float* sK = sQ + M * DP;                         // [kSub][D]
+  float* sV = sK + kSub * D;                       // [kSub][D]
+  float* sS = sV + kSub * D;                       // [kSub][MP]  scores, then weights
+  float* sE = sS + kSub * MP;                      // [kSub][MP]
+  float* sMu = sE + kSub * MP;                     // [M]
+  float* sL = sMu + M;                             // [M]
+  float* sA = sL + M;                              // [M]
+  float* sCm = sA + M;                             // [kSub]
+  float* sCs = sCm + kSub;                         // [kSub]
+  float* sY = sCs + kSub;                          // [2][G][D]
+
+  const int tid = threadIdx.x;
+  const int d = tid % D, g = tid / D;
+  const int nlat = M / G;                          // latents of this thread: g, g + G, ...
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int n0 = chunk * a.tokens_per_cta, n1 = min(a.N, n0 + a.tokens_per_cta);
+  const int W = D + 2;
+
+  const T* qp = reinterpret_cast<const T*>(a.q) + b * a.qs[0] + h * a.qs[1];
+  const T* kp = reinterpret_cast<const T*>(a.k) + b * a.ks[0] + h * a.ks[1];
+  const T* vp = reinterpret_cast<const T*>(a.v) + b * a.vs[0] + h * a.vs[1];
+  T* yp = reinterpret_cast<T*>(a.y) + b * a.ys[0] + h * a.ys[1];
+  const float* rec = a.prefix ? a.prefix + (((long long)chunk * a.B + b) * a.H + h) * M * W
+                              : a.state + ((long long)b * a.H + h) * M * W;
+
+  for (int i = tid; i < M * D; i += kThreads) sQ[(i / D) * DP + i % D] = to_f32(qp[(i / D) * a.qs[2] + i % D]);
+  for (int m = tid; m < M; m += kThreads) { sMu[m] = rec[m * W + D]; sL[m] = rec[m * W + D + 1]; }
+  float acc[kMaxLat];
+#pragma unroll
+  for (int j = 0; j < kMaxLat; ++j) acc[j] = (j < nlat) ? rec[(g + j * G) * W + d] : 0.f;
+  __syncthreads();
+
+  for (int s0 = n0; s0 < n1; s0 += kSub) {
+    const int cnt = min(kSub, n1 - s0);
+    for (int i = tid; i < cnt * D; i += kThreads) {
+      const int t = i / D, dd = i % D;
+      sK[i] = to_f32(kp[(long long)(s0 + t) * a.ks[2] + dd]);
+      sV[i] = to_f32(vp[(long long)(s0 + t) * a.vs[2] + dd]);
+    }
+    __syncthreads();
+    // scores S[t][m] = scale q_m . k_t
+    for (int i = tid; i < cnt * M; i += kThreads) {
+      const int t = i / M, m = i % M;
+      const float* qr = sQ + m * DP;
+      const float* kr = sK + t * D;
+      float s = 0.f;
+#pragma unroll 8
+      for (int dd = 0; dd < D; ++dd) s = fmaf(qr[dd], kr[dd], s);
+      sS[t * MP + m] = s * a.scale;
+    }
+    __syncthreads();
+    // per token: max and sum over the latents (the scatter softmax)
+    for (int t = tid; t < cnt; t += kThreads) {
+      float mx = -INFINITY;
+      for (int m = 0; m < M; ++m) mx = fmaxf(mx, sS[t * MP + m]);
+      float su = 0.f;
+      for (int m = 0; m < M; ++m) su += __expf(sS[t * MP + m] - mx);
+      sCm[t] = mx; sCs[t] = su;
+    }
+    __syncthreads();
+    // per latent: new running max over the sub-chunk, E = e^{S - mu}, running l, weights
+    for (int m = tid; m < M; m += kThreads) {
+      const float mu0 = sMu[m];
+      float mu = mu0;
+      for (int t = 0; t < cnt; ++t) mu = fmaxf(mu, sS[t * MP + m]);
+      const float al = (mu0 == -INFINITY) ? 0.f : __expf(mu0 - mu);
+      float l = al * sL[m];
+      for (int t = 0; t < cnt; ++t) {
+        const float s = sS[t * MP + m];
+        const float e = __expf(s - mu);
+        l += e;
+        sE[t * MP + m] = e;
+        sS[t * MP + m] = __expf(s - sCm[t]) / (sCs[t] * l);     // softmax_M(s_:t)_m / l_mt
+      }
+      sMu[m] = mu; sL[m] = l; sA[m] = al;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) acc[j] *= sA[g + j * G];
+    // the recurrence over the sub-chunk's tokens
+    for (int t = 0; t < cnt; ++t) {
+      const float vd = sV[t * D + d];
+      const float* er = sE + t * MP + g;
+      const float* gr = sS + t * MP + g;
+      float y = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxLat; ++j) {
+        if (j < nlat) {
+          acc[j] = fmaf(er[j * G], vd, acc[j]);
+          y = fmaf(gr[j * G], acc[j], y);
+        }
+      }
+      float* yb = sY + (t & 1) * kThreads;         // two buffers: one barrier per token
+      yb[g * D + d] = y;
+      __syncthreads();
+      if (g == 0) {
+        float ys = 0.f;
+#pragma unroll
+        for (int gg = 0; gg < G; ++gg) ys += yb[gg * D + d];
+        yp[(long long)(s0 + t) * a.ys[2] + d] = from_f32<T>(ys);
+      }
+    }
+    __syncthreads();
+  }
+  if (!a.prefix) {                                 // decode: the record moves on
+    float* st = a.state + ((long long)b * a.H + h) * M * W;
+#pragma unroll
+    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) st[(g + j * G) * W + d] = acc[j];
+    for (int m = tid; m < M; m += kThreads) { st[m * W + D] = sMu[m]; st[m * W + D + 1] = sL[m]; }
+  }
+}
+
+size_t walk_smem(int M, int D) {
+  return sizeof(float) * ((size_t)M * (D + 1) + 2 * kSub * D + 2 * (size_t)kSub * (M + 1) + 3 * M + 2 * kSub + 2 * kThreads);
+}
+
+template <typename T, int D>
+int launch_walk(const CausalArgs& a, int n_cta_x, cudaStream_t st) {
+  const size_t smem = walk_smem(a.M, D);
+  if (smem > 227 * 1024) return refuse(FLARE_EUNSUPPORTED, "causal: M=%d D=%d needs %zu bytes of shared memory", a.M, D, smem);
+  cudaError_t e = cudaFuncSetAttribute(k_causal_walk<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
+  k_causal_walk<T, D><<<dim3((unsigned)n_cta_x, (unsigned)(a.B * a.H)), kThreads, smem, st>>>(a);
+  e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
+  return FLARE_OK;
+}
+
+template <typename T>
+int dispatch_walk(const CausalArgs& a, int n_cta_x, cudaStream_t st) {
+  switch (a.D) {
+    case 16: return launch_walk<T, 16>(a, n_cta_x, st);
+    case 32: return launch_walk<T, 32>(a, n_cta_x, st);
+    case 64: return launch_walk<T, 64>(a, n_cta_x, st);
+    case 128: return launch_walk<T, 128>(a, n_cta_x, st);
+  }
+  return refuse(FLARE_EUNSUPPORTED, "causal: head dim %d not in {16,32,64,128}", a.D);
+}
+
+int fill_args(const FlareProblem* p, CausalArgs* a) {
+  if (!p) return refuse(FLARE_EINVAL, "causal: null problem");
+  if (p->B < 1 || p->H < 1 || p->M < 1 || p->N < 1) return refuse(FLARE_EINVAL, "causal: bad sizes");
+  if ((long long)p->B * p->H > 65535) return refuse(FLARE_EUNSUPPORTED, "causal: B*H > 65535");
+  if (!(p->scale > 0.f)) return refuse(FLARE_EINVAL, "causal: scale must be > 0");
+  const int D = p->D;
+  if (D != 16 && D != 32 && D != 64 && D != 128) return refuse(FLARE_EUNSUPPORTED, "causal: head dim %d not in {16,32,64,128}", D);
+  const int G = kThreads / D;
+  if (p->M % G != 0 || p->M / G > kMaxLat)
+    return refuse(FLARE_EUNSUPPORTED, "causal: M=%d must be a multiple of %d and at most %d for D=%d", p->M, G, G * kMaxLat, D);
+  a->B = p->B; a->H = p->H; a->N = p->N; a->M = p->M; a->D = D; a->scale = p->scale;
+  for (int i = 0; i < 3; ++i) { a->qs[i] = p->q_stride[i]; a->ks[i] = p->k_stride[i]; a->vs[i] = p->v_stride[i]; a->ys[i] = p->y_stride[i]; }
+  return FLARE_OK;
+}
+
+int run_walk(const FlareProblem* p, const CausalArgs& a, int n_cta_x, cudaStream_t st) {
+  switch (p->dtype) {
+    case FLARE_F32: return dispatch_walk<float>(a, n_cta_x, st);
+    case FLARE_F16: return dispatch_walk<__half>(a, n_cta_x, st);
+    case FLARE_BF16: return dispatch_walk<__nv_bfloat16>(a, n_cta_x, st);
+  }
+  return refuse(FLARE_EINVAL, "causal: bad dtype %d", p->dtype);
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t flare_causal_workspace_bytes(const FlareProblem* p) {
+  if (!p || p->N < 1) return 0;
+  const size_t chunks = ((size_t)p->N + kChunk - 1) / kChunk;
+  return chunks * p->B * p->H * p->M * (p->D + 2) * sizeof(float) + 256;
+}
+
+int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
+                         const float* state_in, float* state_out, float* workspace, flare_stream_t stream) {
+  CausalArgs a;
+  int rc = fill_args(p, &a);
+  if (rc != FLARE_OK) return rc;
+  if (!q || !k || !v || !y || !workspace) return refuse(FLARE_EINVAL, "causal_prefill: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int chunks = (p->N + kChunk - 1) / kChunk;
+  // pass 1: one record per 128-token chunk
+  FlareProblem pp = *p;
+  pp.n_splits = chunks;
+  rc = flare_gather_partial(&pp, q, k, v, nullptr, workspace, st);
+  if (rc != FLARE_OK) return rc;
+  // pass 2: exclusive prefix along the chunk axis
+  const long long rows = (long long)p->B * p->H * p->M;
+  const int rpb = kThreads / 32;
+  k_causal_scan<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(workspace, chunks, rows, p->D, state_in, state_out);
+  // pass 3: the tokens of every chunk
+  a.q = q; a.k = k; a.v = v; a.y = y;
+  a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;
+  return run_walk(p, a, chunks, st);
+}
+
+int flare_causal_decode(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
+                        float* state, flare_stream_t stream) {
+  CausalArgs a;
+  int rc = fill_args(p, &a);
+  if (rc != FLARE_OK) return rc;
+  if (!q || !k || !v || !y || !state) return refuse(FLARE_EINVAL, "causal_decode: null pointer");
+  a.q = q; a.k = k; a.v = v; a.y = y;
+  a.prefix = nullptr; a.state = state; a.tokens_per_cta = p->N;
+  return run_walk(p, a, 1, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

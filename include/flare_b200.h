@@ -172,6 +172,23 @@ int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, co
                          const uint8_t* key_mask, float* z32, void* z_out, float* lse_m,
                          flare_stream_t stream);
 
+/* Causal FLARE: y_t = softmax_M(S[:,t]) . z_t with z_t = softmax_{n<=t}(S) v.  The reference links
+ * this path (README.md:60) but ships no code for it; the semantics follow figs/flare_decoder.py:211-250.
+ * The state is one gather record per (b, h): float [B,H,M,D+2] = (acc[D], m, l) per latent, the same
+ * record flare_gather_partial writes; start from acc = 0, m = -inf, l = 0.
+ *   flare_causal_prefill: all N tokens at once.  workspace: flare_causal_workspace_bytes(p) bytes.
+ *     state_in (may be NULL: empty prefix) is the record before token 0, state_out (may be NULL)
+ *     receives the record after token N-1.
+ *   flare_causal_decode: the N tokens of k, v (usually N = 1) one after the other on `state`,
+ *     updated in place.
+ * Requires D in {16,32,64,128}, M a multiple of 256/D and at most 32*256/D; dtype as p->dtype. */
+size_t flare_causal_workspace_bytes(const FlareProblem* p);
+int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
+                         const float* state_in, float* state_out, float* workspace,
+                         flare_stream_t stream);
+int flare_causal_decode(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
+                        float* state, flare_stream_t stream);
+
 /* Reads (and optionally clears) the device status word of the current device; synchronises.
  * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */

@@ -1,0 +1,96 @@
+"""Causal FLARE on the GPU against the CPU oracle (dense and recurrent forms).
+
+The reference has no code for this path, so the oracle itself is checked for self-consistency
+(tests/test_oracle.py); here the CUDA prefill and decode are compared with it.
+"""
+import pytest
+import torch
+
+from oracle import flare_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2, torch.float16: 5e-3}
+
+
+def _inputs(B, H, N, M, D, dtype, seed=0):
+    q, k, v, _ = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=seed)
+    return q, k, v
+
+
+@pytest.mark.parametrize("B,H,N,M,D,dtype", [
+    (1, 2, 64, 32, 32, torch.float32),
+    (2, 2, 200, 64, 32, torch.float32),       # ragged: 1.56 chunks, partial sub-chunk
+    (1, 2, 384, 128, 64, torch.float32),      # the serving shape's M and D
+    (1, 2, 300, 256, 32, torch.bfloat16),
+    (2, 3, 257, 128, 64, torch.bfloat16),
+    (1, 1, 130, 64, 16, torch.float16),
+])
+def test_prefill_matches_oracle(cuda_dev, B, H, N, M, D, dtype):
+    import flare_b200 as fb
+    q, k, v = _inputs(B, H, N, M, D, dtype)
+    y_ref, (m_ref, l_ref, a_ref) = O.causal_recurrent(q.double(), k.double(), v.double(), 1.0)
+    y, st = fb.flare_causal_prefill(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), 1.0)
+    assert O.rel_l2(y.double().cpu(), y_ref) <= TOL[dtype]
+    # the final record, compared through what it represents: z = acc / l and lse = m + log l
+    st = st.double().cpu()
+    z = st[..., :D] / st[..., D + 1:D + 2]
+    lse = st[..., D] + torch.log(st[..., D + 1])
+    assert O.rel_l2(z, a_ref / l_ref[..., None]) <= TOL[dtype]
+    assert O.rel_l2(lse, m_ref + torch.log(l_ref)) <= TOL[dtype]
+
+
+def test_prefill_dense_small(cuda_dev):
+    import flare_b200 as fb
+    q, k, v = _inputs(1, 2, 40, 16, 16, torch.float32, seed=3)
+    y_ref = O.causal_dense(q.double(), k.double(), v.double(), 0.7)
+    y, _ = fb.flare_causal_prefill(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), 0.7)
+    assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_decode_continues_prefill(cuda_dev, dtype):
+    """prefill(first part) then token-by-token decode == prefill(everything)."""
+    import flare_b200 as fb
+    B, H, N, M, D = 2, 2, 160, 64, 32
+    q, k, v = _inputs(B, H, N, M, D, dtype, seed=5)
+    qd, kd, vd = q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)
+    y_all, st_all = fb.flare_causal_prefill(qd, kd, vd, 1.0)
+    n0 = 100
+    y0, st = fb.flare_causal_prefill(qd, kd[:, :, :n0], vd[:, :, :n0], 1.0)
+    ys = [y0]
+    for t in range(n0, N - 8):
+        ys.append(fb.flare_causal_decode(qd, kd[:, :, t:t + 1], vd[:, :, t:t + 1], st, 1.0))
+    ys.append(fb.flare_causal_decode(qd, kd[:, :, N - 8:], vd[:, :, N - 8:], st, 1.0))   # several tokens in one call
+    y_inc = torch.cat(ys, dim=2)
+    y_ref, _ = O.causal_recurrent(q.double(), k.double(), v.double(), 1.0)
+    assert O.rel_l2(y_inc.double().cpu(), y_ref) <= TOL[dtype]
+    assert O.rel_l2(y_inc.double().cpu(), y_all.double().cpu()) <= TOL[dtype]
+
+
+def test_decode_from_empty_state(cuda_dev):
+    import flare_b200 as fb
+    B, H, N, M, D = 1, 2, 24, 32, 32
+    q, k, v = _inputs(B, H, N, M, D, torch.float32, seed=7)
+    st = fb.causal_state_init(B, H, M, D, cuda_dev)
+    y = fb.flare_causal_decode(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), st, 1.0)
+    y_ref, _ = O.causal_recurrent(q.double(), k.double(), v.double(), 1.0)
+    assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-5
+
+
+def test_prefill_with_prior_state(cuda_dev):
+    import flare_b200 as fb
+    B, H, N, M, D = 1, 2, 300, 64, 32
+    q, k, v = _inputs(B, H, N, M, D, torch.float32, seed=9)
+    qd, kd, vd = q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)
+    _, st = fb.flare_causal_prefill(qd, kd[:, :, :128], vd[:, :, :128], 1.0)
+    y2, _ = fb.flare_causal_prefill(qd, kd[:, :, 128:], vd[:, :, 128:], 1.0, state=st)
+    y_ref, _ = O.causal_recurrent(q.double(), k.double(), v.double(), 1.0)
+    assert O.rel_l2(y2.double().cpu(), y_ref[:, :, 128:]) <= 2e-5
+
+
+def test_unsupported_shape_is_refused(cuda_dev):
+    import flare_b200 as fb
+    q, k, v = _inputs(1, 1, 16, 520, 64, torch.float32)
+    with pytest.raises(Exception):
+        fb.flare_causal_prefill(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), 1.0)
