@@ -54,6 +54,11 @@ SIGNATURES = {
     "flare_causal_workspace_bytes": (_sz, [_P]),
     "flare_causal_prefill": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_causal_decode": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_causal_linear_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "flare_causal_linear": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_triple_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "flare_triple_outer": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp]),
+    "flare_triple_contract": (_i, [_i, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _vp, C.c_float, _vp, _vp]),
     "flare_device_status": (_i, [C.POINTER(C.c_int), _i]),
     "flare_debug_phase_counters": (_i, [_vp]),
     "flare_probe_ex2": (_i, [_i, _i, _vp, _vp]),

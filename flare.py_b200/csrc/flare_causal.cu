@@ -103,7 +103,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
 k_causal_walk(CausalArgs a) {
   constexpr int G = kThreads / D;                  // latent groups
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   const int M = a.M;
   constexpr int DP = D + 1;                        // padded rows: no bank conflicts when a warp walks rows
   const int MP = M + 1;

@@ -189,6 +189,32 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
 int flare_causal_decode(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
                         float* state, flare_stream_t stream);
 
+/* Causal linear attention, Y_t = Q_t . sum_{n<=t} K_n^T V_n / N (lra/models/triton/causal_linear.py:23-145;
+ * reference form :317-336; forward only, as there).  q, k: [B,H,N,Dk]; v, y: [B,H,N,Dv]; strides in
+ * elements for dims (b, h, n), unit stride on the last dim.  workspace:
+ * flare_causal_linear_workspace_bytes bytes.  Dk, Dv up to 256. */
+size_t flare_causal_linear_workspace_bytes(int B, int H, int N, int Dk, int Dv);
+int flare_causal_linear(int B, int H, int N, int Dk, int Dv, int dtype, const void* q, const int64_t* q_stride,
+                        const void* k, const int64_t* k_stride, const void* v, const int64_t* v_stride,
+                        void* y, const int64_t* y_stride, float* workspace, flare_stream_t stream);
+
+/* Triple attention (lra/models/triton/triple.py:27-290; einsum references :846-860, :887-931) as the two
+ * shapes of work its forward and backward are made of.  Inputs are [BH, N, D] contiguous in `dtype`,
+ * as the reference makes them (triple.py:51-55); tensors of rank 3 are fp32.
+ *   flare_triple_outer:    out[bh][i][j][k] = alpha * sum_n a[n,i] b[n,j] c[n,k]   (STATE with alpha = 1/N,
+ *                          dSTATE with alpha = 1).  Da in {16,32,64}; Db, Dc multiples of 4 up to 64.
+ *                          workspace: flare_triple_workspace_bytes bytes.
+ *   flare_triple_contract: out[bh][n][x] = alpha * sum_{y,z} T[x,y,z] a[n,y] b[n,z], where T[x,y,z] is read
+ *                          at t + bh*Dx*Dy*Dz + x*sx + y*sy + z*sz (element strides: any permutation of a
+ *                          contiguous [D0,D1,D2] tensor).  O, dQ1, dQ2, dK1, dK2, dV are all of this form.
+ *                          Dz in {16,32,64}; Dx, Dy multiples of 4 up to 64. */
+size_t flare_triple_workspace_bytes(int BH, int N, int Da, int Db, int Dc);
+int flare_triple_outer(int BH, int N, int Da, int Db, int Dc, int dtype, const void* a, const void* b,
+                       const void* c, float alpha, float* out, float* workspace, flare_stream_t stream);
+int flare_triple_contract(int BH, int N, int Dx, int Dy, int Dz, int dtype, const float* t, int64_t sx,
+                          int64_t sy, int64_t sz, const void* a, const void* b, float alpha, void* out,
+                          flare_stream_t stream);
+
 /* Reads (and optionally clears) the device status word of the current device; synchronises.
  * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
