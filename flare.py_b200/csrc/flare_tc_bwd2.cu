@@ -567,8 +567,10 @@ int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, cons
   k_bwd_range_c<<<dim3(kRangeParts, (unsigned)bh), 256, 0, st>>>(lse_n, c.N, part);
   k_bwd_range_final<<<(unsigned)bh, 256, 0, st>>>(lse_m, c.M, part, mu, flag);
   *flag_out = flag;
-  // the software-pipelined kernel where it applies (D = 32, 128 < M <= 256), else the step-serial one;
-  // FLARE_NO_PIPELINE=1 forces the latter
+  // the 128-latent-step kernel where it applies (D = 32, M <= 256), else the step-serial one;
+  // FLARE_BWD3 / FLARE_NO_PIPELINE select the earlier kernels (tuning and tests)
+  if (tc_bwd4_supported(c, FLARE_BF16) && !getenv("FLARE_BWD3") && !getenv("FLARE_NO_PIPELINE"))
+    return tc_bwd4_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
   if (tc_bwd3_supported(c, FLARE_BF16) && !getenv("FLARE_NO_PIPELINE"))
     return tc_bwd3_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
   switch (c.D) {

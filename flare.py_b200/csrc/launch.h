@@ -57,6 +57,11 @@ bool tc_bwd3_supported(const Ctx& c, int dtype);
 int tc_bwd3_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                    const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* dq_part, const float* mu, const int* flag, cudaStream_t st);
+// the same pass in 128-latent steps (two per token tile): S^T double-buffered, T' single
+bool tc_bwd4_supported(const Ctx& c, int dtype);
+int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                   const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                   float* dq_part, const float* mu, const int* flag, cudaStream_t st);
 int tc_read_status(int* out, bool clear);
 int* tc_status_ptr();
 void tc_set_phase_counters(long long* dev_ptr);

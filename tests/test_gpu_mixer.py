@@ -74,6 +74,22 @@ def test_parity_fwd_bwd(fb, cuda_dev, path, dtype, B, H, N, M, D, scale):
     assert_close(got, oracle_all(q, k, v, dy, scale), TOL[dtype])
 
 
+@pytest.mark.parametrize("variant", ["FLARE_BWD3", "FLARE_NO_PIPELINE"])
+@pytest.mark.parametrize("B,H,N,M,D", [
+    (1, 2, 1000, 256, 32),      # ragged last tile, two 128-latent blocks
+    (2, 2, 2048, 192, 32),      # second latent block half full
+    (1, 3, 700, 128, 32),       # one block
+    (1, 1, 128 * 37 + 5, 256, 32),
+    (2, 1, 300, 64, 32),
+])
+def test_backward_kernel_variants(fb, cuda_dev, monkeypatch, variant, B, H, N, M, D):
+    """The alternative one-exponential backward kernels (selected by environment switches) against the oracle."""
+    monkeypatch.setenv(variant, "1")
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=torch.bfloat16, seed=11)
+    got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev)
+    assert_close(got, oracle_all(q, k, v, dy, 1.0), 2e-2)
+
+
 def test_single_token(fb, cuda_dev):
     # N = 1: z = v, y = v and every gradient of q and k vanishes identically
     q, k, v, dy = O.make_inputs(3, 2, 1, 16, 16, seed=17)
