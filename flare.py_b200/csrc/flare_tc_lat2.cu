@@ -68,7 +68,7 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 
 constexpr int kLat2Softmax = 256;
 
-// One chunk of 16 score columns of one row: P = 2^(S sl - m) (MODE 0) or 2^(S sl - C log2e) (MODE 1),
+// One chunk of 16 score columns of one row: P = 2^(S sl - m) (MODE 0) or 2^(S sl - C2) (MODE 1, C2 = C log2e),
 // packed to bf16 pairs; the two running sums take alternate columns.
 template <int MODE, bool MASKED>
 __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_run, const float* c16, int col0,
@@ -88,8 +88,8 @@ __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_
       x0 = fmaf(__uint_as_float(r[2 * j]), sl, -m_run);
       x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -m_run);
     } else {
-      x0 = fmaf(__uint_as_float(r[2 * j]), sl, -cv[2 * j] * kLog2e);
-      x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -cv[2 * j + 1] * kLog2e);
+      x0 = fmaf(__uint_as_float(r[2 * j]), sl, -cv[2 * j]);
+      x1 = fmaf(__uint_as_float(r[2 * j + 1]), sl, -cv[2 * j + 1]);
     }
     float e0 = ex2(x0), e1 = ex2(x1);
     if (MASKED) {
@@ -236,6 +236,18 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       __syncwarp();
     };
 
+    // MODE 1: the landed C_n row of a tile, converted to log2 units once for all 256 softmax threads
+    // (lane l takes entries 4l..4l+3) and published through bar_k like the norm bound of MODE 0
+    auto tile_cscale = [&](int t) {
+      float4* c4 = reinterpret_cast<float4*>(sC + (t % NS) * 128) + lane;
+      float4 c = *c4;
+      c.x *= kLog2e; c.y *= kLog2e; c.z *= kLog2e; c.w *= kLog2e;
+      *c4 = c;
+      __syncwarp();
+      if (lane == 0) mbar_arrive_l2(&bar_k[t & 1]);
+      __syncwarp();
+    };
+
     const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
     const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
     const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
@@ -260,6 +272,9 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     if (MODE == 0) {
       tile_kmax(0);
       if (T > 1) { mbar_wait(&bar_full[1], 0, a.status, abort_flag); tile_kmax(1); }
+    } else if (c_bulk) {
+      tile_cscale(0);
+      if (T > 1) { mbar_wait(&bar_full[1], 0, a.status, abort_flag); tile_cscale(1); }
     }
     for (int t = 0; t < T; ++t) {
       const int p = t & 1;
@@ -296,10 +311,10 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         }
         __syncwarp();
       }
-      if (MODE == 0 && t + 2 < T) {
-        // the bound of tile t+2, while the softmax threads work on tile t+1
+      if ((MODE == 0 || c_bulk) && t + 2 < T) {
+        // the bound (or the C_n row) of tile t+2, while the softmax threads work on tile t+1
         mbar_wait(&bar_full[(t + 2) % NS], (uint32_t)((t + 2) / NS) & 1, a.status, abort_flag);
-        tile_kmax(t + 2);
+        if (MODE == 0) tile_kmax(t + 2); else tile_cscale(t + 2);
       }
     }
     __syncwarp();
@@ -327,10 +342,13 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       const int cnt = min(128, n1 - tile0);
       float bound = 0.f;
       if (MODE == 1) {
-        // C_n of the tile: landed with K and dY, or (unaligned rows) fetched by the first 128 threads
-        mbar_wait(&bar_full[st], (uint32_t)(t / NS) & 1, a.status, abort_flag);
-        if (!c_bulk) {
-          if (tid < 128) sC[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] : 0.f;
+        // C_n of the tile in log2 units: landed with K and dY and scaled by the issuer warp, or
+        // (unaligned rows) fetched by the first 128 threads
+        if (c_bulk) {
+          mbar_wait(&bar_k[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
+        } else {
+          mbar_wait(&bar_full[st], (uint32_t)(t / NS) & 1, a.status, abort_flag);
+          if (tid < 128) sC[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] * kLog2e : 0.f;
           named_bar_sync(2, kLat2Softmax);
         }
       } else {
