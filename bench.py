@@ -310,14 +310,33 @@ def run_ours(args):
     hdv = torch.empty_like(hk).pin_memory()
     hdq = torch.empty(H, M, D, dtype=DTYPE).pin_memory()
 
+    # The step a user of the library runs with host-resident data.  The two PCIe directions are used at
+    # the same time where the data dependences allow it: dY goes up while the forward runs and y comes
+    # down (side streams), everything else is ordered on the current stream.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
     def e2e_step():
+        cur = torch.cuda.current_stream(dev)
         q_ = hq.to(dev, non_blocking=True).requires_grad_(True)
         k_ = hk.to(dev, non_blocking=True).requires_grad_(True)
         v_ = hv.to(dev, non_blocking=True).requires_grad_(True)
-        dy_ = hdy.to(dev, non_blocking=True)
+        up = torch.cuda.Event()
+        up.record(cur)
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(up)                       # after k, v: the link is busy until then anyway
+            dy_ = hdy.to(dev, non_blocking=True)
+            dy_.record_stream(cur)
         y_ = mixer(q_, k_, v_)
+        fwd = torch.cuda.Event()
+        fwd.record(cur)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(fwd)
+            yd = y_.detach()
+            yd.record_stream(s_out)
+            hy.copy_(yd, non_blocking=True)
+        cur.wait_stream(s_in)
         y_.backward(dy_)
-        hy.copy_(y_.detach(), non_blocking=True)
+        cur.wait_stream(s_out)                        # device-to-host copies share one direction: keep them in order
         hdk.copy_(k_.grad, non_blocking=True)
         hdv.copy_(v_.grad, non_blocking=True)
         hdq.copy_(q_.grad, non_blocking=True)
