@@ -12,7 +12,7 @@
 //
 // and decode is one launch of the same kernel per token on the caller's record.  Pass 3 and decode are fp32
 // SIMT kernels: thread (d, g) keeps acc[m][d] of its latents m = g, g + G, ... in registers, scores and
-// weights of a 64-token sub-chunk sit in shared memory.  Scores are computed once per token; the
+// weights of a 32-token sub-chunk sit in shared memory (two CTAs per SM).  Scores are computed once per token; the
 // sequential part is O(T M D) fused multiply-adds per chunk, the minimum for this recurrence.
 #include <cstdarg>
 #include <cstdio>
@@ -26,7 +26,7 @@ namespace {
 using namespace flare;
 
 constexpr int kThreads = 256;
-constexpr int kSub = 64;          // tokens per sub-chunk
+constexpr int kSub = 32;          // tokens per sub-chunk (two CTAs per SM fit with this)
 constexpr int kChunk = 128;       // tokens per record (pass 1 range length)
 constexpr int kMaxLat = 32;       // latents per thread
 
@@ -58,12 +58,26 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) acc[i] = state_in[row * W + lane + 32 * i];
   }
+  // the record of chunk c + 1 is fetched while chunk c is combined: the chain is latency bound
+  float mn_ = 0.f, ln_ = 0.f, an_[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const float* r = rec + row * W;
+    mn_ = r[D]; ln_ = r[D + 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) an_[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+  }
   for (int c = 0; c < n_chunks; ++c) {
     float* r = rec + c * cs + row * W;
-    const float mc = r[D], lc = r[D + 1];
+    const float mc = mn_, lc = ln_;
     float ac[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ac[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+    for (int i = 0; i < 4; ++i) ac[i] = an_[i];
+    if (c + 1 < n_chunks) {
+      const float* rn = r + cs;
+      mn_ = rn[D]; ln_ = rn[D + 1];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) an_[i] = (lane + 32 * i < D) ? rn[lane + 32 * i] : 0.f;
+    }
     __syncwarp();
     // the record of everything before chunk c
 #pragma unroll
@@ -106,10 +120,10 @@ k_causal_walk(CausalArgs a) {
   extern __shared__ __align__(16) float sm[];
   const int M = a.M;
   constexpr int DP = D + 1;                        // padded rows: no bank conflicts when a warp walks rows
-  const int MP = M + 1;
+  const int MP = M + 4;                            // keeps rows 16-byte aligned for the recurrence's vector loads
   float* sQ = sm;                                  // [M][DP]
-  float* sK = sQ + M * DP;                         // [kSub][D]
-  float* sV = sK + kSub * D;                       // [kSub][D]
+  float* sK = sQ + M * DP;                         // [kSub][DP]
+  float* sV = sK + kSub * DP;                      // [kSub][D]
   float* sS = sV + kSub * D;                       // [kSub][MP]  scores, then weights
   float* sE = sS + kSub * MP;                      // [kSub][MP]
   float* sMu = sE + kSub * MP;                     // [M]
@@ -121,7 +135,7 @@ k_causal_walk(CausalArgs a) {
 
   const int tid = threadIdx.x;
   const int d = tid % D, g = tid / D;
-  const int nlat = M / G;                          // latents of this thread: g, g + G, ...
+  const int nlat = M / G;                          // latents of this thread: g * nlat ... g * nlat + nlat - 1
   const int chunk = blockIdx.x, bh = blockIdx.y;
   const int b = bh / a.H, h = bh % a.H;
   const int n0 = chunk * a.tokens_per_cta, n1 = min(a.N, n0 + a.tokens_per_cta);
@@ -138,35 +152,75 @@ k_causal_walk(CausalArgs a) {
   for (int m = tid; m < M; m += kThreads) { sMu[m] = rec[m * W + D]; sL[m] = rec[m * W + D + 1]; }
   float acc[kMaxLat];
 #pragma unroll
-  for (int j = 0; j < kMaxLat; ++j) acc[j] = (j < nlat) ? rec[(g + j * G) * W + d] : 0.f;
+  for (int j = 0; j < kMaxLat; ++j) acc[j] = (j < nlat) ? rec[(g * nlat + j) * W + d] : 0.f;
   __syncthreads();
 
   for (int s0 = n0; s0 < n1; s0 += kSub) {
     const int cnt = min(kSub, n1 - s0);
     for (int i = tid; i < cnt * D; i += kThreads) {
       const int t = i / D, dd = i % D;
-      sK[i] = to_f32(kp[(long long)(s0 + t) * a.ks[2] + dd]);
+      sK[t * DP + dd] = to_f32(kp[(long long)(s0 + t) * a.ks[2] + dd]);
       sV[i] = to_f32(vp[(long long)(s0 + t) * a.vs[2] + dd]);
     }
     __syncthreads();
-    // scores S[t][m] = scale q_m . k_t
-    for (int i = tid; i < cnt * M; i += kThreads) {
-      const int t = i / M, m = i % M;
-      const float* qr = sQ + m * DP;
-      const float* kr = sK + t * D;
-      float s = 0.f;
+    // scores S[t][m] = scale q_m . k_t.  Few tokens (decode): one dot product per thread.
+    if (cnt < 8) {
+      for (int i = tid; i < cnt * M; i += kThreads) {
+        const int t = i / M, m = i % M;
+        const float* qr = sQ + m * DP;
+        const float* kr = sK + t * DP;
+        float sacc = 0.f;
 #pragma unroll 8
-      for (int dd = 0; dd < D; ++dd) s = fmaf(qr[dd], kr[dd], s);
-      sS[t * MP + m] = s * a.scale;
+        for (int dd = 0; dd < D; ++dd) sacc = fmaf(qr[dd], kr[dd], sacc);
+        sS[t * MP + m] = sacc * a.scale;
+      }
+    } else {
+      // thread (mg, tg) computes latents mg + 32a and tokens 4tg + b in registers, so every shared-memory
+      // load feeds 4 (q) or up to 16 (k) multiply-adds
+      const int mg = tid & 31, tg = tid >> 5;
+      const int rm = (M + 31) >> 5;                // latents per thread, at most 16 (M <= 512)
+      float sc[16][4];
+#pragma unroll
+      for (int a_ = 0; a_ < 16; ++a_)
+#pragma unroll
+        for (int b_ = 0; b_ < 4; ++b_) sc[a_][b_] = 0.f;
+      const float* k0 = sK + (4 * tg) * DP;
+      for (int dd = 0; dd < D; ++dd) {
+        const float kv0 = k0[dd], kv1 = k0[DP + dd], kv2 = k0[2 * DP + dd], kv3 = k0[3 * DP + dd];
+#pragma unroll
+        for (int a_ = 0; a_ < 16; ++a_) {
+          if (a_ < rm) {
+            const int m = min(mg + 32 * a_, M - 1);
+            const float qv = sQ[m * DP + dd];
+            sc[a_][0] = fmaf(qv, kv0, sc[a_][0]); sc[a_][1] = fmaf(qv, kv1, sc[a_][1]);
+            sc[a_][2] = fmaf(qv, kv2, sc[a_][2]); sc[a_][3] = fmaf(qv, kv3, sc[a_][3]);
+          }
+        }
+      }
+#pragma unroll
+      for (int a_ = 0; a_ < 16; ++a_) {
+        const int m = mg + 32 * a_;
+        if (a_ < rm && m < M) {
+#pragma unroll
+          for (int b_ = 0; b_ < 4; ++b_)
+            if (4 * tg + b_ < cnt) sS[(4 * tg + b_) * MP + m] = sc[a_][b_] * a.scale;
+        }
+      }
     }
     __syncthreads();
-    // per token: max and sum over the latents (the scatter softmax)
-    for (int t = tid; t < cnt; t += kThreads) {
+    // per token: max and sum over the latents (the scatter softmax); eight threads per token, latents
+    // part, part + 8, ... each, combined by shuffles
+    {
+      const int t = tid >> 3, part = tid & 7;
       float mx = -INFINITY;
-      for (int m = 0; m < M; ++m) mx = fmaxf(mx, sS[t * MP + m]);
+      if (t < cnt) for (int m = part; m < M; m += 8) mx = fmaxf(mx, sS[t * MP + m]);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       float su = 0.f;
-      for (int m = 0; m < M; ++m) su += __expf(sS[t * MP + m] - mx);
-      sCm[t] = mx; sCs[t] = su;
+      if (t < cnt) for (int m = part; m < M; m += 8) su += __expf(sS[t * MP + m] - mx);
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) su += __shfl_xor_sync(0xffffffffu, su, o);
+      if (t < cnt && part == 0) { sCm[t] = mx; sCs[t] = su; }
     }
     __syncthreads();
     // per latent: new running max over the sub-chunk, E = e^{S - mu}, running l, weights
@@ -187,18 +241,34 @@ k_causal_walk(CausalArgs a) {
     }
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) acc[j] *= sA[g + j * G];
+    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) acc[j] *= sA[g * nlat + j];
     // the recurrence over the sub-chunk's tokens
     for (int t = 0; t < cnt; ++t) {
       const float vd = sV[t * D + d];
-      const float* er = sE + t * MP + g;
-      const float* gr = sS + t * MP + g;
+      const float* er = sE + t * MP + g * nlat;
+      const float* gr = sS + t * MP + g * nlat;
       float y = 0.f;
+      if ((nlat & 3) == 0) {                       // this thread's latents are contiguous: 16-byte broadcast loads
+        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;   // four chains instead of one of length nlat
 #pragma unroll
-      for (int j = 0; j < kMaxLat; ++j) {
-        if (j < nlat) {
-          acc[j] = fmaf(er[j * G], vd, acc[j]);
-          y = fmaf(gr[j * G], acc[j], y);
+        for (int j4 = 0; j4 < kMaxLat / 4; ++j4) {
+          if (4 * j4 < nlat) {
+            const float4 e4 = *reinterpret_cast<const float4*>(er + 4 * j4);
+            const float4 g4 = *reinterpret_cast<const float4*>(gr + 4 * j4);
+            acc[4 * j4] = fmaf(e4.x, vd, acc[4 * j4]);         y0 = fmaf(g4.x, acc[4 * j4], y0);
+            acc[4 * j4 + 1] = fmaf(e4.y, vd, acc[4 * j4 + 1]); y1 = fmaf(g4.y, acc[4 * j4 + 1], y1);
+            acc[4 * j4 + 2] = fmaf(e4.z, vd, acc[4 * j4 + 2]); y2 = fmaf(g4.z, acc[4 * j4 + 2], y2);
+            acc[4 * j4 + 3] = fmaf(e4.w, vd, acc[4 * j4 + 3]); y3 = fmaf(g4.w, acc[4 * j4 + 3], y3);
+          }
+        }
+        y = (y0 + y1) + (y2 + y3);
+      } else {
+#pragma unroll
+        for (int j = 0; j < kMaxLat; ++j) {
+          if (j < nlat) {
+            acc[j] = fmaf(er[j], vd, acc[j]);
+            y = fmaf(gr[j], acc[j], y);
+          }
         }
       }
       float* yb = sY + (t & 1) * kThreads;         // two buffers: one barrier per token
@@ -216,13 +286,13 @@ k_causal_walk(CausalArgs a) {
   if (!a.prefix) {                                 // decode: the record moves on
     float* st = a.state + ((long long)b * a.H + h) * M * W;
 #pragma unroll
-    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) st[(g + j * G) * W + d] = acc[j];
+    for (int j = 0; j < kMaxLat; ++j) if (j < nlat) st[(g * nlat + j) * W + d] = acc[j];
     for (int m = tid; m < M; m += kThreads) { st[m * W + D] = sMu[m]; st[m * W + D + 1] = sL[m]; }
   }
 }
 
 size_t walk_smem(int M, int D) {
-  return sizeof(float) * ((size_t)M * (D + 1) + 2 * kSub * D + 2 * (size_t)kSub * (M + 1) + 3 * M + 2 * kSub + 2 * kThreads);
+  return sizeof(float) * ((size_t)(M + kSub) * (D + 1) + kSub * D + 2 * (size_t)kSub * (M + 4) + 3 * M + 2 * kSub + 2 * kThreads);
 }
 
 template <typename T, int D>
