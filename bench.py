@@ -416,6 +416,40 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_causal(args):
+    """Secondary workload (not the headline line): causal FLARE prefill and one decode step at the serving
+    shape B=4, H=16, N=8192, D=64, M=128 bf16, device-resident inputs, CUDA events."""
+    import flare_b200 as fb
+    dev = torch.device("cuda:0")
+    B, H, N, D, M = 4, 16, 8192, 64, 128
+    g = torch.Generator().manual_seed(0)
+    q = (torch.randn(H, M, D, generator=g) * D ** -0.25).bfloat16().to(dev)
+    k = (torch.randn(B, H, N, D, generator=g) * D ** -0.25).bfloat16().to(dev)
+    v = torch.randn(B, H, N, D, generator=g).bfloat16().to(dev)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    for _ in range(max(args.warmup, 1)):
+        _, st = fb.flare_causal_prefill(q, k, v, 1.0)
+    ms = timed(lambda: fb.flare_causal_prefill(q, k, v, 1.0), args.steps)
+    k1, v1 = k[:, :, :1].contiguous(), v[:, :, :1].contiguous()
+    fb.flare_causal_decode(q, k1, v1, st, 1.0)
+    us = timed(lambda: fb.flare_causal_decode(q, k1, v1, st, 1.0), max(args.steps, 20)) * 1e3
+    print(json.dumps(dict(metric="causal FLARE prefill Mtokens/s", value=B * N / ms / 1e3, unit="Mtokens/s", n_gpus=1,
+                          steps=args.steps, warmup=max(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
+                          dtype="bf16", data="synthetic", decode_step_us=us,
+                          config=dict(workload=f"causal_prefill: B={B} H={H} N={N} M={M} D={D} bf16, one layer's mixer"))),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -424,8 +458,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override N (profiling on a smaller case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal"],
+                    help="mixer: the headline line; causal: a secondary line for causal prefill/decode")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "causal":
+        run_causal(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
