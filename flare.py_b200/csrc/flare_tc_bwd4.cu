@@ -27,17 +27,6 @@
 #include "tc_common.cuh"
 #include "tma_host.h"
 
-#ifndef EXPER
-#define EXPER 0
-#endif
-#if EXPER >= 20
-#define PROF_T(x) const long long x = clock64()
-#define PROF_ADD(c, d) c += (unsigned)(d)
-#else
-#define PROF_T(x)
-#define PROF_ADD(c, d)
-#endif
-
 namespace flare {
 
 using namespace tc;
@@ -60,7 +49,6 @@ struct Bwd4Args {
   long long dks[3], dvs[3];
   float* dq_part;              // [S,B,H,M,D]
   int* status;
-  long long* prof;
 };
 
 struct Bwd4Smem {
@@ -512,18 +500,13 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   } else {
     // ================= softmax threads =================
     int s = 0;
-#if EXPER >= 20
-    unsigned c_ws = 0, c_a = 0, c_wt = 0, c_ld = 0, c_b = 0, c_dr = 0;
-#endif
     for (int u = 0; u < U; ++u) {
       const int xb = u & 1;
       const uint32_t buf = lane_base + cS + 128 * xb + 32 * c4;
-      PROF_T(s0);
       const float* l2p = sL2 + s * 128 + 32 * c4;
       // ---- phase A: P = ex2(S^T sl - L), packed into the first 16 of this thread's 32 columns ------
       mbar_wait_hot(&bar_s[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
-      PROF_T(s1);
       uint32_t ra[16], rb[16];
       float p[32];
       tmem_ld16(buf, ra);
@@ -553,17 +536,14 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         tmem_st16(buf, pp);
       }
       // ---- phase B: dS = P * T', packed into the last 16 columns and to shared memory ---------------
-      PROF_T(s2);
       mbar_wait_hot(bar_t, (uint32_t)u & 1, a.status, abort_flag);
       tc_fence_after();
-      PROF_T(s3);
       const uint32_t tcol = lane_base + cT + 32 * c4;
       tmem_ld16(tcol, ra);
       tmem_ld16(tcol + 16, rb);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive4(bar_tl);                        // the T' buffer may take the next step
-      PROF_T(s4);
       uint32_t pd[16];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -577,29 +557,13 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       for (int i = 0; i < 4; ++i)
         *reinterpret_cast<uint4*>(ds_row + swz_off<128>(row, 4 * (c4 & 1) + i)) =
             make_uint4(pd[4 * i], pd[4 * i + 1], pd[4 * i + 2], pd[4 * i + 3]);
-      PROF_T(s5);
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive4(&bar_pd[xb]);
-#if EXPER >= 20
-      { const long long s6 = clock64();
-        c_ws += (unsigned)(s1 - s0); c_a += (unsigned)(s2 - s1); c_wt += (unsigned)(s3 - s2); c_ld += (unsigned)(s4 - s3);
-        c_b += (unsigned)(s5 - s4); c_dr += (unsigned)(s6 - s5); }
-#endif
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       if (++s == n_sub) s = 0;
     }
-#if EXPER >= 20
-    if (a.prof && tid == 0) {
-      atomicAdd((unsigned long long*)&a.prof[8], (unsigned long long)c_ws);
-      atomicAdd((unsigned long long*)&a.prof[9], (unsigned long long)c_a);
-      atomicAdd((unsigned long long*)&a.prof[10], (unsigned long long)c_wt);
-      atomicAdd((unsigned long long*)&a.prof[11], (unsigned long long)c_ld);
-      atomicAdd((unsigned long long*)&a.prof[12], (unsigned long long)c_b);
-      atomicAdd((unsigned long long*)&a.prof[13], (unsigned long long)c_dr);
-    }
-#endif
 
     // ---- tail: the dQ partial --------------------------------------------------------------------
     if (!*reinterpret_cast<volatile int*>(abort_flag)) {
@@ -659,7 +623,6 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   for (int i = 0; i < 3; ++i) { a.ys[i] = c.ys[i]; a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
-  a.prof = tc_phase_counters();
   static bool attr_done = false;
   constexpr int smem = Bwd4Smem::kBytes;
   if (!attr_done) {
