@@ -58,6 +58,9 @@ int auto_splits(const FlareProblem* p) {
   const long long base = (long long)p->B * p->H * ((p->M + lpb - 1) / lpb);
   long long s = (4LL * 148 + base - 1) / base;
   const long long max_s = (p->N + 127) / 128;
+  // short ranges (a context-parallel shard, a small N): one wave of CTAs instead of two, so that the
+  // per-CTA set-up (resident operands, first tiles) is paid once
+  if (max_s / s < 64) s = (2LL * 148) / base > 0 ? (2LL * 148) / base : 1;
   if (s > max_s) s = max_s;
   if (s > 1024) s = 1024;
   if (s < 1) s = 1;
