@@ -265,9 +265,16 @@ def run_ours(args):
     v = hv.to(dev).requires_grad_(True)
     dy = hdy.to(dev)
 
+    # N > 1: the exchanges go through symmetric memory and peer loads (FLARE_CP_EXCHANGE=nccl selects the
+    # torch.distributed collectives instead)
+    cp_ex = None
+    if world > 1:
+        from flare_b200.parallel import PeerExchange, RecordExchange
+        cp_ex = RecordExchange() if os.environ.get("FLARE_CP_EXCHANGE", "peer") == "nccl" else PeerExchange()
+
     def mixer(q_, k_, v_):
         if world > 1:
-            return flare_mixer_context_parallel(q_, k_, v_, 1.0)
+            return flare_mixer_context_parallel(q_, k_, v_, 1.0, exchange=cp_ex)
         return fb.flare_multihead_mixer(q_, k_, v_, scale=1.0)
 
     def step():

@@ -45,6 +45,8 @@ SIGNATURES = {
     "flare_mixer_bwd": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "flare_gather_partial": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_combine": (_i, [_P, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "flare_combine_peers": (_i, [_P, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "flare_reduce_sum_peers": (_i, [_vp, _i, _i64, _i, _vp, _vp]),
     "flare_scatter": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_bwd_dz_partial": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_reduce_sum": (_i, [_vp, _i, _i64, _i, _vp, _vp]),

@@ -160,6 +160,23 @@ int flare_combine(const FlareProblem* p, const float* rec, int n_parts, float* z
   return after_launch("combine");
 }
 
+int flare_combine_peers(const FlareProblem* p, const float* const* rec_ptrs, int n_parts, float* z32,
+                        void* z_out, float* lse_m, float* rec_out, flare_stream_t stream) {
+  TRY(check_problem(p));
+  if (!rec_ptrs || n_parts < 1) return fail(FLARE_EINVAL, "combine_peers: rec_ptrs null or n_parts < 1");
+  const long long rows = (long long)p->B * p->H * p->M;
+  TRY(launch_combine_ptrs(rec_ptrs, n_parts, rows, p->D, p->dtype, z32, z_out, lse_m, rec_out, (cudaStream_t)stream));
+  return after_launch("combine_peers");
+}
+
+int flare_reduce_sum_peers(const float* const* part_ptrs, int n_parts, int64_t rows, int width, float* out,
+                           flare_stream_t stream) {
+  if (!part_ptrs || !out || n_parts < 1 || rows < 0 || width < 1) return fail(FLARE_EINVAL, "reduce_sum_peers: bad arguments");
+  if (rows == 0) return FLARE_OK;
+  TRY(launch_reduce_sum_ptrs(part_ptrs, n_parts, (long long)rows * width, out, (cudaStream_t)stream));
+  return after_launch("reduce_sum_peers");
+}
+
 int flare_scatter(const FlareProblem* p, const void* q, const void* k, const float* z32,
                   const uint8_t* key_mask, void* y, float* lse_n, flare_stream_t stream) {
   TRY(check_problem(p));

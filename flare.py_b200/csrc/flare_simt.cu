@@ -414,30 +414,41 @@ k_bwd_tokens(Ctx c, const T* __restrict__ q, const T* __restrict__ k, const T* _
 // ---------------------------------------------------------------------------------
 // log-sum-exp combine of records, and plain ordered sum
 // ---------------------------------------------------------------------------------
+// Where part p of a partial array lives: at base + p * stride (one buffer of this GPU), or at ptrs[p]
+// (one buffer per rank, this GPU's or a peer's memory mapped into this process; plain loads).
+struct PartsStrided {
+  const float* base; long long stride;
+  __device__ __forceinline__ const float* at(int p) const { return base + p * stride; }
+};
+struct PartsPtrs {
+  const float* const* ptrs;
+  __device__ __forceinline__ const float* at(int p) const { return ptrs[p]; }
+};
+
+template <typename Parts>
 __global__ void __launch_bounds__(kThreads)
-k_combine(const float* __restrict__ rec, int n_parts, long long rows, int D, int dtype,
+k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
           float* __restrict__ z32, void* __restrict__ z_out, float* __restrict__ lse_m,
           float* __restrict__ rec_out) {
   const long long row = (long long)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   if (row >= rows) return;
   const int W = D + 2;
-  const long long pstride = rows * W;
   float mx = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, rec[p * pstride + row * W + D]);
+  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, parts.at(p)[row * W + D]);
   float lt = 0.f;
   for (int p = 0; p < n_parts; ++p) {
-    const float m = rec[p * pstride + row * W + D];
+    const float m = parts.at(p)[row * W + D];
     const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
-    lt = fmaf(w, rec[p * pstride + row * W + D + 1], lt);
+    lt = fmaf(w, parts.at(p)[row * W + D + 1], lt);
   }
   const float inv = 1.f / lt;
   for (int d = lane; d < D; d += 32) {
     float a = 0.f;
     for (int p = 0; p < n_parts; ++p) {
-      const float m = rec[p * pstride + row * W + D];
+      const float m = parts.at(p)[row * W + D];
       const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
-      a = fmaf(w, rec[p * pstride + row * W + d], a);
+      a = fmaf(w, parts.at(p)[row * W + d], a);
     }
     if (rec_out) rec_out[row * W + d] = a;
     const float z = a * inv;
@@ -454,12 +465,13 @@ k_combine(const float* __restrict__ rec, int n_parts, long long rows, int D, int
   }
 }
 
+template <typename Parts>
 __global__ void __launch_bounds__(256)
-k_reduce_sum(const float* __restrict__ parts, int n_parts, long long n, float* __restrict__ out) {
+k_reduce_sum(Parts parts, int n_parts, long long n, float* __restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float a = 0.f;
-  for (int p = 0; p < n_parts; ++p) a += parts[p * n + i];
+  for (int p = 0; p < n_parts; ++p) a += parts.at(p)[i];
   out[i] = a;
 }
 
@@ -539,13 +551,28 @@ int simt_bwd_tokens(const Ctx& c, int dtype, const void* q, const void* k, const
 int launch_combine(const float* rec, int n_parts, long long rows, int D, int dtype, float* z32,
                    void* z_out, float* lse_m, float* rec_out, cudaStream_t st) {
   const int rpb = kThreads / 32;
-  k_combine<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(rec, n_parts, rows, D, dtype, z32, z_out,
-                                                                    lse_m, rec_out);
+  k_combine<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(PartsStrided{rec, rows * (D + 2)}, n_parts, rows, D,
+                                                                    dtype, z32, z_out, lse_m, rec_out);
   return FLARE_OK;
 }
 
 int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st) {
-  k_reduce_sum<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(parts, n_parts, n, out);
+  k_reduce_sum<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(PartsStrided{parts, n}, n_parts, n, out);
+  return FLARE_OK;
+}
+
+// The same two kernels over one buffer per rank (device array of n_parts pointers; peers' buffers are
+// read with plain loads over NVLink): the all-gather of the context-parallel exchange fused into its consumer.
+int launch_combine_ptrs(const float* const* recs, int n_parts, long long rows, int D, int dtype, float* z32,
+                        void* z_out, float* lse_m, float* rec_out, cudaStream_t st) {
+  const int rpb = kThreads / 32;
+  k_combine<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(PartsPtrs{recs}, n_parts, rows, D, dtype, z32, z_out,
+                                                                    lse_m, rec_out);
+  return FLARE_OK;
+}
+
+int launch_reduce_sum_ptrs(const float* const* parts, int n_parts, long long n, float* out, cudaStream_t st) {
+  k_reduce_sum<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(PartsPtrs{parts}, n_parts, n, out);
   return FLARE_OK;
 }
 

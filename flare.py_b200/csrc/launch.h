@@ -21,6 +21,9 @@ int simt_bwd_tokens(const Ctx& c, int dtype, const void* q, const void* k, const
 int launch_combine(const float* rec, int n_parts, long long rows, int D, int dtype, float* z32,
                    void* z_out, float* lse_m, float* rec_out, cudaStream_t st);
 int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st);
+int launch_combine_ptrs(const float* const* recs, int n_parts, long long rows, int D, int dtype, float* z32,
+                        void* z_out, float* lse_m, float* rec_out, cudaStream_t st);
+int launch_reduce_sum_ptrs(const float* const* parts, int n_parts, long long n, float* out, cudaStream_t st);
 int launch_probe_ex2(int blocks, int iters, float* out, cudaStream_t st);
 
 

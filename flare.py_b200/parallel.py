@@ -11,9 +11,14 @@ enough:
   backward: local dZ partial -> all_reduce(SUM) -> local dK, dV, dQ partial ->
             all_reduce(SUM) of dQ (the latents are replicated).
 
-The collectives are plain ``torch.distributed`` calls (NCCL on GPUs, gloo in the
-CPU tests); ``RecordExchange`` holds them so that the plumbing can be exercised
-without a GPU.
+``RecordExchange`` does this with plain ``torch.distributed`` calls (NCCL on GPUs,
+gloo in the CPU tests), so that the plumbing can be exercised without a GPU.
+``PeerExchange`` (GPUs of one node) fuses each collective into the kernel that
+consumes it: every rank writes its record (or partial sum) into a symmetric-memory
+buffer, a barrier on the stream orders the writes, and the combine / reduce kernel
+reads all ranks' buffers through peer pointers with plain loads over NVLink
+(``flare_combine_peers``, ``flare_reduce_sum_peers``).  No multicast, no waiting
+inside the library's kernels.
 """
 from __future__ import annotations
 
@@ -27,7 +32,7 @@ from . import _cabi
 from ._cabi import check, lib, ptr, stream_of
 from .mixer import _need_cuda, _q3, _tok, make_problem
 
-__all__ = ["RecordExchange", "flare_mixer_context_parallel", "shard_bounds"]
+__all__ = ["RecordExchange", "PeerExchange", "flare_mixer_context_parallel", "shard_bounds"]
 
 
 def shard_bounds(n_tokens: int, world: int, rank: int, multiple: int = 1):
@@ -60,6 +65,42 @@ class RecordExchange:
         return t
 
 
+class PeerExchange(RecordExchange):
+    """The same exchanges through symmetric memory and peer loads (one node, NVLink).
+
+    Buffers are allocated once per (name, size) and used alternately (two halves), so one barrier
+    per exchange is enough: a half is rewritten two exchanges later, after every rank has passed
+    the barrier of the exchange in between, which it reaches only after its reads.
+    """
+
+    def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        super().__init__(group)
+        import torch.distributed._symmetric_memory as symm_mem
+        self._symm = symm_mem
+        self._slots = {}
+
+    def _slot(self, name: str, numel: int, device):
+        key = (name, numel)
+        if key not in self._slots:
+            buf = self._symm.empty(2 * numel, dtype=torch.float32, device=device)
+            hdl = self._symm.rendezvous(buf, group=self.group if self.group is not None else dist.group.WORLD)
+            ptrs = [torch.tensor([int(p) + half * numel * 4 for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
+                    for half in (0, 1)]
+            self._slots[key] = dict(buf=buf, hdl=hdl, ptrs=ptrs, turn=0)
+        s = self._slots[key]
+        half = s["turn"] & 1
+        s["turn"] += 1
+        return s["buf"][half * numel:(half + 1) * numel], s["ptrs"][half], s["hdl"]
+
+    def exchange_buffer(self, name: str, shape, device):
+        """(this rank's buffer for the next exchange, device array of all ranks' pointers, barrier handle)."""
+        numel = 1
+        for d in shape:
+            numel *= int(d)
+        local, ptrs, hdl = self._slot(name, numel, device)
+        return local.view(*shape), ptrs, hdl
+
+
 class _CPMixerFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, scale, ex: RecordExchange, reduce_dq: bool):
@@ -77,14 +118,23 @@ class _CPMixerFn(torch.autograd.Function):
             p = make_problem(q, k, scale, v=v, y=y)
             p.n_splits = lib.flare_pick_splits(C.byref(p))
             rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
-            merged = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=dev)
+            peer = isinstance(ex, PeerExchange)
+            if peer:
+                merged, rec_ptrs, hdl = ex.exchange_buffer("rec", (B, H, M, D + 2), dev)
+            else:
+                merged = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=dev)
             check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), None, ptr(rec), st), "flare_gather_partial")
             check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, None, None, None, ptr(merged), st), "flare_combine")
-            allrec = ex.gather_records(merged)
             z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
             lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
             lse_n = torch.empty(B, H, N, dtype=torch.float32, device=dev)
-            check(lib.flare_combine(C.byref(p), ptr(allrec), ex.world, ptr(z32), None, ptr(lse_m), None, st), "flare_combine")
+            if peer:
+                hdl.barrier()
+                check(lib.flare_combine_peers(C.byref(p), ptr(rec_ptrs), ex.world, ptr(z32), None, ptr(lse_m), None, st),
+                      "flare_combine_peers")
+            else:
+                allrec = ex.gather_records(merged)
+                check(lib.flare_combine(C.byref(p), ptr(allrec), ex.world, ptr(z32), None, ptr(lse_m), None, st), "flare_combine")
             check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st), "flare_scatter")
         ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n)
         ctx.scale, ctx.ex, ctx.reduce_dq, ctx.batched = scale, ex, reduce_dq, batched
@@ -113,19 +163,30 @@ class _CPMixerFn(torch.autograd.Function):
             delta = torch.empty(B, H, N, dtype=torch.float32, device=dev)
             T = _cabi.TERM_BOTH
             check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st), "flare_bwd_dz_partial")
-            check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
-            ex.sum_(dz32)
+            peer = isinstance(ex, PeerExchange)
+            if peer:
+                mine, ptrs, hdl = ex.exchange_buffer("dz", (B, H, M, D), dev)
+                check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(mine), st), "flare_reduce_sum")
+                hdl.barrier()
+                check(lib.flare_reduce_sum_peers(ptr(ptrs), ex.world, B * H * M, D, ptr(dz32), st), "flare_reduce_sum_peers")
+            else:
+                check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
+                ex.sum_(dz32)
             check(lib.flare_bwd_main(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
                                      ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), ptr(part), st),
                   "flare_bwd_main")
-            if ctx.batched:
-                dq = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
-                check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dq), st), "flare_reduce_sum")
+            dq_shape = (B, H, M, D) if ctx.batched else (H, M, D)
+            n_parts, rows = (p.n_splits, B * H * M) if ctx.batched else (p.n_splits * B, H * M)
+            dq = torch.empty(dq_shape, dtype=torch.float32, device=dev)
+            if peer and ctx.reduce_dq:
+                mine, ptrs, hdl = ex.exchange_buffer("dq", dq_shape, dev)
+                check(lib.flare_reduce_sum(ptr(part), n_parts, rows, D, ptr(mine), st), "flare_reduce_sum")
+                hdl.barrier()
+                check(lib.flare_reduce_sum_peers(ptr(ptrs), ex.world, rows, D, ptr(dq), st), "flare_reduce_sum_peers")
             else:
-                dq = torch.empty(H, M, D, dtype=torch.float32, device=dev)
-                check(lib.flare_reduce_sum(ptr(part), p.n_splits * B, H * M, D, ptr(dq), st), "flare_reduce_sum")
-            if ctx.reduce_dq:
-                ex.sum_(dq)
+                check(lib.flare_reduce_sum(ptr(part), n_parts, rows, D, ptr(dq), st), "flare_reduce_sum")
+                if ctx.reduce_dq:
+                    ex.sum_(dq)
         return dq.to(q.dtype), dk, dv, None, None, None
 
 

@@ -119,6 +119,18 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
 int flare_combine(const FlareProblem* p, const float* rec, int n_parts, float* z32,
                   void* z_out, float* lse_m, float* rec_out, flare_stream_t stream);
 
+/* flare_combine / flare_reduce_sum over one buffer per rank instead of one strided array: `rec_ptrs` /
+ * `part_ptrs` is a DEVICE array of n_parts device pointers, each to a [B,H,M,D+2] record (resp. a
+ * rows x width array), on this GPU or in a peer GPU's memory mapped into this process (symmetric
+ * memory, IPC); the kernels read them with plain loads over NVLink, in index order on every rank, so
+ * all ranks get bit-identical results.  This is the context-parallel all-gather (resp. all-reduce)
+ * fused into its consumer; the caller orders it after the peers' writes (a barrier on the stream).
+ * No counterpart in the reference (its only parallelism is data-parallel replicas). */
+int flare_combine_peers(const FlareProblem* p, const float* const* rec_ptrs, int n_parts, float* z32,
+                        void* z_out, float* lse_m, float* rec_out, flare_stream_t stream);
+int flare_reduce_sum_peers(const float* const* part_ptrs, int n_parts, int64_t rows, int width,
+                           float* out, flare_stream_t stream);
+
 /* Second SDPA call: y = softmax_M(k q^T) z32; lse_n may be NULL. */
 int flare_scatter(const FlareProblem* p, const void* q, const void* k, const float* z32,
                   const uint8_t* key_mask, void* y, float* lse_n, flare_stream_t stream);

@@ -24,7 +24,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, q_out):
+def _worker(rank, world, port, q_out, exchange="nccl"):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -32,8 +32,9 @@ def _worker(rank, world, port, q_out):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         import flare_b200 as fb
-        from flare_b200.parallel import flare_mixer_context_parallel, shard_bounds
+        from flare_b200.parallel import PeerExchange, RecordExchange, flare_mixer_context_parallel, shard_bounds
         from oracle import flare_oracle as O
+        ex = PeerExchange() if exchange == "peer" else RecordExchange()
         for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
             B, H, N, M, D, scale = 2, 4, 1500, 64, 32, 0.9
             q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=7)
@@ -41,7 +42,7 @@ def _worker(rank, world, port, q_out):
             qd = q.to(dev).requires_grad_(True)
             kd = k[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
             vd = v[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
-            y = flare_mixer_context_parallel(qd, kd, vd, scale)
+            y = flare_mixer_context_parallel(qd, kd, vd, scale, exchange=ex)
             y.backward(dy[:, :, n0:n1].contiguous().to(dev))
             torch.cuda.synchronize()
             qf, kf, vf, dyf = (t.float() for t in (q, k, v, dy))
@@ -59,13 +60,13 @@ def _worker(rank, world, port, q_out):
         dist.destroy_process_group()
 
 
-def _run(world):
+def _run(world, exchange="nccl"):
     import __graft_entry__
     __graft_entry__.build()
     ctx = mp.get_context("spawn")
     q_out = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q_out, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q_out.get(timeout=300) for _ in procs]
@@ -82,3 +83,10 @@ def test_two_ranks_shard_the_tokens(cuda_dev):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(2)
+
+
+def test_two_ranks_peer_memory_exchange(cuda_dev):
+    """The exchanges fused into the combine / reduce kernels over symmetric memory (plain peer loads)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, "peer")
