@@ -21,7 +21,6 @@ import ctypes as C
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -55,48 +54,52 @@ def peaks():
 # clocks sampled while the timed region runs
 # ----------------------------------------------------------------------------------
 class ClockSampler:
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, polled through NVML every ~2 ms from a thread while the timed
+    region runs (the timed region is tens of milliseconds: nvidia-smi's own loop is too coarse for it).
+    Reading only; nothing is set."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.sm, self.mask, self.max_mhz = index, [], 0, None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nv = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
             return
-        threading.Thread(target=self._read, daemon=True).start()
+        self._thread = threading.Thread(target=self._poll, daemon=True)
+        self._thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _poll(self):
+        nv = self._nv
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                if get_reasons:
+                    self.mask |= int(get_reasons(self._h))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def stop(self):
-        if not self.proc:
+        if not self._thread:
             return None
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            try:
-                sm.append(float(r[1])); mx.append(float(r[2]))
-            except (ValueError, IndexError):
-                continue
-            for n, v in zip(names, r[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
+        self._stop.set()
+        self._thread.join(timeout=2)
+        if not self.sm:
             return None
-        return dict(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        reasons = sorted(n for bit, n in self.REASONS.items() if self.mask & bit)
+        return dict(sm_mhz=statistics.median(self.sm), sm_max_mhz=self.max_mhz, reasons=reasons, samples=len(self.sm))
 
 
 # ----------------------------------------------------------------------------------
@@ -267,10 +270,21 @@ def run_ours(args):
 
     # N > 1: the exchanges go through symmetric memory and peer loads (FLARE_CP_EXCHANGE=nccl selects the
     # torch.distributed collectives instead)
-    cp_ex = None
+    cp_ex, cp_kind = None, None
     if world > 1:
         from flare_b200.parallel import PeerExchange, RecordExchange
-        cp_ex = RecordExchange() if os.environ.get("FLARE_CP_EXCHANGE", "peer") == "nccl" else PeerExchange()
+        cp_kind = os.environ.get("FLARE_CP_EXCHANGE", "peer")
+        if cp_kind == "peer":
+            try:
+                cp_ex = PeerExchange()
+                cp_ex.exchange_buffer("probe", (16,), dev)      # forces the symmetric-memory rendezvous now
+            except Exception as e:                              # no symmetric memory on this box: NCCL collectives
+                print(f"[bench] peer-memory exchange unavailable ({e!r}); using NCCL", file=sys.stderr, flush=True)
+                cp_kind, cp_ex = "nccl", None
+        ok = torch.tensor([1 if cp_kind == "peer" else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)               # all ranks must agree
+        if ok.item() == 0:
+            cp_kind, cp_ex = "nccl", RecordExchange()
 
     def mixer(q_, k_, v_):
         if world > 1:
@@ -408,7 +422,8 @@ def run_ours(args):
             ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
             data="synthetic",
             config=dict(workload=f"mixer_1M: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd",
-                        parallelism=("single GPU" if world == 1 else f"context parallel, N sharded over {world} ranks"),
+                        parallelism=("single GPU" if world == 1 else
+                                     f"context parallel, N sharded over {world} ranks, exchange={cp_kind}"),
                         tokens_per_rank=Nl, l2="inputs larger than L2 (K,V,dY,Y,dK,dV 64 B x tokens x heads each); no flush",
                         kernel_path="tcgen05 (decoupled gather/scatter/dZ, pipelined one-exponential backward behind an on-device range check); fp32 SIMT reductions"),
             clocks=clocks,
