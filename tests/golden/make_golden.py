@@ -167,7 +167,9 @@ def triton_ref_cases(root: Path):
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of a FLARE.py checkout>")
+    root = Path(sys.argv[1])
     ref = _load(root / "pdebench/models/flare.py", "_ref_pde_flare")
     pkg = types.ModuleType("_ref_lra_models")
     pkg.__path__ = [str(root / "lra/models")]
