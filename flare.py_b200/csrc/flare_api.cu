@@ -186,8 +186,8 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (!z32) return fail(FLARE_EINVAL, "z32 is null");
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
-  if (g_path.load() != FLARE_PATH_SIMT && tc_scatter_supported(c, p->dtype)) {
-    const int rc = (tc_scatter2_supported(c, p->dtype) && !getenv("FLARE_SCATTER_V1"))
+  if (g_path.load() != FLARE_PATH_SIMT && (tc_scatter_supported(c, p->dtype) || tc_scatter2_supported(c, p->dtype))) {
+    const int rc = (tc_scatter2_supported(c, p->dtype) && (c.M > 256 || !getenv("FLARE_SCATTER_V1")))
                        ? tc_scatter2(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream)
                        : tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
     if (rc == FLARE_OK) return after_launch("scatter (tcgen05)");

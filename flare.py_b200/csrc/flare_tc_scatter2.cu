@@ -34,6 +34,8 @@ struct Scatter2Args {
   __nv_bfloat16* y;
   long long ys[3];
   float* lse_n;                // [B,H,N] or null
+  long long z_bh_stride;       // floats between the z32 blocks of consecutive (b, h)
+  int accumulate;              // 1: merge with the y / lse_n a previous latent block left (log-sum-exp weights)
   int* status;
 };
 
@@ -110,7 +112,7 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
 
   // Z of this (b, h) as bf16 in the swizzled operand layout (rows past M are never read)
   {
-    const float* zb = a.z32 + ((long long)b * a.H + h) * M * D;
+    const float* zb = a.z32 + ((long long)b * a.H + h) * a.z_bh_stride;
     constexpr int CPR = ROWB / 16;
     for (int i = tid; i < M * CPR; i += blockDim.x) {
       const int r = i / CPR, c = i % CPR;
@@ -254,18 +256,40 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
       const int tok = n0 + t * 128 + row;
       if (tok < n1) {
         const bool keep = !a.mask || a.mask[(long long)b * a.N + tok];
-        const float inv = keep ? 1.f / sum : 0.f;
+        float inv = keep ? 1.f / sum : 0.f;
+        float c_new = (rmax * sl + log2f(sum)) * kLn2;
         __nv_bfloat16* yp = a.y + b * a.ys[0] + h * a.ys[1] + (long long)tok * a.ys[2];
+        float w_old = 0.f;
+        if (a.accumulate) {
+          // this launch covers one block of the latents: y = w_old y_old + w_new y_block, C = logaddexp
+          const float c_old = a.lse_n[((long long)b * a.H + h) * a.N + tok];
+          const float cm = fmaxf(c_old, c_new);
+          const float e_old = __expf(c_old - cm), e_new = __expf(c_new - cm);
+          const float tot = e_old + e_new;
+          w_old = e_old / tot;
+          inv *= e_new / tot;
+          c_new = cm + __logf(tot);
+        }
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * c + j]) * inv;
+          if (a.accumulate) {
+            const uint4 old = reinterpret_cast<const uint4*>(yp)[c];
+            const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 of = __bfloat1622float2(op[j]);
+              f[2 * j] = fmaf(w_old, of.x, f[2 * j]); f[2 * j + 1] = fmaf(w_old, of.y, f[2 * j + 1]);
+            }
+          }
           uint4 o;
-          o.x = pack_bf16(__uint_as_float(r[8 * c]) * inv, __uint_as_float(r[8 * c + 1]) * inv);
-          o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * inv, __uint_as_float(r[8 * c + 3]) * inv);
-          o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * inv, __uint_as_float(r[8 * c + 5]) * inv);
-          o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * inv, __uint_as_float(r[8 * c + 7]) * inv);
+          o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+          o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
           reinterpret_cast<uint4*>(yp)[c] = o;
         }
-        if (a.lse_n) a.lse_n[((long long)b * a.H + h) * a.N + tok] = (rmax * sl + log2f(sum)) * kLn2;
+        if (a.lse_n) a.lse_n[((long long)b * a.H + h) * a.N + tok] = c_new;
       }
     }
   }
@@ -276,21 +300,20 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
 
 // ------------------------------------------------------------------------------------------
 bool tc_scatter2_supported(const Ctx& c, int dtype) {
-  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.M >= 32 && c.M <= 256 && c.M % 32 == 0 && c.N >= 1;
+  // more than 256 latents run as blocks of 256, each launch merging into y and C_n (needs C_n storage)
+  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.M >= 32 && c.M <= 1024 && c.M % 32 == 0 && c.N >= 1;
 }
 
 template <int D>
 static int launch_scatter2(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask,
                            void* y, float* lse_n, cudaStream_t st) {
-  CUtensorMap tmK, tmQ;
+  CUtensorMap tmK;
   const uint64_t e = 2;
+  if (c.M > 256 && !lse_n) return FLARE_EUNSUPPORTED;
   if (!make_tile_map(&tmK, k, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
                      (c.B > 1 ? c.ks[0] : c.ks[1] * c.H) * e, 128))
     return FLARE_EUNSUPPORTED;
   const bool qb = c.qs[0] != 0;
-  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e,
-                     c.qs[1] * e, (qb ? c.qs[0] : c.qs[1] * c.H) * e, (uint32_t)c.M))
-    return FLARE_EUNSUPPORTED;
   // token ranges: two CTAs' worth of work per SM
   const long long bh = (long long)c.B * c.H;
   long long splits = (2LL * num_sms() + bh - 1) / bh;
@@ -300,11 +323,12 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
   const long long chunk = ((tiles + splits - 1) / splits) * 128;
   splits = (c.N + chunk - 1) / chunk;
   Scatter2Args a;
-  a.B = c.B; a.H = c.H; a.N = c.N; a.M = c.M;
+  a.B = c.B; a.H = c.H; a.N = c.N;
   a.scale_log2 = c.scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
   a.n_splits = (int)splits; a.chunk = (int)chunk;
-  a.z32 = z32; a.mask = mask; a.y = reinterpret_cast<__nv_bfloat16*>(y);
+  a.mask = mask; a.y = reinterpret_cast<__nv_bfloat16*>(y);
+  a.z_bh_stride = (long long)c.M * D;
   for (int i = 0; i < 3; ++i) a.ys[i] = c.ys[i];
   a.lse_n = lse_n;
   a.status = tc_status_ptr();
@@ -317,7 +341,18 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
   }
   const long long grid = splits * bh;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_scatter2<D><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+  for (int m0 = 0; m0 < c.M; m0 += 256) {
+    const int mb = c.M - m0 < 256 ? c.M - m0 : 256;
+    CUtensorMap tmQ;
+    const char* qblk = static_cast<const char*>(q) + (long long)m0 * c.qs[2] * e;
+    if (!make_tile_map(&tmQ, qblk, 1, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e,
+                       c.qs[1] * e, (qb ? c.qs[0] : c.qs[1] * c.H) * e, (uint32_t)mb))
+      return FLARE_EUNSUPPORTED;
+    a.M = mb;
+    a.z32 = z32 + (long long)m0 * D;
+    a.accumulate = m0 > 0 ? 1 : 0;
+    k_tc_scatter2<D><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+  }
   return FLARE_OK;
 }
 

@@ -63,6 +63,8 @@ def test_golden_masked_lra(fb, cuda_dev):
     (1, 2, 515, 48, 64, 0.5),
     (1, 1, 300, 24, 128, 0.25),
     (1, 4, 2048, 256, 32, 1.0),         # latent count and head dim of the headline case
+    (1, 2, 1500, 512, 32, 1.0),         # more than 256 latents: blocks of 256 merged by log-sum-exp
+    (2, 1, 700, 320, 32, 0.7),          # a full block and a 64-latent one
 ])
 def test_parity_fwd_bwd(fb, cuda_dev, path, dtype, B, H, N, M, D, scale):
     q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=N + M)
