@@ -341,6 +341,32 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
     if (rc == FLARE_OK) return after_launch("bwd_main (tcgen05)");
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_main (tcgen05): launch setup failed");
   }
+  // More than 256 latents: the one-exponential kernel in blocks of 256.  The exact kernel that takes over
+  // flagged (b, h) has no blocked form, so the flags are read back (one small copy and a stream
+  // synchronisation per call, this shape only) and a flagged problem goes to the fp32 kernels below.
+  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && c.M > 256 && tc_bwd4_supported(c, p->dtype) && delta_n &&
+      !getenv("FLARE_BWD3") && !getenv("FLARE_NO_PIPELINE") &&
+      (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 && z32 && dz32 && lse_m && lse_n &&
+      (size_t)p->B * p->H * (size_t)p->N * sizeof(float) >= tc_bwd2_scratch_bytes(c) && p->B * p->H <= 4096 &&
+      check_tok("q", q, p->q_stride, p->dtype) == FLARE_OK && check_tok("k", k, p->k_stride, p->dtype) == FLARE_OK &&
+      check_tok("v", v, p->v_stride, p->dtype) == FLARE_OK && check_tok("dy", dy, p->dy_stride, p->dtype) == FLARE_OK &&
+      check_tok("y", y, p->y_stride, p->dtype) == FLARE_OK && check_tok("dk", dk, p->dk_stride, p->dtype) == FLARE_OK &&
+      check_tok("dv", dv, p->dv_stride, p->dtype) == FLARE_OK) {
+    const int* flag = nullptr;
+    int rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
+    if (rc == FLARE_OK) {
+      static int host_flags[4096];
+      const int nbh = p->B * p->H;
+      if (cudaMemcpyAsync(host_flags, flag, nbh * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+          cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)
+        return fail(FLARE_ECUDA, "bwd_main: reading the range flags failed");
+      bool flagged = false;
+      for (int i = 0; i < nbh; ++i) flagged |= host_flags[i] != 0;
+      if (!flagged) return after_launch("bwd_main (tcgen05, latent blocks)");
+    } else if (rc != FLARE_EUNSUPPORTED) {
+      return fail(rc, "bwd_main (tcgen05, latent blocks): launch setup failed");
+    }
+  }
   if ((terms & FLARE_TERM_SCATTER) && !delta_n) return fail(FLARE_EINVAL, "bwd_main: delta_n scratch is null");
   TRY(flare_bwd_tokens(p, terms, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta_n, stream));
   TRY(flare_bwd_dq_partial(p, terms, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part, stream));

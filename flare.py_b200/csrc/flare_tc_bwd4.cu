@@ -47,7 +47,9 @@ struct Bwd4Args {
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
   long long dks[3], dvs[3];
-  float* dq_part;              // [S,B,H,M,D]
+  float* dq_part;              // [S,B,H,M_total,D]
+  int M_total, m0;             // this launch covers latents [m0, m0 + M) of M_total
+  int accumulate;              // 1: add to the dK/dV an earlier latent block wrote
   int* status;
 };
 
@@ -119,7 +121,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   const int n0 = split * a.chunk, n1 = min(a.N, n0 + a.chunk);
   const int n_tiles = n1 > n0 ? (n1 - n0 + 127) / 128 : 0;
   const int U = n_tiles * n_sub;                   // steps
-  float* dq_out = a.dq_part + (((long long)split * a.B + b) * a.H + h) * M * D;
+  float* dq_out = a.dq_part + ((((long long)split * a.B + b) * a.H + h) * a.M_total + a.m0) * D;
 
   if (n_tiles == 0) {
     for (int i = tid; i < M * D; i += blockDim.x) dq_out[i] = 0.f;
@@ -167,7 +169,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   const float mu = a.mu[bh];
   // resident latent operands of B': dZ, eL*Z and the extension columns
   {
-    const long long lrow = ((long long)b * a.H + h) * M;
+    const long long lrow = ((long long)b * a.H + h) * a.M_total + a.m0;
     const float* zb = a.z32 + lrow * D;
     const float* dzb = a.dz32 + lrow * D;
     for (int i = tid; i < 256 * CPR; i += blockDim.x) {
@@ -318,11 +320,21 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     for (int pc = 0; pc < 2; ++pc) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
+        float g[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] = __uint_as_float(r[pc][8 * c + j]) * f;
+        if (a.accumulate) {                        // a later latent block: add to what the earlier ones wrote
+          const uint4 old = reinterpret_cast<const uint4*>(op + 16 * pc)[c];
+          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 of = __bfloat1622float2(o2[j]);
+            g[2 * j] += of.x; g[2 * j + 1] += of.y;
+          }
+        }
         uint4 o;
-        o.x = pack_bf16(__uint_as_float(r[pc][8 * c]) * f, __uint_as_float(r[pc][8 * c + 1]) * f);
-        o.y = pack_bf16(__uint_as_float(r[pc][8 * c + 2]) * f, __uint_as_float(r[pc][8 * c + 3]) * f);
-        o.z = pack_bf16(__uint_as_float(r[pc][8 * c + 4]) * f, __uint_as_float(r[pc][8 * c + 5]) * f);
-        o.w = pack_bf16(__uint_as_float(r[pc][8 * c + 6]) * f, __uint_as_float(r[pc][8 * c + 7]) * f);
+        o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]);
+        o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
         reinterpret_cast<uint4*>(op + 16 * pc)[c] = o;
       }
     }
@@ -593,26 +605,24 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
 // ------------------------------------------------------------------------------------------
 bool tc_bwd4_supported(const Ctx& c, int dtype) {
-  return dtype == FLARE_BF16 && c.D == 32 && c.M >= 32 && c.M <= 256 && c.N >= 1 && c.terms == FLARE_TERM_BOTH;
+  // more than 256 latents run as blocks of 256 that add into dK/dV
+  return dtype == FLARE_BF16 && c.D == 32 && c.M >= 32 && c.M <= 1024 && c.N >= 1 && c.terms == FLARE_TERM_BOTH;
 }
 
 int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                    const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* dq_part, const float* mu, const int* flag, cudaStream_t st) {
   constexpr int D = 32;
-  CUtensorMap tmQ, tmK, tmV, tmG;
+  CUtensorMap tmK, tmV, tmG;
   const uint64_t e = 2;
   const bool qb = c.qs[0] != 0;
   auto tokmap = [&](CUtensorMap* m, const void* p, const long long* s) {
     return make_tile_map(m, p, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, s[2] * e, s[1] * e,
                          (c.B > 1 ? s[0] : s[1] * c.H) * e, 128);
   };
-  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
-                     (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256) ||
-      !tokmap(&tmK, k, c.ks) || !tokmap(&tmV, v, c.vs) || !tokmap(&tmG, dy, c.dys))
-    return FLARE_EUNSUPPORTED;
+  if (!tokmap(&tmK, k, c.ks) || !tokmap(&tmV, v, c.vs) || !tokmap(&tmG, dy, c.dys)) return FLARE_EUNSUPPORTED;
   Bwd4Args a;
-  a.B = c.B; a.H = c.H; a.N = c.N; a.M = c.M;
+  a.B = c.B; a.H = c.H; a.N = c.N; a.M_total = c.M;
   a.scale = c.scale; a.scale_log2 = c.scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
   a.n_splits = c.n_splits; a.chunk = c.chunk;
@@ -632,7 +642,16 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   }
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_bwd4<<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+  for (int m0 = 0; m0 < c.M; m0 += 256) {
+    const int mb = c.M - m0 < 256 ? c.M - m0 : 256;
+    CUtensorMap tmQ;
+    const char* qblk = static_cast<const char*>(q) + (long long)m0 * c.qs[2] * e;
+    if (!make_tile_map(&tmQ, qblk, 1, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
+                       (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
+      return FLARE_EUNSUPPORTED;
+    a.M = mb; a.m0 = m0; a.accumulate = m0 > 0 ? 1 : 0;
+    k_tc_bwd4<<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+  }
   return FLARE_OK;
 }
 
