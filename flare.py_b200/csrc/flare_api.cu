@@ -355,7 +355,7 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
     const int* flag = nullptr;
     int rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
     if (rc == FLARE_OK) {
-      static int host_flags[4096];
+      int host_flags[4096];
       const int nbh = p->B * p->H;
       if (cudaMemcpyAsync(host_flags, flag, nbh * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
           cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)

@@ -230,3 +230,13 @@ def test_large_scores_are_stable(fb, cuda_dev):
     q, k, v, dy = O.make_inputs(1, 2, 700, 32, 16, seed=8)
     got = run_mixer(fb, q * 6, k * 6, v, dy, 1.0, cuda_dev)
     assert_close(got, oracle_all(q * 6, k * 6, v, dy, 1.0), 2e-5)
+
+
+@pytest.mark.parametrize("M", [256, 512])
+def test_wide_score_range_takes_the_exact_path(fb, cuda_dev, M):
+    """bf16 logits of magnitude ~60: the on-device range check rejects the one-exponential backward; at
+    M = 256 the exact tensor-core kernel takes over, above 256 latents the fp32 kernels do."""
+    q, k, v, dy = O.make_inputs(1, 2, 900, M, 32, dtype=torch.bfloat16, seed=21)
+    q, k = (q.float() * 4).bfloat16(), (k.float() * 4).bfloat16()
+    got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev)
+    assert_close(got, oracle_all(q, k, v, dy, 1.0), 2e-2)
