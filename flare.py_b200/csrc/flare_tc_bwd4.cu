@@ -49,7 +49,6 @@ struct Bwd4Args {
   long long dks[3], dvs[3];
   float* dq_part;              // [S,B,H,M_total,D]
   int M_total, m0;             // this launch covers latents [m0, m0 + M) of M_total
-  int accumulate;              // 1: add to the dK/dV an earlier latent block wrote
   int* status;
 };
 
@@ -74,6 +73,7 @@ __device__ __forceinline__ void mbar_arrive4(uint64_t* bar) {
 
 constexpr int kB4Softmax = 512, kB4Helpers = 96;   // + the issuer warp
 
+template <bool ACC>                               // ACC: add to the dK/dV an earlier latent block wrote
 __global__ void __launch_bounds__(kB4Softmax + kB4Helpers + 32, 1)
 k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, Bwd4Args a) {
@@ -323,7 +323,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         float g[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) g[j] = __uint_as_float(r[pc][8 * c + j]) * f;
-        if (a.accumulate) {                        // a later latent block: add to what the earlier ones wrote
+        if constexpr (ACC) {                       // a later latent block: add to what the earlier ones wrote
           const uint4 old = reinterpret_cast<const uint4*>(op + 16 * pc)[c];
           const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
 #pragma unroll
@@ -636,7 +636,8 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   static bool attr_done = false;
   constexpr int smem = Bwd4Smem::kBytes;
   if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_bwd4, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(k_tc_bwd4<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(k_tc_bwd4<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return FLARE_ECUDA;
     attr_done = true;
   }
@@ -649,8 +650,9 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
     if (!make_tile_map(&tmQ, qblk, 1, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
                        (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
       return FLARE_EUNSUPPORTED;
-    a.M = mb; a.m0 = m0; a.accumulate = m0 > 0 ? 1 : 0;
-    k_tc_bwd4<<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+    a.M = mb; a.m0 = m0;
+    if (m0 == 0) k_tc_bwd4<false><<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+    else k_tc_bwd4<true><<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
   }
   return FLARE_OK;
 }
