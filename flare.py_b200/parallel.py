@@ -17,7 +17,7 @@ gloo in the CPU tests), so that the plumbing can be exercised without a GPU.
 consumes it: every rank writes its record (or partial sum) into a symmetric-memory
 buffer, a barrier on the stream orders the writes, and the combine / reduce kernel
 reads all ranks' buffers through peer pointers with plain loads over NVLink
-(``flare_combine_peers``, ``flare_reduce_sum_peers``).  No multicast, no waiting
+(``flare_combine_peers``, ``flare_reduce_sum_peers``).  Ordinary loads only, no waiting
 inside the library's kernels.
 """
 from __future__ import annotations
