@@ -94,3 +94,27 @@ def test_unsupported_shape_is_refused(cuda_dev):
     q, k, v = _inputs(1, 1, 16, 520, 64, torch.float32)
     with pytest.raises(Exception):
         fb.flare_causal_prefill(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), 1.0)
+
+
+def test_serving_shape_split_prefill(cuda_dev):
+    """B=4, H=16, N=8192, D=64, M=128 bf16 (too large for the CPU oracle): prefilling the prompt in two pieces
+    with the carried record, and decoding its last tokens one by one, give what one prefill gives."""
+    import flare_b200 as fb
+    B, H, N, M, D = 4, 16, 8192, 128, 64
+    g = torch.Generator().manual_seed(31)
+    q = (torch.randn(H, M, D, generator=g) * D ** -0.25).bfloat16().to(cuda_dev)
+    k = (torch.randn(B, H, N, D, generator=g) * D ** -0.25).bfloat16().to(cuda_dev)
+    v = torch.randn(B, H, N, D, generator=g).bfloat16().to(cuda_dev)
+    y_all, st_all = fb.flare_causal_prefill(q, k, v, 1.0)
+    n0 = 5000                                            # not a multiple of the chunk
+    y0, st = fb.flare_causal_prefill(q, k[:, :, :n0], v[:, :, :n0], 1.0)
+    y1, st = fb.flare_causal_prefill(q, k[:, :, n0:N - 16], v[:, :, n0:N - 16], 1.0, state=st)
+    ys = [y0, y1]
+    for t in range(N - 16, N):
+        ys.append(fb.flare_causal_decode(q, k[:, :, t:t + 1], v[:, :, t:t + 1], st, 1.0))
+    y_inc = torch.cat(ys, dim=2)
+    err = ((y_inc.float() - y_all.float()).norm() / y_all.float().norm()).item()
+    assert err <= 2e-2, err
+    z_a = st_all[..., :D] / st_all[..., D + 1:D + 2]
+    z_b = st[..., :D] / st[..., D + 1:D + 2]
+    assert ((z_a - z_b).norm() / z_a.norm()).item() <= 2e-2

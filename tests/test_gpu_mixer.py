@@ -240,3 +240,41 @@ def test_wide_score_range_takes_the_exact_path(fb, cuda_dev, M):
     q, k = (q.float() * 4).bfloat16(), (k.float() * 4).bfloat16()
     got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev)
     assert_close(got, oracle_all(q, k, v, dy, 1.0), 2e-2)
+
+
+def test_full_size_properties(fb, cuda_dev):
+    """The benchmark's own size (B=1, H=8, N=2^20, M=256, D=32, bf16), where the CPU oracle is out of reach:
+    (1) the tensor-core path agrees with the fp32 kernels (themselves checked against the oracle above);
+    (2) the backward is linear in dy: doubling dy doubles every gradient bit for bit (powers of two scale
+        exactly through every product, sum and bf16 rounding of the path)."""
+    B, H, N, M, D = 1, 8, 1 << 20, 256, 32
+    g = torch.Generator(device="cpu").manual_seed(99)
+    sd = D ** -0.25
+    q = (torch.randn(H, M, D, generator=g) * sd).bfloat16().to(cuda_dev)
+    k = (torch.randn(B, H, N, D, generator=g) * sd).bfloat16().to(cuda_dev)
+    v = (torch.randn(B, H, N, D, generator=g) * sd).bfloat16().to(cuda_dev)
+    dy = torch.randn(B, H, N, D, generator=g).bfloat16().to(cuda_dev)
+
+    def run(path, dy_):
+        prev = fb.set_kernel_path(path)
+        try:
+            qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+            y = fb.flare_multihead_mixer(qd, kd, vd)
+            y.backward(dy_)
+            torch.cuda.synchronize()
+            return y.detach(), qd.grad, kd.grad, vd.grad
+        finally:
+            fb.set_kernel_path(prev)
+
+    def rel(a, b):
+        a, b = a.float(), b.float()
+        return ((a - b).norm() / b.norm()).item()
+
+    tc = run("auto", dy)
+    ref = run("simt", dy)
+    errs = {n: rel(a, b) for n, a, b in zip(("y", "dq", "dk", "dv"), tc, ref)}
+    assert all(e <= 2e-2 for e in errs.values()), errs
+    tc2 = run("auto", dy * 2)
+    assert torch.equal(tc2[0], tc[0])
+    for n, a, b in zip(("dq", "dk", "dv"), tc2[1:], tc[1:]):
+        assert torch.equal(a.float(), b.float() * 2), n
