@@ -522,8 +522,8 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       uint32_t ra[16], rb[16];
       float p[32];
       tmem_ld16(buf, ra);
-      tmem_wait_ld();
       tmem_ld16(buf + 16, rb);
+      tmem_wait_ld();
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float4 l4 = *reinterpret_cast<const float4*>(l2p + 4 * e);
