@@ -89,15 +89,17 @@ k_triple_outer(const T* __restrict__ A, const T* __restrict__ Bm, const T* __res
 
 constexpr int kCThreads = 256;
 
-template <typename T, int DZ>
+// NT tokens per lane (tokens lane, lane + 32, ...): every 16-byte load of T feeds 4 NT multiply-adds.
+template <typename T, int DZ, int NT>
 __global__ void __launch_bounds__(kCThreads)
 k_triple_contract(const float* __restrict__ Tn, long long sx, long long sy, long long sz, int Dx, int Dy, int xb,
                   const T* __restrict__ A, const T* __restrict__ Bm, int N, int chunk, float alpha, T* __restrict__ out) {
+  constexpr int TT = kTok * NT;                    // tokens per tile
   extern __shared__ __align__(16) float sm[];
   const int DyP = Dy + 1, xbP = xb + 1;
   float* sT = sm;                                  // [xb][Dy][DZ]
-  float* sAt = sT + (size_t)xb * Dy * DZ;          // [kTok][DyP]
-  float* sO = sAt + kTok * DyP;                    // [kTok][xbP]
+  float* sAt = sT + (size_t)xb * Dy * DZ;          // [TT][DyP]
+  float* sO = sAt + TT * DyP;                      // [TT][xbP]
   const int x0 = blockIdx.x * xb, bh = blockIdx.z;
   const int nx = min(xb, Dx - x0);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -110,34 +112,47 @@ k_triple_contract(const float* __restrict__ Tn, long long sx, long long sy, long
   const T* b = Bm + (long long)bh * N * DZ;
   T* o = out + (long long)bh * N * Dx;
   const int n0 = blockIdx.y * chunk, n1 = min(N, n0 + chunk);
-  for (int t0 = n0; t0 < n1; t0 += kTok) {
-    const int cnt = min(kTok, n1 - t0);
+  for (int t0 = n0; t0 < n1; t0 += TT) {
+    const int cnt = min(TT, n1 - t0);
     __syncthreads();
     for (int e = threadIdx.x; e < cnt * Dy; e += kCThreads) sAt[(e / Dy) * DyP + e % Dy] = to_f32(a[(long long)t0 * Dy + e]);
-    float bn[DZ];
-    if (lane < cnt) {
+    float bn[NT][DZ];
 #pragma unroll
-      for (int z = 0; z < DZ; ++z) bn[z] = to_f32(b[(long long)(t0 + lane) * DZ + z]);
-    } else {
+    for (int q = 0; q < NT; ++q) {
+      const int n = lane + 32 * q;
+      if (n < cnt) {
 #pragma unroll
-      for (int z = 0; z < DZ; ++z) bn[z] = 0.f;
+        for (int z = 0; z < DZ; ++z) bn[q][z] = to_f32(b[(long long)(t0 + n) * DZ + z]);
+      } else {
+#pragma unroll
+        for (int z = 0; z < DZ; ++z) bn[q][z] = 0.f;
+      }
     }
     __syncthreads();
     for (int x = warp; x < nx; x += kCThreads / 32) {
-      float ox = 0.f;
+      float ox[NT];
+#pragma unroll
+      for (int q = 0; q < NT; ++q) ox[q] = 0.f;
       const float* tx = sT + (size_t)x * Dy * DZ;
       for (int y = 0; y < Dy; ++y) {
         const float4* tr = reinterpret_cast<const float4*>(tx + y * DZ);
-        float t = 0.f;
+        float t[NT];
+#pragma unroll
+        for (int q = 0; q < NT; ++q) t[q] = 0.f;
 #pragma unroll
         for (int z = 0; z < DZ / 4; ++z) {
           const float4 t4 = tr[z];
-          t = fmaf(t4.x, bn[4 * z], t); t = fmaf(t4.y, bn[4 * z + 1], t);
-          t = fmaf(t4.z, bn[4 * z + 2], t); t = fmaf(t4.w, bn[4 * z + 3], t);
+#pragma unroll
+          for (int q = 0; q < NT; ++q) {
+            t[q] = fmaf(t4.x, bn[q][4 * z], t[q]); t[q] = fmaf(t4.y, bn[q][4 * z + 1], t[q]);
+            t[q] = fmaf(t4.z, bn[q][4 * z + 2], t[q]); t[q] = fmaf(t4.w, bn[q][4 * z + 3], t[q]);
+          }
         }
-        ox = fmaf(sAt[lane * DyP + y], t, ox);
+#pragma unroll
+        for (int q = 0; q < NT; ++q) ox[q] = fmaf(sAt[(lane + 32 * q) * DyP + y], t[q], ox[q]);
       }
-      sO[lane * xbP + x] = ox * alpha;
+#pragma unroll
+      for (int q = 0; q < NT; ++q) sO[(lane + 32 * q) * xbP + x] = ox[q] * alpha;
     }
     __syncthreads();
     for (int e = threadIdx.x; e < cnt * nx; e += kCThreads) {
@@ -193,12 +208,14 @@ int launch_contract(int BH, int N, int Dx, int Dy, const float* t, long long sx,
   if (chunks > maxc) chunks = maxc;
   if (chunks < 1) chunks = 1;
   if (chunks > 65535) chunks = 65535;
-  const int chunk = (int)(((N + chunks - 1) / chunks + kTok - 1) / kTok * kTok);
+  constexpr int NT = DZ <= 32 ? 2 : 1;             // tokens per lane: registers allow two up to DZ = 32
+  constexpr int TT = kTok * NT;
+  const int chunk = (int)(((N + chunks - 1) / chunks + TT - 1) / TT * TT);
   const int nch = (N + chunk - 1) / chunk;
-  const size_t smem = sizeof(float) * ((size_t)xb * Dy * DZ + kTok * (Dy + 1) + kTok * (xb + 1));
-  if (cudaFuncSetAttribute(k_triple_contract<T, DZ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+  const size_t smem = sizeof(float) * ((size_t)xb * Dy * DZ + TT * (Dy + 1) + TT * (xb + 1));
+  if (cudaFuncSetAttribute(k_triple_contract<T, DZ, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return refuse(FLARE_ECUDA, "triple_contract: cudaFuncSetAttribute failed (%zu bytes)", smem);
-  k_triple_contract<T, DZ><<<dim3((unsigned)nxb, (unsigned)nch, (unsigned)BH), kCThreads, smem, st>>>(
+  k_triple_contract<T, DZ, NT><<<dim3((unsigned)nxb, (unsigned)nch, (unsigned)BH), kCThreads, smem, st>>>(
       t, sx, sy, sz, Dx, Dy, xb, reinterpret_cast<const T*>(a), reinterpret_cast<const T*>(b), N, chunk, alpha,
       reinterpret_cast<T*>(out));
   const cudaError_t e = cudaPeekAtLastError();
