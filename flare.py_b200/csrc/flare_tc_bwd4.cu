@@ -15,9 +15,10 @@
 //
 //   two issuing warps, so that neither stream of products waits behind the other's instructions (a
 //   lone warp that shares its scheduler with busy softmax warps issues a product every ~45 clocks):
-//     warp 18: T'(u+1) as soon as the threads hold T'(u) in registers; S^T(u+2) once the dV/dK/dQ
-//              products of step u have completed (they read the buffer); the TMA loads
-//     warp 19: dV/dK/dQ products of step u once P/dS are written
+//     warp 18: T'(u+1) as soon as the threads hold T'(u) in registers; the TMA loads
+//     warp 19: once P/dS of step u are written: dV/dK(u), then S^T(u+2) into the buffer those just read
+//              (products issued by one thread execute in issue order: no completion round trip between
+//              them), then dQ(u)
 //   helper warps 16, 17: per-token operands of the next tile (eC*dY, the A' extension with delta_n),
 //   two token rows per thread.  dV/dK of finished tiles -> global: one lane quarter per warp 16-19.
 // Token tiles (K, V, dY) arrive by TMA in a three-stage ring; Y is read from global memory a tile
@@ -102,8 +103,8 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   uint64_t* bar_pd = bars + 7;                     // [2] P/dS of step u written (512 arrivals)
   uint64_t* bar_p2 = bars + 9;                     // [2] dV/dK/dQ products of step u complete
   uint64_t* bar_q = bars + 11;
-  uint64_t* bar_free = bars + 12;                  // dV/dK of a finished tile have been read (96 arrivals)
-  uint64_t* bar_tile = bars + 13;                  // every product of a tile is complete
+  uint64_t* bar_free = bars + 12;                  // dV/dK of a finished tile have been read (warps 16-19: 128 arrivals)
+  uint64_t* bar_tile = bars + 13;                  // the dV/dK products of a tile are complete
   uint64_t* bar_ge = bars + 14;                    // [2] every T' product of tile tau complete, on bar_ge[tau&1]
   uint64_t* bar_prep = bars + 16;                  // per-token operands of the next tile written (96 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
@@ -134,7 +135,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       mbar_init(&bar_s[i], 1); mbar_init(&bar_p2[i], 1); mbar_init(&bar_pd[i], kB4Softmax); mbar_init(&bar_ge[i], 1);
     }
     mbar_init(bar_t, 1); mbar_init(bar_tl, kB4Softmax);
-    mbar_init(bar_q, 1); mbar_init(bar_free, kB4Helpers); mbar_init(bar_tile, 1); mbar_init(bar_prep, 64);
+    mbar_init(bar_q, 1); mbar_init(bar_free, 128); mbar_init(bar_tile, 1); mbar_init(bar_prep, 64);
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmG);
@@ -282,7 +283,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   auto issue_s = [&](int u2, int stg, int s) {
     const uint32_t d = tmem + cS + 128 * (u2 & 1);
     const uint64_t aK = hi64 | (tok_lo + stg * (L::kStage >> 4)), bQ = hi64 | (q_lo + s * 512);
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < 2; ++kk) mma_ss(d, aK + 2 * kk, bQ + 2 * kk, id_n128, kk > 0);
   };
   // T' of the step (tile in stage stg, per-token buffers of parity par, latent block s)
@@ -291,26 +292,28 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     const uint64_t aV = hi64 | (tok_lo + stg * (L::kStage >> 4) + (L::kT >> 4)), aG = hi64 | (ge_lo + par * (L::kT >> 4)),
                    aX = hi32 | (xa_lo + par * (L::kExtA >> 4));
     const uint64_t bDZ = hi64 | (dz_lo + s * 512), bZe = hi64 | (ze_lo + s * 512), bX = hi32 | (xb_lo + s * 256);
-    // rolled on purpose: the issuing warp runs this once per step between long waits, and a short
-    // loop body stays in the instruction cache where an unrolled sequence has to be fetched again
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < 2; ++kk) mma_ss(d, aV + 2 * kk, bDZ + 2 * kk, id_n128, kk > 0);
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < 2; ++kk) mma_ss(d, aG + 2 * kk, bZe + 2 * kk, id_n128, true);
     mma_ss(d, aX, bX, id_n128, true);
   };
-  // dV += P^T dZ_s, dK += dS^T Q_s, dQ_s += dS K_t  (P at +32(kk/2)+8(kk%2) of the step's buffer, dS 16 further)
-  auto issue_p2 = [&](int u, int stg, int t, int s) {
+  // dV += P^T dZ_s, dK += dS^T Q_s  (P at +32(kk/2)+8(kk%2) of the step's buffer, dS 16 further): the
+  // products that read the S^T buffer
+  auto issue_dvdk = [&](int u, int s) {
     const uint32_t buf = tmem + cS + 128 * (u & 1);
     const uint64_t bDZ = hi64 | (dz_lo + s * 512), bQ = hi64 | (q_lo + s * 512);
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < 8; ++kk) {
       const uint32_t pa = buf + 32 * (kk >> 1) + 8 * (kk & 1);
       mma_ts(tmem + cDV, pa, bDZ + 64 * kk, id_tv, (s > 0) || (kk > 0));
       mma_ts(tmem + cDK, pa + 16, bQ + 64 * kk, id_tv, (s > 0) || (kk > 0));
     }
+  };
+  // dQ_s += dS K_t  (dS from shared memory)
+  auto issue_dq = [&](int u, int stg, int t, int s) {
     const uint64_t bK = hi64 | (tok_lo + stg * (L::kStage >> 4)), aDS = himn | (ds_lo + (u & 1) * (L::kDS >> 4));
-#pragma unroll 1
+#pragma unroll
     for (int kk = 0; kk < 8; ++kk)
       mma_ss(tmem + cDQ + 32 * s, aDS + 128 * kk, bK + 64 * kk, id_dq, (t > 0) || (kk > 0));
   };
@@ -352,8 +355,8 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   __syncthreads();
 
   // One lane quarter of dV/dK of finished tile t: dV first (read, write out), then dK, so that only half
-  // of the values sit in registers at a time.  `before_dk_write` runs once both have been read.
-  auto store_quarter = [&](int t, auto&& before_dk_write) {
+  // of the values sit in registers at a time.
+  auto store_quarter = [&](int t) {
     const int n = n0 + t * 128 + row;
     {
       uint32_t r[2][16];
@@ -368,7 +371,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       tmem_ld16(lane_base + cDK + 16, r[1]);
       tmem_wait_ld();
       tc_fence_before();
-      before_dk_write();
+      mbar_arrive4(bar_free);
       if (n < n1) write_half(a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2], r, a.scale);
     }
   };
@@ -415,68 +418,54 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         }
         __syncwarp();
       }
-      // Once the dV/dK/dQ products of step u have completed, its buffer takes S^T(u+2); after the last
-      // step of a tile the tile's token stage is free for the tile three further on and its dV/dK
-      // accumulators can be read out.
-      const bool last = s == n_sub - 1;
-      const bool reload = last && (t + 3 < n_tiles);
-      if (u + 2 < U || last) {
-        mbar_wait_hot(&bar_p2[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
+      // After the last step of a tile: its dV/dK accumulators are read out once their products have
+      // completed, and its token stage takes the tile three further on once dQ has read K too.
+      if (s == n_sub - 1) {
+        mbar_wait_hot(bar_tile, (uint32_t)t & 1, a.status, abort_flag);
         if (*reinterpret_cast<volatile int*>(abort_flag)) break;
         tc_fence_after();
-        if (reload) {
+        store_quarter(t);
+        if (t + 3 < n_tiles) {
+          mbar_wait_hot(&bar_p2[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);
           if (elect_one()) load_tile(t + 3);
           __syncwarp();
         }
-        if (u + 2 < U) {
-          int t2 = t1, s2 = s1 + 1, stg2 = stg1;   // step u+2
-          if (s2 == n_sub) { s2 = 0; ++t2; stg2 = stg1 == 2 ? 0 : stg1 + 1; }
-          if (s2 == 0) mbar_wait_hot(&bar_full[stg2], (uint32_t)(t2 / 3) & 1, a.status, abort_flag);
-          tc_fence_after();
-          if (elect_one()) { issue_s(u + 2, stg2, s2); mma_commit(&bar_s[xb]); }
-          __syncwarp();
-        }
-        if (last) store_quarter(t, [&] { mbar_arrive4(bar_free); });
       }
       t = t1; s = s1; stg = stg1;
     }
   } else if (is_p2) {
-    // ================= dV / dK / dQ issuer =================
+    // ================= dV / dK / S^T / dQ issuer =================
+    // dV/dK of step u, then S^T(u+2) into the buffer they read: products issued by one thread execute in
+    // issue order, so no completion round trip sits between them; then dQ(u).  After the last step of a
+    // tile this warp reads its lane quarter of dV/dK as soon as their products are complete, so that the
+    // accumulators are free before the next tile's first dS is written.
     int t = 0, s = 0, stg = 0;
     for (int u = 0; u < U; ++u) {
       const int xb = u & 1;
+      int t2 = t, s2 = s + 2, stg2 = stg;            // step u+2
+      while (s2 >= n_sub) { s2 -= n_sub; ++t2; stg2 = stg2 == 2 ? 0 : stg2 + 1; }
+      const bool next = u + 2 < U;
+      const bool last = s == n_sub - 1;
       mbar_wait_hot(&bar_pd[xb], (uint32_t)(u >> 1) & 1, a.status, abort_flag);   // P and dS of step u are written
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
+      if (s == 0 && t > 0) mbar_wait_hot(bar_free, (uint32_t)(t - 1) & 1, a.status, abort_flag);   // dV/dK of tile t-1 read out
+      if (next && t2 != t) mbar_wait_hot(&bar_full[stg2], (uint32_t)(t2 / 3) & 1, a.status, abort_flag);
       tc_fence_after();
-      if (s == 0 && t > 0) {
-        // the dV/dK accumulators still hold tile t-1: read this warp's lane quarter, wait for the other
-        // three quarters, then start this tile's accumulation
-        mbar_wait_hot(bar_tile, (uint32_t)(t - 1) & 1, a.status, abort_flag);
+      if (elect_one()) {
+        issue_dvdk(u, s);
+        if (last) mma_commit(bar_tile);              // one phase per tile: the other warps follow it in order
+        issue_dq(u, stg, t, s);
+        if (next) { issue_s(u + 2, stg2, s2); mma_commit(&bar_s[xb]); }
+        mma_commit(&bar_p2[xb]);
+      }
+      __syncwarp();
+      if (last) {
+        mbar_wait_hot(bar_tile, (uint32_t)t & 1, a.status, abort_flag);
+        if (*reinterpret_cast<volatile int*>(abort_flag)) break;
         tc_fence_after();
-        store_quarter(t - 1, [&] {
-          mbar_wait_hot(bar_free, (uint32_t)(t - 1) & 1, a.status, abort_flag);
-          tc_fence_after();
-          if (elect_one()) {
-            issue_p2(u, stg, t, s);
-            mma_commit(&bar_p2[xb]);
-            if (s == n_sub - 1) mma_commit(bar_tile);
-          }
-          __syncwarp();
-        });
-      } else {
-        if (elect_one()) {
-          issue_p2(u, stg, t, s);
-          mma_commit(&bar_p2[xb]);
-          if (s == n_sub - 1) mma_commit(bar_tile);   // one phase per tile: the other warps follow it in order
-        }
-        __syncwarp();
+        store_quarter(t);
       }
       if (++s == n_sub) { s = 0; ++t; stg = stg == 2 ? 0 : stg + 1; }
-    }
-    if (!*reinterpret_cast<volatile int*>(abort_flag)) {   // this warp's quarter of the last tile
-      mbar_wait(bar_tile, (uint32_t)(n_tiles - 1) & 1, a.status, abort_flag);
-      tc_fence_after();
-      store_quarter(n_tiles - 1, [] {});
     }
   } else if (is_helper) {
     // ================= helper warps: per-token operands of tile t+1, then dV/dK of tile t -> global =========
@@ -507,7 +496,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       mbar_wait_hot(bar_tile, (uint32_t)t & 1, a.status, abort_flag);
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       tc_fence_after();
-      store_quarter(t, [&] { mbar_arrive4(bar_free); });
+      store_quarter(t);
     }
   } else {
     // ================= softmax threads =================
@@ -563,6 +552,8 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         pd[8 + e] = pack_bf16(p[16 + 2 * e] * __uint_as_float(rb[2 * e]), p[16 + 2 * e + 1] * __uint_as_float(rb[2 * e + 1]));
       }
       tmem_st16(buf + 16, pd);
+      // (the shared-memory dS block of this step was last read by dQ(u-2), issued ahead of S^T(u) by the
+      // same thread, hence complete)
       // dS^T of the step as the MN-major A operand of dQ: 64-latent half c4/2, 16-byte chunks 4(c4%2)..+3
       uint8_t* ds_row = sDS + xb * L::kDS + (c4 >> 1) * (128 * 128);
 #pragma unroll

@@ -23,7 +23,7 @@ from ._cabi import FlareProblem, check, lib, ptr, stream_of
 
 __all__ = [
     "flare_multihead_mixer", "flare_gather", "flare_scatter",
-    "mixer_forward", "mixer_backward", "make_problem", "set_kernel_path",
+    "mixer_forward", "mixer_backward", "make_problem", "set_kernel_path", "device_status",
 ]
 
 
@@ -32,6 +32,14 @@ def set_kernel_path(path: str) -> str:
     code = {"auto": 0, "simt": 1, "tc_exact": 2}[path]
     prev = lib.flare_set_path(code)
     return {0: "auto", 1: "simt", 2: "tc_exact"}[prev]
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the current device (synchronises): non-zero if a tensor-core kernel gave up on a
+    bounded wait since the word was last cleared, in which case that kernel's output is not valid."""
+    out = C.c_int(0)
+    check(lib.flare_device_status(C.byref(out), 1 if clear else 0), "flare_device_status")
+    return out.value
 
 
 def _need_cuda(*ts):

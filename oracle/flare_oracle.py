@@ -35,7 +35,7 @@ import torch.nn.functional as F
 
 __all__ = [
     "mixer_sdpa", "mixer_explicit", "mixer_lra", "gather", "scatter",
-    "mixer_fwd_stats", "mixer_bwd_closed_form", "gather_partials",
+    "mixer_fwd_stats", "mixer_bwd_closed_form", "mixer_fwd_bwd_streamed", "gather_partials",
     "lse_combine", "causal_dense", "causal_recurrent", "causal_chunked",
     "triple_attention", "triple_attention_bwd", "causal_linear", "rel_l2",
 ]
@@ -153,6 +153,44 @@ def mixer_bwd_autograd(q, k, v, dy, scale: float = 1.0, fn=None):
     y = fn(q, k, v, scale)
     y.backward(dy)
     return q.grad, k.grad, v.grad
+
+
+def mixer_fwd_bwd_streamed(q, k, v, dy, scale: float = 1.0, chunk: int = 65536):
+    """(y, dq, dk, dv) of the encoder mixer with the token axis walked in chunks.
+
+    The same arithmetic as ``mixer_sdpa`` + ``mixer_bwd_closed_form`` (README.md:37-53 and its
+    autograd), arranged so that no more than M x chunk scores exist at a time: the oracle for
+    token counts where the dense M x N matrices do not fit (one (b, h) of the million-token case).
+    Three sweeps: records of the gather + log-sum-exp combine -> Z, L; then Y and dZ; then dV, dK, dQ.
+    """
+    B, H, N, D = k.shape
+    qe = _expand_q(q, B)
+    bounds = [(n0, min(N, n0 + chunk)) for n0 in range(0, N, chunk)]
+    m, l, acc = gather_partials(q, k, v, scale, bounds)
+    Z, L = lse_combine(m, l, acc)                      # [B,H,M,D], [B,H,M]
+    y = torch.empty_like(v)
+    dZ = torch.zeros_like(Z)
+    for n0, n1 in bounds:
+        S = scale * (qe @ k[:, :, n0:n1].transpose(-2, -1))
+        A = torch.softmax(S, dim=-2)
+        y[:, :, n0:n1] = A.transpose(-2, -1) @ Z
+        dZ += A @ dy[:, :, n0:n1]
+    Delta_m = (dZ * Z).sum(-1)
+    dQ = torch.zeros_like(qe)
+    dK, dV = torch.empty_like(k), torch.empty_like(v)
+    for n0, n1 in bounds:
+        kk, vv, gg = k[:, :, n0:n1], v[:, :, n0:n1], dy[:, :, n0:n1]
+        S = scale * (qe @ kk.transpose(-2, -1))
+        P = torch.exp(S - L[..., None])
+        A = torch.softmax(S, dim=-2)
+        delta_n = (gg * y[:, :, n0:n1]).sum(-1)
+        dV[:, :, n0:n1] = P.transpose(-2, -1) @ dZ
+        dS = P * (dZ @ vv.transpose(-2, -1) - Delta_m[..., None]) + A * (Z @ gg.transpose(-2, -1) - delta_n[..., None, :])
+        dQ += scale * (dS @ kk)
+        dK[:, :, n0:n1] = scale * (dS.transpose(-2, -1) @ qe)
+    if q.dim() == 3:
+        dQ = dQ.sum(0)
+    return y, dQ, dK, dV
 
 
 # ---------------------------------------------------------------------------

@@ -90,3 +90,12 @@ def test_triple_and_causal_linear_references():
     g = load_golden("causal_linear_ref")
     y = O.causal_linear(g["q"], g["k"], g["v"])
     assert O.rel_l2(y, g["y"]) < 1e-5
+
+
+def test_streamed_form_equals_dense_closed_form():
+    """The token-chunked oracle used for the million-token check is the dense one, chunk by chunk."""
+    q, k, v, dy = O.make_inputs(2, 3, 333, 20, 8, dtype=torch.float64, seed=5)
+    y, dq, dk, dv = O.mixer_fwd_bwd_streamed(q, k, v, dy, 0.8, chunk=100)
+    assert O.rel_l2(y, O.mixer_sdpa(q, k, v, 0.8)) < 1e-12
+    for a, b in zip((dq, dk, dv), O.mixer_bwd_closed_form(q, k, v, dy, 0.8)):
+        assert O.rel_l2(a, b) < 1e-12
