@@ -15,7 +15,7 @@ LIB_PATH = PKG / "libflare_b200.so"
 
 F32, F16, BF16 = 0, 1, 2
 TERM_GATHER, TERM_SCATTER, TERM_BOTH = 1, 2, 3
-PATH_AUTO, PATH_SIMT = 0, 1
+PATH_AUTO, PATH_SIMT, PATH_TC_EXACT = 0, 1, 2
 
 DTYPE_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
 
@@ -62,8 +62,8 @@ SIGNATURES = {
     "flare_triple_outer": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp]),
     "flare_triple_contract": (_i, [_i, _i, _i, _i, _i, _i, _vp, _i64, _i64, _i64, _vp, _vp, C.c_float, _vp, _vp]),
     "flare_device_status": (_i, [C.POINTER(C.c_int), _i]),
-    "flare_debug_phase_counters": (_i, [_vp]),
     "flare_probe_ex2": (_i, [_i, _i, _vp, _vp]),
+    "flare_pass_counts": (_i, [C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
     "flare_bwd_dq_partial": (_i, [_P, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
 }
 

@@ -2,7 +2,6 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include "common.cuh"
 #include "launch.h"
@@ -13,6 +12,7 @@ namespace {
 
 thread_local char g_err[512] = "";
 std::atomic<int> g_path{FLARE_PATH_AUTO};
+std::atomic<long long> g_tc_passes{0}, g_simt_passes{0};   // passes enqueued on each kernel family (flare_pass_counts)
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -48,11 +48,6 @@ int check_tok(const char* name, const void* ptr, const int64_t* st, int dtype) {
 }
 
 int auto_splits(const FlareProblem* p) {
-  // FLARE_SPLITS=<n> overrides the choice (tuning and experiments)
-  if (const char* env = getenv("FLARE_SPLITS")) {
-    const int v = atoi(env);
-    if (v >= 1) return v;
-  }
   const int tpt = p->D <= 32 ? 1 : p->D / 32;
   const int lpb = 128 / tpt;
   const long long base = (long long)p->B * p->H * ((p->M + lpb - 1) / lpb);
@@ -140,13 +135,14 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("v", v, p->v_stride, p->dtype));
   if (!rec) return fail(FLARE_EINVAL, "rec is null");
   Ctx c = make_ctx(p);
-  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
-    const int rc = (tc_lat2_supported(c, p->dtype) && !getenv("FLARE_LAT_V1"))
-                       ? tc_gather_partial2(c, q, k, v, rec, (cudaStream_t)stream)
-                       : tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
-    if (rc == FLARE_OK) return after_launch("gather_partial (tcgen05)");
+  if (g_path.load() != FLARE_PATH_SIMT && (tc_lat2_supported(c, p->dtype) || (!key_mask && tc_lat_supported(c, p->dtype)))) {
+    // head dims 16 and 32: the decoupled-schedule kernel; 64 (bf16, no mask): the first-generation one
+    const int rc = tc_lat2_supported(c, p->dtype) ? tc_gather_partial2(c, p->dtype, q, k, v, key_mask, rec, (cudaStream_t)stream)
+                                                  : tc_gather_partial(c, q, k, v, rec, (cudaStream_t)stream);
+    if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("gather_partial (tcgen05)"); }
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "gather_partial (tcgen05): launch setup failed");
   }
+  ++g_simt_passes;
   TRY(simt_gather_partial(c, p->dtype, q, k, v, key_mask, rec, (cudaStream_t)stream));
   return after_launch("gather_partial");
 }
@@ -187,12 +183,12 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
   if (g_path.load() != FLARE_PATH_SIMT && (tc_scatter_supported(c, p->dtype) || tc_scatter2_supported(c, p->dtype))) {
-    const int rc = (tc_scatter2_supported(c, p->dtype) && (c.M > 256 || !getenv("FLARE_SCATTER_V1")))
-                       ? tc_scatter2(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream)
-                       : tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
-    if (rc == FLARE_OK) return after_launch("scatter (tcgen05)");
+    const int rc = tc_scatter2_supported(c, p->dtype) ? tc_scatter2(c, p->dtype, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream)
+                                                      : tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
+    if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("scatter (tcgen05)"); }
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "scatter (tcgen05): launch setup failed");
   }
+  ++g_simt_passes;
   TRY(simt_scatter(c, p->dtype, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream));
   return after_launch("scatter");
 }
@@ -207,13 +203,14 @@ int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
   if (!lse_n || !dz_part) return fail(FLARE_EINVAL, "lse_n or dz_part is null");
   Ctx c = make_ctx(p);
-  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_lat_supported(c, p->dtype)) {
-    const int rc = (tc_lat2_supported(c, p->dtype) && !getenv("FLARE_LAT_V1"))
-                       ? tc_dz_partial2(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream)
+  if (g_path.load() != FLARE_PATH_SIMT && (tc_lat2_supported(c, p->dtype) || (!key_mask && tc_lat_supported(c, p->dtype)))) {
+    const int rc = tc_lat2_supported(c, p->dtype)
+                       ? tc_dz_partial2(c, p->dtype, q, k, dy, key_mask, lse_n, dz_part, (cudaStream_t)stream)
                        : tc_dz_partial(c, q, k, dy, lse_n, dz_part, (cudaStream_t)stream);
-    if (rc == FLARE_OK) return after_launch("bwd_dz_partial (tcgen05)");
+    if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("bwd_dz_partial (tcgen05)"); }
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_dz_partial (tcgen05): launch setup failed");
   }
+  ++g_simt_passes;
   TRY(simt_dz_partial(c, p->dtype, q, k, dy, key_mask, lse_n, dz_part, (cudaStream_t)stream));
   return after_launch("bwd_dz_partial");
 }
@@ -248,6 +245,7 @@ int flare_bwd_tokens(const FlareProblem* p, int terms, const void* q, const void
   }
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p, terms);
+  ++g_simt_passes;
   TRY(simt_bwd_tokens(c, p->dtype, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta_n,
                       (cudaStream_t)stream));
   return after_launch("bwd_tokens");
@@ -272,6 +270,7 @@ int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const 
     if (!lse_n || !delta_n) return fail(FLARE_EINVAL, "scatter term needs lse_n and delta_n");
   }
   Ctx c = make_ctx(p, terms);
+  ++g_simt_passes;
   TRY(simt_dq_partial(c, p->dtype, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part,
                       (cudaStream_t)stream));
   return after_launch("bwd_dq_partial");
@@ -284,8 +283,9 @@ int flare_device_status(int* out, int clear) {
   return FLARE_OK;
 }
 
-int flare_debug_phase_counters(long long* dev_counters) {
-  tc_set_phase_counters(dev_counters);
+int flare_pass_counts(long long* tensor_core, long long* simt) {
+  if (tensor_core) *tensor_core = g_tc_passes.load();
+  if (simt) *simt = g_simt_passes.load();
   return FLARE_OK;
 }
 
@@ -320,54 +320,41 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
   if (p->n_splits < 1) return fail(FLARE_EINVAL, "flare_bwd_main needs n_splits >= 1");
   if (!dq_part) return fail(FLARE_EINVAL, "dq_part is null");
   Ctx c = make_ctx(p, terms);
-  if (g_path.load() != FLARE_PATH_SIMT && !key_mask && tc_bwd_supported(c, p->dtype)) {
+  const bool use_g = (terms & FLARE_TERM_GATHER) != 0, use_s = (terms & FLARE_TERM_SCATTER) != 0;
+  if (g_path.load() != FLARE_PATH_SIMT && p->N > 0 && tc_bwd_supported(c, p->dtype)) {
     TRY(check_tok("q", q, p->q_stride, p->dtype));
     TRY(check_tok("k", k, p->k_stride, p->dtype));
-    TRY(check_tok("v", v, p->v_stride, p->dtype));
-    TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
-    TRY(check_tok("y", y, p->y_stride, p->dtype));
     TRY(check_tok("dk", dk, p->dk_stride, p->dtype));
-    TRY(check_tok("dv", dv, p->dv_stride, p->dtype));
-    if (!z32 || !dz32 || !lse_m || !lse_n) return fail(FLARE_EINVAL, "bwd_main: z32, dz32, lse_m, lse_n are required");
-    // delta_n ([B,H,N] floats) is not needed by the fused kernels; it doubles as the scratch of the
-    // range check that picks, per (b, h), the one-exponential kernel or the exact one
+    if (!z32) return fail(FLARE_EINVAL, "bwd_main: z32 is null");
+    if (use_g) {
+      TRY(check_tok("v", v, p->v_stride, p->dtype));
+      TRY(check_tok("dv", dv, p->dv_stride, p->dtype));
+      if (!dz32 || !lse_m) return fail(FLARE_EINVAL, "bwd_main: the gather term needs dz32 and lse_m");
+    }
+    if (use_s) {
+      TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
+      TRY(check_tok("y", y, p->y_stride, p->dtype));
+      if (!lse_n) return fail(FLARE_EINVAL, "bwd_main: the scatter term needs lse_n");
+    }
+    // The one-exponential kernels cover the plain case (bf16, both terms, no mask; D = 32 for any M up to
+    // 1024, D = 16 up to 256 latents).  An on-device range check picks, per (b, h), between them (flag 0)
+    // and the general two-exponential kernel (flag 1); both are launched and each returns at once on the
+    // (b, h) it does not own.  delta_n ([B,H,N] floats) is not needed by the fused kernels and doubles as
+    // the scratch of that check.  Everything else goes to the general kernel directly.
     const int* flag = nullptr;
     int rc = FLARE_OK;
     const size_t have = (size_t)p->B * p->H * (size_t)p->N * sizeof(float);
-    if (g_path.load() != FLARE_PATH_TC_EXACT && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
-        have >= tc_bwd2_scratch_bytes(c))
+    const bool fast = p->dtype == FLARE_BF16 && terms == FLARE_TERM_BOTH && !key_mask && g_path.load() != FLARE_PATH_TC_EXACT &&
+                      (c.D == 32 || c.M <= 256) && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
+                      have >= tc_bwd2_scratch_bytes(c);
+    if (fast)
       rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
-    if (rc == FLARE_OK) rc = tc_bwd_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, (cudaStream_t)stream);
-    if (rc == FLARE_OK) return after_launch("bwd_main (tcgen05)");
+    if (rc == FLARE_OK)
+      rc = tc_bwd_main(c, p->dtype, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, (cudaStream_t)stream);
+    if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("bwd_main (tcgen05)"); }
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_main (tcgen05): launch setup failed");
   }
-  // More than 256 latents: the one-exponential kernel in blocks of 256.  The exact kernel that takes over
-  // flagged (b, h) has no blocked form, so the flags are read back (one small copy and a stream
-  // synchronisation per call, this shape only) and a flagged problem goes to the fp32 kernels below.
-  if (g_path.load() == FLARE_PATH_AUTO && !key_mask && c.M > 256 && tc_bwd4_supported(c, p->dtype) && delta_n &&
-      !getenv("FLARE_BWD3") && !getenv("FLARE_NO_PIPELINE") &&
-      (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 && z32 && dz32 && lse_m && lse_n &&
-      (size_t)p->B * p->H * (size_t)p->N * sizeof(float) >= tc_bwd2_scratch_bytes(c) && p->B * p->H <= 4096 &&
-      check_tok("q", q, p->q_stride, p->dtype) == FLARE_OK && check_tok("k", k, p->k_stride, p->dtype) == FLARE_OK &&
-      check_tok("v", v, p->v_stride, p->dtype) == FLARE_OK && check_tok("dy", dy, p->dy_stride, p->dtype) == FLARE_OK &&
-      check_tok("y", y, p->y_stride, p->dtype) == FLARE_OK && check_tok("dk", dk, p->dk_stride, p->dtype) == FLARE_OK &&
-      check_tok("dv", dv, p->dv_stride, p->dtype) == FLARE_OK) {
-    const int* flag = nullptr;
-    int rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
-    if (rc == FLARE_OK) {
-      int host_flags[4096];
-      const int nbh = p->B * p->H;
-      if (cudaMemcpyAsync(host_flags, flag, nbh * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
-          cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess)
-        return fail(FLARE_ECUDA, "bwd_main: reading the range flags failed");
-      bool flagged = false;
-      for (int i = 0; i < nbh; ++i) flagged |= host_flags[i] != 0;
-      if (!flagged) return after_launch("bwd_main (tcgen05, latent blocks)");
-    } else if (rc != FLARE_EUNSUPPORTED) {
-      return fail(rc, "bwd_main (tcgen05, latent blocks): launch setup failed");
-    }
-  }
-  if ((terms & FLARE_TERM_SCATTER) && !delta_n) return fail(FLARE_EINVAL, "bwd_main: delta_n scratch is null");
+  if (use_s && !delta_n) return fail(FLARE_EINVAL, "bwd_main: delta_n scratch is null");
   TRY(flare_bwd_tokens(p, terms, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta_n, stream));
   TRY(flare_bwd_dq_partial(p, terms, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part, stream));
   return FLARE_OK;

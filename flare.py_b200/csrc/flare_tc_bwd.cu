@@ -16,7 +16,13 @@
 //          dQ_j += dS K_t                     (A and B from shared memory) -> columns [448+32j, +D)
 // Q, Z, dZ stay resident in shared memory for the whole range, each tile in one layout that
 // serves both as a K-major and as an MN-major operand.  K, V, dY, Y tiles arrive by TMA in a
-// two-stage ring.  Requires bf16, D in {16, 32}, M <= 256.
+// two-stage ring.
+//
+// This is the general tensor-core backward: bf16 or fp16, D in {16, 32}, a key-padding mask (excluded
+// tokens get P = A = 0, hence zero dK, dV and no share in dQ), either softmax term alone (the separate
+// gather / scatter operators), and more than 256 latents as blocks of 256 per launch, each block adding
+// its dK/dV to what the earlier ones wrote.  The one-exponential kernels (flare_tc_bwd2.cu,
+// flare_tc_bwd4.cu) are the fast form of its unmasked two-term bf16 case.
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -35,10 +41,13 @@ struct BwdArgs {
   const float* dz32;
   const float* lse_m;
   const float* lse_n;
-  __nv_bfloat16* dk;
-  __nv_bfloat16* dv;
+  void* dk;                    // 16-bit rows
+  void* dv;
   long long dks[3], dvs[3];
-  float* dq_part;              // [S,B,H,M,D]
+  float* dq_part;              // [S,B,H,M_total,D]
+  int M_total, m0;             // this launch covers latents [m0, m0 + M) of M_total
+  int terms;                   // FLARE_TERM_GATHER | FLARE_TERM_SCATTER
+  const uint8_t* mask;         // [B,N] key-padding mask (non-zero = keep) or null
   int* status;
   const int* flag;             // [B*H] or null: run only the (b, h) whose flag is 1
 };
@@ -50,10 +59,10 @@ struct BwdSmem {
   static constexpr int kT = 128 * ROWB;            // one token tile
   static constexpr int kStage = 4 * kT;            // K, V, dY, Y
   static constexpr int kDS = 2 * 128 * 128;        // dS^T [2 blocks of 64 latents][128 tok][128 B]
-  static constexpr int kBytes = 3 * kLat + 2 * kStage + kDS + 256 * 8 + 2 * 128 * 8 + 1024 + 128;
+  static constexpr int kBytes = 3 * kLat + 2 * kStage + kDS + 256 * 8 + 2 * 128 * 8 + 2 * 128 * 4 + 1024 + 128;
 };
 
-template <int D>
+template <int D, typename T16, bool ACC>          // ACC: add to the dK/dV an earlier latent block wrote
 __global__ void __launch_bounds__(256, 1)
 k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
@@ -70,7 +79,8 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
   uint8_t* sDS = sTok + 2 * L::kStage;
   float2* sLD = reinterpret_cast<float2*>(sDS + L::kDS);     // [256] {L_m log2e, Delta_m}
   float2* sCD = sLD + 256;                                    // [2][128] {C_n log2e, delta_n}
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sCD + 256);
+  float* sBias = reinterpret_cast<float*>(sCD + 256);         // [2][128] 0, or -inf for an excluded token
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sBias + 256);
   uint64_t* bar_full = bars;                       // [2]
   uint64_t* bar_mma = bars + 2;
   uint64_t* bar_q = bars + 3;
@@ -85,10 +95,11 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
   if (a.flag && a.flag[bh] != 1) return;           // the one-exponential kernel owns this (b, h)
   const int b = bh / a.H, h = bh % a.H;
   const int M = a.M;
+  const bool use_g = (a.terms & FLARE_TERM_GATHER) != 0, use_s = (a.terms & FLARE_TERM_SCATTER) != 0;
   const int n_mblk = (M + 127) / 128;
   const int n0 = split * a.chunk, n1 = min(a.N, n0 + a.chunk);
   const int n_tiles = n1 > n0 ? (n1 - n0 + 127) / 128 : 0;
-  float* dq_out = a.dq_part + (((long long)split * a.B + b) * a.H + h) * M * D;
+  float* dq_out = a.dq_part + ((((long long)split * a.B + b) * a.H + h) * a.M_total + a.m0) * D;
 
   if (n_tiles == 0) {                              // empty range contributes nothing
     for (int i = tid; i < M * D; i += 256) dq_out[i] = 0.f;
@@ -112,11 +123,13 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
 
   auto load_tile = [&](int stage, int tok0) {
     uint8_t* dst = sTok + stage * L::kStage;
-    mbar_expect_tx(&bar_full[stage], 4 * L::kT);
+    mbar_expect_tx(&bar_full[stage], (1 + (use_g ? 1 : 0) + (use_s ? 2 : 0)) * L::kT);
     tma_load_4d(dst, &tmK, &bar_full[stage], 0, tok0, h, b);
-    tma_load_4d(dst + L::kT, &tmV, &bar_full[stage], 0, tok0, h, b);
-    tma_load_4d(dst + 2 * L::kT, &tmG, &bar_full[stage], 0, tok0, h, b);
-    tma_load_4d(dst + 3 * L::kT, &tmY, &bar_full[stage], 0, tok0, h, b);
+    if (use_g) tma_load_4d(dst + L::kT, &tmV, &bar_full[stage], 0, tok0, h, b);
+    if (use_s) {
+      tma_load_4d(dst + 2 * L::kT, &tmG, &bar_full[stage], 0, tok0, h, b);
+      tma_load_4d(dst + 3 * L::kT, &tmY, &bar_full[stage], 0, tok0, h, b);
+    }
   };
 
   if (tid == 0) {
@@ -126,19 +139,23 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
   }
   // resident latent operands: Z and dZ as bf16 in the swizzled tile layout; L and Delta per latent
   {
-    const long long lrow = ((long long)b * a.H + h) * M;
+    const long long lrow = ((long long)b * a.H + h) * a.M_total + a.m0;
     const float* zb = a.z32 + lrow * D;
-    const float* dzb = a.dz32 + lrow * D;
+    const float* dzb = use_g ? a.dz32 + lrow * D : nullptr;
     for (int i = tid; i < 256 * CPR; i += 256) {
       const int r = i / CPR, c = i % CPR;
       uint4 pz = make_uint4(0, 0, 0, 0), pd = make_uint4(0, 0, 0, 0);
       if (r < M) {
         const float4 z0 = *reinterpret_cast<const float4*>(zb + r * D + c * 8);
         const float4 z1 = *reinterpret_cast<const float4*>(zb + r * D + c * 8 + 4);
-        const float4 d0 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8);
-        const float4 d1 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8 + 4);
-        pz = make_uint4(pack_bf16(z0.x, z0.y), pack_bf16(z0.z, z0.w), pack_bf16(z1.x, z1.y), pack_bf16(z1.z, z1.w));
-        pd = make_uint4(pack_bf16(d0.x, d0.y), pack_bf16(d0.z, d0.w), pack_bf16(d1.x, d1.y), pack_bf16(d1.z, d1.w));
+        pz = make_uint4(Op16<T16>::pack(z0.x, z0.y), Op16<T16>::pack(z0.z, z0.w), Op16<T16>::pack(z1.x, z1.y),
+                        Op16<T16>::pack(z1.z, z1.w));
+        if (use_g) {
+          const float4 d0 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8);
+          const float4 d1 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8 + 4);
+          pd = make_uint4(Op16<T16>::pack(d0.x, d0.y), Op16<T16>::pack(d0.z, d0.w), Op16<T16>::pack(d1.x, d1.y),
+                          Op16<T16>::pack(d1.z, d1.w));
+        }
       }
       *reinterpret_cast<uint4*>(sZ + swz_off<ROWB>(r, c)) = pz;
       *reinterpret_cast<uint4*>(sDZ + swz_off<ROWB>(r, c)) = pd;
@@ -146,7 +163,7 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
     {
       const int m = tid;                           // 256 threads, 256 latent slots
       float l2 = INFINITY, dl = 0.f;
-      if (m < M) {
+      if (m < M && use_g) {                        // without the gather term P = 0 (L = +inf)
         for (int i = 0; i < D; ++i) dl = fmaf(dzb[m * D + i], zb[m * D + i], dl);
         l2 = a.lse_m[lrow + m] * kLog2e;
       }
@@ -157,11 +174,13 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
   __syncthreads();
   mbar_wait(bar_q, 0, a.status, abort_flag);
 
-  const uint32_t id_st = idesc_f16(128, 128, 1, 1, 0, 0);    // S^T, T1, T2: A, B K-major
-  const uint32_t id_tv = idesc_f16(128, D, 1, 1, 0, 1);      // dV, dK: A in tensor memory, B MN-major
-  const uint32_t id_dq = idesc_f16(128, D, 1, 1, 1, 1);      // dQ: A and B MN-major
+  constexpr int F = Op16<T16>::kFmt;
+  const uint32_t id_st = idesc_f16(128, 128, F, F, 0, 0);    // S^T, T1, T2: A, B K-major
+  const uint32_t id_tv = idesc_f16(128, D, F, F, 0, 1);      // dV, dK: A in tensor memory, B MN-major
+  const uint32_t id_dq = idesc_f16(128, D, F, F, 1, 1);      // dQ: A and B MN-major
   const float sl = a.scale_log2;
-  const float* cb = a.lse_n + ((long long)b * a.H + h) * a.N;
+  const float* cb = use_s ? a.lse_n + ((long long)b * a.H + h) * a.N : nullptr;
+  const uint8_t* mrow = a.mask ? a.mask + (long long)b * a.N : nullptr;
   uint32_t ph_mma = 0;
   bool aborted = false;
 
@@ -175,30 +194,33 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
     if (tid == 0 && t + 1 < n_tiles) load_tile(st ^ 1, tok0 + 128);   // every MMA of tile t-1 is complete
     mbar_wait(&bar_full[st], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
 
-    // per-token scalars: C_n (log2 units) and delta_n = dY_n . Y_n from the tiles just loaded
+    // per-token scalars: C_n (log2 units) and delta_n = dY_n . Y_n from the tiles just loaded; the score
+    // bias that removes a token (past the end of the range, or masked out): P = A = 0 for it
     if (tid < 128) {
       const int n = tok0 + tid;
       float dl = 0.f, c2 = INFINITY;
-      if (n < n1) {
+      const bool keep = n < n1 && (!mrow || mrow[n] != 0);
+      if (keep && use_s) {
 #pragma unroll
         for (int c = 0; c < CPR; ++c) {
           const uint4 g4 = *reinterpret_cast<const uint4*>(tG + swz_off<ROWB>(tid, c));
           const uint4 y4 = *reinterpret_cast<const uint4*>(tY + swz_off<ROWB>(tid, c));
-          const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
-          const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y4);
+          const uint32_t* gp = reinterpret_cast<const uint32_t*>(&g4);
+          const uint32_t* yp = reinterpret_cast<const uint32_t*>(&y4);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            const float2 gf = __bfloat1622float2(gp[j]), yf = __bfloat1622float2(yp[j]);
+            const float2 gf = Op16<T16>::unpack(gp[j]), yf = Op16<T16>::unpack(yp[j]);
             dl = fmaf(gf.x, yf.x, dl); dl = fmaf(gf.y, yf.y, dl);
           }
         }
         c2 = cb[n] * kLog2e;
       }
       sCD[st * 128 + tid] = make_float2(c2, dl);
+      sBias[st * 128 + tid] = keep ? 0.f : -INFINITY;
     }
     __syncthreads();
     const float2 cd = sCD[st * 128 + row];
-    const float c2n = cd.x, deln = cd.y;
+    const float c2n = cd.x, deln = cd.y, bias = sBias[st * 128 + row];
 
     for (int j = 0; j < n_mblk; ++j) {
       if (tid == 0) {
@@ -210,10 +232,14 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
                        dDZ_ = smem_desc<ROWB>(smem_u32(sDZ) + lo);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cS, dK_ + 2 * kk, dQ_ + 2 * kk, id_st, kk > 0);
+        if (use_g) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT1, dV_ + 2 * kk, dDZ_ + 2 * kk, id_st, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT1, dV_ + 2 * kk, dDZ_ + 2 * kk, id_st, kk > 0);
+        }
+        if (use_s) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT2, dG_ + 2 * kk, dZ_ + 2 * kk, id_st, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cT2, dG_ + 2 * kk, dZ_ + 2 * kk, id_st, kk > 0);
+        }
         mma_commit(bar_mma);
       }
       mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
@@ -228,19 +254,26 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       for (int i = 0; i < 4; ++i) {
         uint32_t rs[16], r1[16], r2[16], pp[8], pd[8];
         tmem_ld16(lane_base + cS + colb + 16 * i, rs);
-        tmem_ld16(lane_base + cT1 + colb + 16 * i, r1);
-        tmem_ld16(lane_base + cT2 + colb + 16 * i, r2);
+        if (use_g) tmem_ld16(lane_base + cT1 + colb + 16 * i, r1);
+        if (use_s) tmem_ld16(lane_base + cT2 + colb + 16 * i, r2);
         tmem_wait_ld();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float4 l4 = *reinterpret_cast<const float4*>(&ld[16 * i + 2 * e]);   // {L2,Dl} x 2
-          const float x0 = __uint_as_float(rs[2 * e]) * sl, x1 = __uint_as_float(rs[2 * e + 1]) * sl;
+          const float x0 = fmaf(__uint_as_float(rs[2 * e]), sl, bias), x1 = fmaf(__uint_as_float(rs[2 * e + 1]), sl, bias);
           const float p0 = ex2(x0 - l4.x), p1 = ex2(x1 - l4.z);
-          const float a0 = ex2(x0 - c2n), a1 = ex2(x1 - c2n);
-          const float s0 = fmaf(p0, __uint_as_float(r1[2 * e]) - l4.y, a0 * (__uint_as_float(r2[2 * e]) - deln));
-          const float s1 = fmaf(p1, __uint_as_float(r1[2 * e + 1]) - l4.w, a1 * (__uint_as_float(r2[2 * e + 1]) - deln));
-          pp[e] = pack_bf16(p0, p1);
-          pd[e] = pack_bf16(s0, s1);
+          float s0 = 0.f, s1 = 0.f;
+          if (use_s) {
+            const float a0 = ex2(x0 - c2n), a1 = ex2(x1 - c2n);
+            s0 = a0 * (__uint_as_float(r2[2 * e]) - deln);
+            s1 = a1 * (__uint_as_float(r2[2 * e + 1]) - deln);
+          }
+          if (use_g) {
+            s0 = fmaf(p0, __uint_as_float(r1[2 * e]) - l4.y, s0);
+            s1 = fmaf(p1, __uint_as_float(r1[2 * e + 1]) - l4.w, s1);
+          }
+          pp[e] = Op16<T16>::pack(p0, p1);
+          pd[e] = Op16<T16>::pack(s0, s1);
         }
         tmem_st8(lane_base + cS + colb + 8 * i, pp);
         tmem_st8(lane_base + cT1 + colb + 8 * i, pd);
@@ -264,7 +297,7 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
         for (int kk = 0; kk < 8; ++kk) {           // contraction over the 128 latents of block j
           const uint32_t acol = (kk < 4) ? 8 * kk : 64 + 8 * (kk - 4);
           const uint64_t boff = (uint64_t)((kk * 16 * ROWB) >> 4);
-          mma_ts(tmem + cDV, tmem + cS + acol, bDZ + boff, id_tv, (j > 0) || (kk > 0));
+          if (use_g) mma_ts(tmem + cDV, tmem + cS + acol, bDZ + boff, id_tv, (j > 0) || (kk > 0));
           mma_ts(tmem + cDK, tmem + cT1 + acol, bQ + boff, id_tv, (j > 0) || (kk > 0));
         }
 #pragma unroll
@@ -280,7 +313,7 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
     if (aborted) break;
 
     // ---- dV (first half of the threads) and dK (second half) of this tile -> global -------------
-    {
+    if (wg == 1 || use_g) {
       uint32_t r[D];
       const uint32_t col = wg ? cDK : cDV;
       if constexpr (D == 16) tmem_ld16(lane_base + col, r);
@@ -289,15 +322,25 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       const int n = tok0 + row;
       if (n < n1) {
         const float f = wg ? a.scale : 1.f;
-        __nv_bfloat16* op = wg ? a.dk + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
-                               : a.dv + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
+        uint16_t* op = wg ? static_cast<uint16_t*>(a.dk) + b * a.dks[0] + h * a.dks[1] + (long long)n * a.dks[2]
+                          : static_cast<uint16_t*>(a.dv) + b * a.dvs[0] + h * a.dvs[1] + (long long)n * a.dvs[2];
 #pragma unroll
         for (int c = 0; c < D / 8; ++c) {
+          float g[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) g[j] = __uint_as_float(r[8 * c + j]) * f;
+          if constexpr (ACC) {
+            const uint4 old = reinterpret_cast<const uint4*>(op)[c];
+            const uint32_t* o2 = reinterpret_cast<const uint32_t*>(&old);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 of = Op16<T16>::unpack(o2[j]);
+              g[2 * j] += of.x; g[2 * j + 1] += of.y;
+            }
+          }
           uint4 o;
-          o.x = pack_bf16(__uint_as_float(r[8 * c]) * f, __uint_as_float(r[8 * c + 1]) * f);
-          o.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * f, __uint_as_float(r[8 * c + 3]) * f);
-          o.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * f, __uint_as_float(r[8 * c + 5]) * f);
-          o.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * f, __uint_as_float(r[8 * c + 7]) * f);
+          o.x = Op16<T16>::pack(g[0], g[1]); o.y = Op16<T16>::pack(g[2], g[3]);
+          o.z = Op16<T16>::pack(g[4], g[5]); o.w = Op16<T16>::pack(g[6], g[7]);
           reinterpret_cast<uint4*>(op)[c] = o;
         }
       }
@@ -328,55 +371,69 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
 
 // ------------------------------------------------------------------------------------------
 bool tc_bwd_supported(const Ctx& c, int dtype) {
-  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.M >= 1 && c.M <= 256 && c.N >= 1 &&
-         c.terms == FLARE_TERM_BOTH;
+  return (dtype == FLARE_BF16 || dtype == FLARE_F16) && (c.D == 16 || c.D == 32) && c.M >= 1 && c.M <= 1024 && c.N >= 1 &&
+         c.terms >= 1 && c.terms <= 3;
 }
 
-template <int D>
+template <int D, typename T16>
 static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
-                      const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk,
-                      void* dv, float* dq_part, const int* flag, cudaStream_t st) {
-  CUtensorMap tmQ, tmK, tmV, tmG, tmY;
+                      const uint8_t* mask, const float* z32, const float* dz32, const float* lse_m, const float* lse_n,
+                      void* dk, void* dv, float* dq_part, const int* flag, cudaStream_t st) {
+  CUtensorMap tmK, tmV, tmG, tmY;
   const uint64_t e = 2;
+  constexpr int F = Op16<T16>::kFmt;
   const bool qb = c.qs[0] != 0;
+  const bool use_g = (c.terms & FLARE_TERM_GATHER) != 0, use_s = (c.terms & FLARE_TERM_SCATTER) != 0;
   auto tokmap = [&](CUtensorMap* m, const void* p, const long long* s) {
-    return make_tile_map(m, p, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, s[2] * e, s[1] * e,
+    return make_tile_map(m, p, F, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, s[2] * e, s[1] * e,
                          (c.B > 1 ? s[0] : s[1] * c.H) * e, 128);
   };
-  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
-                     (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256) ||
-      !tokmap(&tmK, k, c.ks) || !tokmap(&tmV, v, c.vs) || !tokmap(&tmG, dy, c.dys) || !tokmap(&tmY, y, c.ys))
+  // a term that is switched off never loads its tiles: its maps stand in with K's
+  if (!tokmap(&tmK, k, c.ks) || !tokmap(&tmV, use_g ? v : k, use_g ? c.vs : c.ks) ||
+      !tokmap(&tmG, use_s ? dy : k, use_s ? c.dys : c.ks) || !tokmap(&tmY, use_s ? y : k, use_s ? c.ys : c.ks))
     return FLARE_EUNSUPPORTED;
   BwdArgs a;
-  a.B = c.B; a.H = c.H; a.N = c.N; a.M = c.M;
+  a.B = c.B; a.H = c.H; a.N = c.N; a.M_total = c.M;
   a.scale = c.scale; a.scale_log2 = c.scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
   a.n_splits = c.n_splits; a.chunk = c.chunk;
   a.z32 = z32; a.dz32 = dz32; a.lse_m = lse_m; a.lse_n = lse_n;
-  a.dk = reinterpret_cast<__nv_bfloat16*>(dk); a.dv = reinterpret_cast<__nv_bfloat16*>(dv);
+  a.dk = dk; a.dv = dv;
   for (int i = 0; i < 3; ++i) { a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
+  a.terms = c.terms;
+  a.mask = mask;
   a.status = tc_status_ptr();
   a.flag = flag;
-  static bool attr_done = false;
   constexpr int smem = BwdSmem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_bwd<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd<D, T16, false>), smem) != FLARE_OK ||
+      tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd<D, T16, true>), smem) != FLARE_OK)
+    return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_bwd<D><<<(unsigned)grid, 256, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
+  for (int m0 = 0; m0 < c.M; m0 += 256) {
+    const int mb = c.M - m0 < 256 ? c.M - m0 : 256;
+    CUtensorMap tmQ;
+    const char* qblk = static_cast<const char*>(q) + (long long)m0 * c.qs[2] * e;
+    if (!make_tile_map(&tmQ, qblk, F, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
+                       (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
+      return FLARE_EUNSUPPORTED;
+    a.M = mb; a.m0 = m0;
+    if (m0 == 0) k_tc_bwd<D, T16, false><<<(unsigned)grid, 256, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
+    else k_tc_bwd<D, T16, true><<<(unsigned)grid, 256, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
+  }
   return FLARE_OK;
 }
 
-int tc_bwd_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
-                const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                float* dq_part, const int* flag, cudaStream_t st) {
+int tc_bwd_main(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                const uint8_t* mask, const float* z32, const float* dz32, const float* lse_m, const float* lse_n,
+                void* dk, void* dv, float* dq_part, const int* flag, cudaStream_t st) {
+  const bool bf = dtype == FLARE_BF16;
   switch (c.D) {
-    case 16: return launch_bwd<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
-    case 32: return launch_bwd<32>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
+    case 16: return bf ? launch_bwd<16, __nv_bfloat16>(c, q, k, v, dy, y, mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st)
+                       : launch_bwd<16, __half>(c, q, k, v, dy, y, mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
+    case 32: return bf ? launch_bwd<32, __nv_bfloat16>(c, q, k, v, dy, y, mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st)
+                       : launch_bwd<32, __half>(c, q, k, v, dy, y, mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, st);
   }
   return FLARE_EUNSUPPORTED;
 }

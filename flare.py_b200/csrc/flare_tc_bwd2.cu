@@ -21,7 +21,6 @@
 // One CTA of 512 threads per SM: thread (row, g) owns token row `row` (tensor-memory lane) and the
 // 32 latent columns [32g, 32g+32) of the current 128-latent block.  Tensor memory: S^T [0,128),
 // T' [128,256), dV 256, dK 288, dQ_j 320+32j.  Requires bf16, D in {16,32}, M <= 256.
-#include <cstdlib>
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -114,7 +113,6 @@ struct Bwd2Args {
   long long dks[3], dvs[3];
   float* dq_part;              // [S,B,H,M,D]
   int* status;
-  long long* prof;             // optional phase counters (clock cycles seen by thread 0), or null
 };
 
 template <int D>
@@ -403,11 +401,9 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   for (int t = 0; t < n_tiles && !aborted; ++t) {
     const int st = t & 1;
     for (int j = 0; j < n_mblk; ++j) {
-      long long c0 = a.prof ? clock64() : 0;
       mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
       ph_mma ^= 1;
       tc_fence_after();
-      long long c1 = a.prof ? clock64() : 0;
       if (j == 0) {
         // every product that read stage st^1 (tile t-1) is complete: refill it, and write out tile t-1
         if (tid == 0 && t + 1 < n_tiles) load_tile(st ^ 1, n0 + (t + 1) * 128);
@@ -446,17 +442,14 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       }
       const bool last_blk = (j + 1 == n_mblk);
       const bool has_next_tile = (t + 1 < n_tiles);
-      long long c2 = a.prof ? clock64() : 0;
       if (last_blk && has_next_tile) {            // operands of the next tile, while this step's stores drain
         mbar_wait(&bar_full[st ^ 1], (uint32_t)((t + 1) >> 1) & 1, a.status, abort_flag);
         prep_tile(t + 1);
       }
-      long long c3 = a.prof ? clock64() : 0;
       tmem_wait_st();
       fence_proxy_async();
       tc_fence_before();
       __syncthreads();
-      long long c4 = a.prof ? clock64() : 0;
       aborted = *reinterpret_cast<volatile int*>(abort_flag) != 0;
       if (aborted) break;
 
@@ -469,15 +462,6 @@ k_tc_bwd2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           mma_commit(bar_mma);
         }
         __syncwarp();
-        if (a.prof && tid == 0) {
-          const long long c5 = clock64();
-          atomicAdd((unsigned long long*)&a.prof[0], (unsigned long long)(c1 - c0));   // wait for the products
-          atomicAdd((unsigned long long*)&a.prof[1], (unsigned long long)(c2 - c1));   // stores + softmax math
-          atomicAdd((unsigned long long*)&a.prof[2], (unsigned long long)(c3 - c2));   // next tile's operands
-          atomicAdd((unsigned long long*)&a.prof[3], (unsigned long long)(c4 - c3));   // drain + CTA barrier
-          atomicAdd((unsigned long long*)&a.prof[4], (unsigned long long)(c5 - c4));   // issue
-          atomicAdd((unsigned long long*)&a.prof[5], 1ull);                             // steps
-        }
       }
     }
   }
@@ -540,14 +524,8 @@ static int launch_bwd2(const Ctx& c, const void* q, const void* k, const void* v
   for (int i = 0; i < 3; ++i) { a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
-  a.prof = tc_phase_counters();
-  static bool attr_done = false;
   constexpr int smem = Bwd2Smem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_bwd2<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd2<D>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   k_tc_bwd2<D><<<(unsigned)grid, 512, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
@@ -567,12 +545,9 @@ int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, cons
   k_bwd_range_c<<<dim3(kRangeParts, (unsigned)bh), 256, 0, st>>>(lse_n, c.N, part);
   k_bwd_range_final<<<(unsigned)bh, 256, 0, st>>>(lse_m, c.M, part, mu, flag);
   *flag_out = flag;
-  // the 128-latent-step kernel where it applies (D = 32, M <= 256), else the step-serial one;
-  // FLARE_BWD3 / FLARE_NO_PIPELINE select the earlier kernels (tuning and tests)
-  if (tc_bwd4_supported(c, FLARE_BF16) && !getenv("FLARE_BWD3") && !getenv("FLARE_NO_PIPELINE"))
+  // D = 32: the pipelined kernel with two issuing warps (flare_tc_bwd4.cu); D = 16: the step-serial one here
+  if (tc_bwd4_supported(c, FLARE_BF16))
     return tc_bwd4_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
-  if (tc_bwd3_supported(c, FLARE_BF16) && !getenv("FLARE_NO_PIPELINE"))
-    return tc_bwd3_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
   switch (c.D) {
     case 16: return launch_bwd2<16>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
     case 32: return launch_bwd2<32>(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);

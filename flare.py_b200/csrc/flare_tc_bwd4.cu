@@ -624,14 +624,9 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   for (int i = 0; i < 3; ++i) { a.ys[i] = c.ys[i]; a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
-  static bool attr_done = false;
   constexpr int smem = Bwd4Smem::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_bwd4<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(k_tc_bwd4<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd4<false>), smem) != FLARE_OK) return FLARE_ECUDA;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd4<true>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   for (int m0 = 0; m0 < c.M; m0 += 256) {

@@ -35,7 +35,6 @@ struct LatArgs {
   const float* lse_n;          // MODE 1: [B,H,N]
   float* out;                  // MODE 0: rec [S,B,H,M,D+2]; MODE 1: dz_part [S,B,H,M,D]
   int* status;                 // device status word
-  long long* prof;             // optional phase counters, or null
 };
 
 template <int D>
@@ -135,11 +134,9 @@ k_tc_lat(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       const int n = tile0 + tid;
       sC2[st * 128 + tid] = (tid < cnt) ? cb[n] * kLog2e : INFINITY;
     }
-    const long long c0 = (a.prof && tid == 0) ? clock64() : 0;
     mbar_wait(bar_mma, ph_mma, a.status, abort_flag);
     ph_mma ^= 1;
     tc_fence_after();
-    const long long c1 = (a.prof && tid == 0) ? clock64() : 0;
     if (tid == 0 && t + 1 < n_tiles) {             // stage st^1 is free: S(t) and PV(t-1) are complete
       mbar_expect_tx(&bar_full[st ^ 1], 2 * L::kT);
       tma_load_4d(sK + (st ^ 1) * L::kT, &tmK, &bar_full[st ^ 1], 0, tile0 + 128, h, b);
@@ -186,7 +183,6 @@ k_tc_lat(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       if (grow) m_run = tmax;
     }
 
-    const long long c2 = (a.prof && tid == 0) ? clock64() : 0;
     // one exponential per score; weights packed two per column over S
     float lsum = 0.f;
     for (int cc = 0; cc < 4; ++cc) {
@@ -216,7 +212,6 @@ k_tc_lat(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       tmem_st16(p_base + c * 16, pk);
     }
     l_run += lsum;
-    const long long c3 = (a.prof && tid == 0) ? clock64() : 0;
     tmem_wait_st();
     tc_fence_before();
     __syncthreads();
@@ -239,15 +234,6 @@ k_tc_lat(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
           mma_ss(tmem + (st ? 0 : 64), dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
       }
       mma_commit(bar_mma);
-    }
-    if (a.prof && tid == 0) {
-      const long long c4 = clock64();
-      const int o = MODE ? 8 : 0;
-      atomicAdd((unsigned long long*)&a.prof[o + 0], (unsigned long long)(c1 - c0));   // wait for products
-      atomicAdd((unsigned long long*)&a.prof[o + 1], (unsigned long long)(c2 - c1));   // barrier + max pass
-      atomicAdd((unsigned long long*)&a.prof[o + 2], (unsigned long long)(c3 - c2));   // exponentials + stores
-      atomicAdd((unsigned long long*)&a.prof[o + 3], (unsigned long long)(c4 - c3));   // drain + barrier + issue
-      atomicAdd((unsigned long long*)&a.prof[o + 4], 1ull);
     }
     if (aborted) break;
   }
@@ -307,14 +293,8 @@ static int launch_lat(const Ctx& c, const void* q, const void* k, const void* v,
   a.n_splits = c.n_splits; a.chunk = c.chunk; a.n_mblk = (c.M + 127) / 128;
   a.lse_n = lse_n; a.out = out;
   a.status = tc_status_ptr();
-  a.prof = tc_phase_counters();
-  static bool attr_done = false;
   constexpr int smem = LatSmem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_lat<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_lat<D, MODE>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * a.n_mblk * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   k_tc_lat<D, MODE><<<(unsigned)grid, 128, smem, st>>>(tmQ, tmK, tmV, a);

@@ -21,7 +21,11 @@
 //     tile's C_n row rides on the same mbarrier as an untiled bulk copy.
 //   * The softmax threads read their 64 columns in four chunks of 16, one chunk ahead of the
 //     arithmetic, so that few registers are live and the MUFU stays fed.
-// Two CTAs (288 threads each) share an SM.
+//   * A key-padding mask (and the ragged end of a range) reaches the softmax threads as one keep bit
+//     per token of the tile, published with the norm bound; excluded tokens get probability zero and
+//     do not enter the exact maximum.
+// Two CTAs (288 threads each) share an SM.  bf16 or fp16 operands (fp16 probabilities must stay below
+// 2^15, so its running maximum may lag the true one by 2^14 at most instead of 2^60).
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -40,6 +44,7 @@ struct Lat2Args {
   float* out;                  // MODE 0: rec [S,B,H,M,D+2]; MODE 1: dz_part [S,B,H,M,D]
   int* status;
   int c_bulk;                  // MODE 1: C_n rows may be fetched with 16-byte-aligned bulk copies
+  const uint8_t* mask;         // [B,N] key-padding mask (non-zero = keep) or null
 };
 
 constexpr int kLat2Stages = 4;
@@ -50,7 +55,7 @@ struct Lat2Smem {
   static constexpr int kQ = 128 * ROWB;
   static constexpr int kT = 128 * ROWB;            // one K or V tile
   static constexpr int kBytes = kQ + 2 * kLat2Stages * kT + kLat2Stages * 128 * 4 /*C*/ + 2 * 128 * 4 /*max*/ +
-                                128 * 4 /*l*/ + 64 /*kmax*/ + 1024 + 256;
+                                128 * 4 /*l*/ + 64 /*kmax*/ + 64 /*keep bits*/ + 1024 + 256;
 };
 
 __device__ __forceinline__ void mbar_arrive_l2(uint64_t* bar) {
@@ -69,10 +74,10 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 constexpr int kLat2Softmax = 256;
 
 // One chunk of 16 score columns of one row: P = 2^(S sl - m) (MODE 0) or 2^(S sl - C2) (MODE 1, C2 = C log2e),
-// packed to bf16 pairs; the two running sums take alternate columns.
-template <int MODE, bool MASKED>
-__device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_run, const float* c16, int col0,
-                                           int cnt, uint32_t* pk, float& s0, float& s1) {
+// packed to 16-bit pairs; the two running sums take alternate columns.  kbits: keep bit of each column.
+template <int MODE, bool MASKED, typename T16>
+__device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_run, const float* c16, uint32_t kbits,
+                                           uint32_t* pk, float& s0, float& s1) {
   float cv[16];
   if (MODE == 1) {
 #pragma unroll
@@ -93,11 +98,11 @@ __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_
     }
     float e0 = ex2(x0), e1 = ex2(x1);
     if (MASKED) {
-      if (col0 + 2 * j >= cnt) e0 = 0.f;
-      if (col0 + 2 * j + 1 >= cnt) e1 = 0.f;
+      if (!(kbits & (1u << (2 * j)))) e0 = 0.f;
+      if (!(kbits & (2u << (2 * j)))) e1 = 0.f;
     }
     s0 += e0; s1 += e1;
-    pk[j] = pack_bf16(e0, e1);
+    pk[j] = Op16<T16>::pack(e0, e1);
   }
 }
 
@@ -105,33 +110,34 @@ __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_
 // Even tiles walk the chunks upwards and odd tiles downwards, so that the packed P of a chunk
 // never lands on score columns that are still to be loaded (P sits in the lower half of the 64
 // columns on even tiles, in the upper half on odd ones).  Registers are indexed statically; only
-// addresses depend on the direction.
-template <int MODE, bool MASKED>
+// addresses depend on the direction.  keep: one bit per column of this thread's 64.
+template <int MODE, bool MASKED, typename T16>
 __device__ __forceinline__ float lat2_row(uint32_t s_cols, uint32_t p_cols, int p, float sl, float m_run,
-                                          const float* c64, int col_half, int cnt) {
+                                          const float* c64, uint64_t keep) {
   uint32_t ra[16], rb[16], pk[8];
   float s0 = 0.f, s1 = 0.f;
   const int c0 = p ? 3 : 0, dc = p ? -1 : 1;
+  auto kb = [&](int c) { return (uint32_t)(keep >> (16 * c)) & 0xffffu; };
   tmem_ld16(s_cols + 16 * c0, ra);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + dc), rb);
-  lat2_chunk<MODE, MASKED>(ra, sl, m_run, c64 + 16 * c0, col_half + 16 * c0, cnt, pk, s0, s1);
+  lat2_chunk<MODE, MASKED, T16>(ra, sl, m_run, c64 + 16 * c0, kb(c0), pk, s0, s1);
   tmem_st8(p_cols + 8 * c0, pk);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + 2 * dc), ra);
-  lat2_chunk<MODE, MASKED>(rb, sl, m_run, c64 + 16 * (c0 + dc), col_half + 16 * (c0 + dc), cnt, pk, s0, s1);
+  lat2_chunk<MODE, MASKED, T16>(rb, sl, m_run, c64 + 16 * (c0 + dc), kb(c0 + dc), pk, s0, s1);
   tmem_st8(p_cols + 8 * (c0 + dc), pk);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + 3 * dc), rb);
-  lat2_chunk<MODE, MASKED>(ra, sl, m_run, c64 + 16 * (c0 + 2 * dc), col_half + 16 * (c0 + 2 * dc), cnt, pk, s0, s1);
+  lat2_chunk<MODE, MASKED, T16>(ra, sl, m_run, c64 + 16 * (c0 + 2 * dc), kb(c0 + 2 * dc), pk, s0, s1);
   tmem_st8(p_cols + 8 * (c0 + 2 * dc), pk);
   tmem_wait_ld();
-  lat2_chunk<MODE, MASKED>(rb, sl, m_run, c64 + 16 * (c0 + 3 * dc), col_half + 16 * (c0 + 3 * dc), cnt, pk, s0, s1);
+  lat2_chunk<MODE, MASKED, T16>(rb, sl, m_run, c64 + 16 * (c0 + 3 * dc), kb(c0 + 3 * dc), pk, s0, s1);
   tmem_st8(p_cols + 8 * (c0 + 3 * dc), pk);
   return s0 + s1;
 }
 
-template <int D, int MODE>
+template <int D, int MODE, typename T16>
 __global__ void __launch_bounds__(kLat2Softmax + 32, 2)
 k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, Lat2Args a) {
@@ -148,7 +154,8 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   float* sMax = sC + NS * 128;                     // [2][128] half-row maxima (exact pass)
   float* sLsum = sMax + 2 * 128;                   // [128]
   float* sKmax = sLsum + 128;                      // [NS] max_n |k_n|^2 of the tile in each stage
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sKmax + 16);
+  uint32_t* sKeep = reinterpret_cast<uint32_t*>(sKmax + 16);   // [NS][4] keep bits of the tile's 128 tokens
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKeep + 16);
   uint64_t* bar_full = bars;                       // [NS]
   uint64_t* bar_s = bars + NS;                     // [2] S(t) complete
   uint64_t* bar_pv = bar_s + 2;                    // [2] P(t) V(t) complete
@@ -200,6 +207,14 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   constexpr uint32_t kAcc = 224;
   const float* cb = (MODE == 1) ? a.lse_n + ((long long)b * a.H + h) * a.N : nullptr;
   const bool c_bulk = (MODE == 1) && a.c_bulk;
+  const uint8_t* mrow = a.mask ? a.mask + (long long)b * a.N : nullptr;
+  // lazy running maximum: how far (log2 units) the tile's score bound may exceed it before the exact pass
+  constexpr float kLag = (sizeof(T16) == 2 && Op16<T16>::kFmt == 0) ? 14.f : 60.f;
+  // keep bits of one 32-token quarter of a tile: token in range and not masked out (full warp)
+  auto keep_word = [&](int tok) -> uint32_t {
+    const bool k1 = tok < n1 && (!mrow || mrow[tok] != 0);
+    return __ballot_sync(0xffffffffu, k1);
+  };
 
   if (is_issuer) {
     // ================================ issuer warp ================================
@@ -215,6 +230,14 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     };
     // max_n |k_n|^2 of a landed tile (rows past the end are zero-filled), published to the softmax
     // threads through bar_k; lane l takes rows l, l+32, l+64, l+96
+    auto tile_keep = [&](int t) {
+      const int tile0 = n0 + t * 128;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t w = keep_word(tile0 + 32 * i + lane);
+        if (lane == 0) sKeep[(t % NS) * 4 + i] = w;
+      }
+    };
     auto tile_kmax = [&](int t) {
       const int st = t % NS;
       float mx = 0.f;
@@ -224,14 +247,15 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 #pragma unroll
         for (int c = 0; c < CPR; ++c) {
           const uint4 k4 = *reinterpret_cast<const uint4*>(sK + st * L::kT + swz_off<ROWB>(lane + 32 * i, c));
-          const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&k4);
+          const uint32_t* kp = reinterpret_cast<const uint32_t*>(&k4);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(kp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
+          for (int j = 0; j < 4; ++j) { const float2 f = Op16<T16>::unpack(kp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
         }
         mx = fmaxf(mx, s2);
       }
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      tile_keep(t);
       if (lane == 0) { sKmax[st] = mx; mbar_arrive_l2(&bar_k[t & 1]); }
       __syncwarp();
     };
@@ -243,13 +267,15 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       float4 c = *c4;
       c.x *= kLog2e; c.y *= kLog2e; c.z *= kLog2e; c.w *= kLog2e;
       *c4 = c;
+      tile_keep(t);
       __syncwarp();
       if (lane == 0) mbar_arrive_l2(&bar_k[t & 1]);
       __syncwarp();
     };
 
-    const uint32_t idesc_s = idesc_f16(128, 128, 1, 1, 0, 0);
-    const uint32_t idesc_pv = idesc_f16(128, D, 1, 1, 0, 1);
+    constexpr int F = Op16<T16>::kFmt;
+    const uint32_t idesc_s = idesc_f16(128, 128, F, F, 0, 0);
+    const uint32_t idesc_pv = idesc_f16(128, D, F, F, 0, 1);
     const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
     if (elect_one()) {
       mbar_expect_tx(bar_q, L::kQ);
@@ -329,9 +355,9 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 #pragma unroll
       for (int c = 0; c < CPR; ++c) {
         const uint4 q4 = *reinterpret_cast<const uint4*>(sQ + swz_off<ROWB>(row, c));
-        const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(&q4);
+        const uint32_t* qp = reinterpret_cast<const uint32_t*>(&q4);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(qp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
+        for (int j = 0; j < 4; ++j) { const float2 f = Op16<T16>::unpack(qp[j]); s2 = fmaf(f.x, f.x, s2); s2 = fmaf(f.y, f.y, s2); }
       }
       qn = sqrtf(s2) * sl * 1.0001f;
     }
@@ -348,7 +374,11 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
           mbar_wait(&bar_k[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
         } else {
           mbar_wait(&bar_full[st], (uint32_t)(t / NS) & 1, a.status, abort_flag);
-          if (tid < 128) sC[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] * kLog2e : 0.f;
+          if (tid < 128) {
+            sC[st * 128 + tid] = (tid < cnt) ? cb[tile0 + tid] * kLog2e : 0.f;
+            const uint32_t w = keep_word(tile0 + tid);
+            if (lane == 0) sKeep[st * 4 + warp] = w;
+          }
           named_bar_sync(2, kLat2Softmax);
         }
       } else {
@@ -358,11 +388,13 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
       mbar_wait_hot(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
+      const uint64_t keep = (uint64_t)sKeep[st * 4 + 2 * half] | ((uint64_t)sKeep[st * 4 + 2 * half + 1] << 32);
+      const bool masked = keep != ~0ull;
       const uint32_t s_cols = lane_base + (p ? 96 : 0) + 64 * half;   // this thread's 64 score columns
       const uint32_t p_cols = s_cols + (p ? 32 : 0);                  // where their packed P goes
 
       if (MODE == 0) {
-        const bool need = (t == 0) || (bound > m_run + 60.f);
+        const bool need = (t == 0) || (bound > m_run + kLag);
         if (__any_sync(0xffffffffu, need)) {       // the partner warp holds the same rows: same vote
           float mx = -INFINITY;
           for (int i = 0; i < 4; ++i) {
@@ -371,7 +403,7 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
             tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              mx = fmaxf(mx, (64 * half + 16 * i + j < cnt) ? __uint_as_float(r[j]) : -INFINITY);
+              mx = fmaxf(mx, ((keep >> (16 * i + j)) & 1) ? __uint_as_float(r[j]) : -INFINITY);
           }
           sMax[half * 128 + row] = mx;
           named_bar_sync(3 + (warp & 3), 64);      // the two warps of this lane quarter
@@ -398,8 +430,8 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
       // ---- one exponential per score; P packed inside this thread's own columns ----------------
       const float* c64 = sC + st * 128 + 64 * half;
-      if (cnt == 128) l_run += lat2_row<MODE, false>(s_cols, p_cols, p, sl, m_run, c64, 64 * half, cnt);
-      else            l_run += lat2_row<MODE, true>(s_cols, p_cols, p, sl, m_run, c64, 64 * half, cnt);
+      if (!masked) l_run += lat2_row<MODE, false, T16>(s_cols, p_cols, p, sl, m_run, c64, keep);
+      else         l_run += lat2_row<MODE, true, T16>(s_cols, p_cols, p, sl, m_run, c64, keep);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_l2(&bar_sm[p]);
@@ -442,21 +474,22 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
 // ------------------------------------------------------------------------------------------
 bool tc_lat2_supported(const Ctx& c, int dtype) {
-  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.N >= 1 && c.M >= 1;
+  return (dtype == FLARE_BF16 || dtype == FLARE_F16) && (c.D == 16 || c.D == 32) && c.N >= 1 && c.M >= 1;
 }
 
-template <int D, int MODE>
-static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v, const float* lse_n, float* out,
-                       cudaStream_t st) {
+template <int D, int MODE, typename T16>
+static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v, const uint8_t* mask, const float* lse_n,
+                       float* out, cudaStream_t st) {
   CUtensorMap tmQ, tmK, tmV;
   const uint64_t e = 2;
+  constexpr int F = Op16<T16>::kFmt;
   const bool qb = c.qs[0] != 0;
   const long long* vs = (MODE == 0) ? c.vs : c.dys;
-  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
+  if (!make_tile_map(&tmQ, q, F, D, (uint64_t)c.M, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e, c.qs[1] * e,
                      (qb ? c.qs[0] : c.qs[1] * c.H) * e, 128) ||
-      !make_tile_map(&tmK, k, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
+      !make_tile_map(&tmK, k, F, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
                      (c.B > 1 ? c.ks[0] : c.ks[1] * c.H) * e, 128) ||
-      !make_tile_map(&tmV, v, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, vs[2] * e, vs[1] * e,
+      !make_tile_map(&tmV, v, F, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, vs[2] * e, vs[1] * e,
                      (c.B > 1 ? vs[0] : vs[1] * c.H) * e, 128))
     return FLARE_EUNSUPPORTED;
   Lat2Args a;
@@ -467,34 +500,36 @@ static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v
   a.lse_n = lse_n; a.out = out;
   a.status = tc_status_ptr();
   a.c_bulk = (MODE == 1 && lse_n && (reinterpret_cast<uintptr_t>(lse_n) & 15) == 0 && (c.N & 3) == 0) ? 1 : 0;
-  static bool attr_done = false;
+  a.mask = mask;
   constexpr int smem = Lat2Smem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_lat2<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_lat2<D, MODE, T16>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * a.n_mblk * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_lat2<D, MODE><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
+  k_tc_lat2<D, MODE, T16><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
   return FLARE_OK;
 }
 
-int tc_gather_partial2(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st) {
+template <int MODE>
+static int dispatch_lat2(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const uint8_t* mask,
+                         const float* lse_n, float* out, cudaStream_t st) {
+  const bool bf = dtype == FLARE_BF16;
   switch (c.D) {
-    case 16: return launch_lat2<16, 0>(c, q, k, v, nullptr, rec, st);
-    case 32: return launch_lat2<32, 0>(c, q, k, v, nullptr, rec, st);
+    case 16: return bf ? launch_lat2<16, MODE, __nv_bfloat16>(c, q, k, v, mask, lse_n, out, st)
+                       : launch_lat2<16, MODE, __half>(c, q, k, v, mask, lse_n, out, st);
+    case 32: return bf ? launch_lat2<32, MODE, __nv_bfloat16>(c, q, k, v, mask, lse_n, out, st)
+                       : launch_lat2<32, MODE, __half>(c, q, k, v, mask, lse_n, out, st);
   }
   return FLARE_EUNSUPPORTED;
 }
 
-int tc_dz_partial2(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,
-                   cudaStream_t st) {
-  switch (c.D) {
-    case 16: return launch_lat2<16, 1>(c, q, k, dy, lse_n, dz_part, st);
-    case 32: return launch_lat2<32, 1>(c, q, k, dy, lse_n, dz_part, st);
-  }
-  return FLARE_EUNSUPPORTED;
+int tc_gather_partial2(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const uint8_t* mask,
+                       float* rec, cudaStream_t st) {
+  return dispatch_lat2<0>(c, dtype, q, k, v, mask, nullptr, rec, st);
+}
+
+int tc_dz_partial2(const Ctx& c, int dtype, const void* q, const void* k, const void* dy, const uint8_t* mask,
+                   const float* lse_n, float* dz_part, cudaStream_t st) {
+  return dispatch_lat2<1>(c, dtype, q, k, dy, mask, lse_n, dz_part, st);
 }
 
 }  // namespace flare

@@ -22,7 +22,6 @@ namespace flare {
 
 using namespace tc;
 
-__device__ int g_tc_status = 0;
 
 struct ScatterArgs {
   int B, H, N, M;
@@ -224,36 +223,6 @@ bool tc_scatter_supported(const Ctx& c, int dtype) {
          c.M % 32 == 0 && c.N >= 1;
 }
 
-// Address of the status word on the current device (looked up once per device).
-int* tc_status_ptr() {
-  static int* ptrs[64] = {nullptr};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return nullptr;
-  if (!ptrs[dev]) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_tc_status) != cudaSuccess) return nullptr;
-    ptrs[dev] = static_cast<int*>(p);
-  }
-  return ptrs[dev];
-}
-
-// Optional phase counters for the tensor-core kernels (8 x int64 on the device), off by default.
-static long long* g_phase_counters = nullptr;
-void tc_set_phase_counters(long long* dev_ptr) { g_phase_counters = dev_ptr; }
-long long* tc_phase_counters() { return g_phase_counters; }
-
-int num_sms() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
 template <int D>
 static int launch_scatter_d(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask,
                             void* y, float* lse_n, cudaStream_t st) {
@@ -276,13 +245,8 @@ static int launch_scatter_d(const Ctx& c, const void* q, const void* k, const fl
   a.tiles_per_bh = (c.N + 127) / 128;
   a.total_tiles = (long long)a.tiles_per_bh * c.B * c.H;
   a.status = tc_status_ptr();
-  static bool attr_done = false;
   constexpr int smem = ScatterSmem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_scatter<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_scatter<D>), smem) != FLARE_OK) return FLARE_ECUDA;
   long long grid = 2LL * num_sms();
   if (grid > a.total_tiles) grid = a.total_tiles;
   k_tc_scatter<D><<<(unsigned)grid, 128, smem, st>>>(tmK, tmQ, a);
@@ -297,17 +261,6 @@ int tc_scatter(const Ctx& c, const void* q, const void* k, const float* z32, con
     case 64: return launch_scatter_d<64>(c, q, k, z32, mask, y, lse_n, st);
   }
   return FLARE_EUNSUPPORTED;
-}
-
-int tc_read_status(int* out, bool clear) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)) != cudaSuccess) return FLARE_ECUDA;
-  if (clear && v) {
-    int z = 0;
-    if (cudaMemcpyToSymbol(g_tc_status, &z, sizeof(int)) != cudaSuccess) return FLARE_ECUDA;
-  }
-  *out = v;
-  return FLARE_OK;
 }
 
 }  // namespace flare

@@ -14,7 +14,7 @@
 // so the tensor core works on tile t+1 and the epilogue on tile t-1 while the exponentials of tile t
 // run.  Buffer layout (256 columns): S^T at [0, M); half hf of a row packs A^T at [128hf, 128hf+64); Y goes
 // to [64, 64+D), columns of half 0 that are dead by then.  K tiles arrive in a three-stage TMA ring.
-// Requires bf16, D in {16, 32}, M a multiple of 32 in [32, 256].
+// Requires bf16 or fp16, D in {16, 32}, M a multiple of 32 in [32, 256] per launch (more latents: blocks of 256).
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -31,7 +31,7 @@ struct Scatter2Args {
   int n_splits, chunk;
   const float* z32;            // [B,H,M,D]
   const uint8_t* mask;         // [B,N] or null
-  __nv_bfloat16* y;
+  void* y;                     // 16-bit rows
   long long ys[3];
   float* lse_n;                // [B,H,N] or null
   long long z_bh_stride;       // floats between the z32 blocks of consecutive (b, h)
@@ -57,7 +57,7 @@ __device__ __forceinline__ void named_bar_sync_s2(int id, int nthreads) {
 
 constexpr int kS2Softmax = 512, kS2Epilogue = 128;
 
-template <int D>
+template <int D, typename T16>
 __global__ void __launch_bounds__(kS2Softmax + kS2Epilogue + 32, 1)
 k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ, Scatter2Args a) {
   constexpr int ROWB = 2 * D;
@@ -119,8 +119,8 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
       const float4 lo = *reinterpret_cast<const float4*>(zb + r * D + c * 8);
       const float4 hi = *reinterpret_cast<const float4*>(zb + r * D + c * 8 + 4);
       uint4 pk;
-      pk.x = pack_bf16(lo.x, lo.y); pk.y = pack_bf16(lo.z, lo.w);
-      pk.z = pack_bf16(hi.x, hi.y); pk.w = pack_bf16(hi.z, hi.w);
+      pk.x = Op16<T16>::pack(lo.x, lo.y); pk.y = Op16<T16>::pack(lo.z, lo.w);
+      pk.z = Op16<T16>::pack(hi.x, hi.y); pk.w = Op16<T16>::pack(hi.z, hi.w);
       *reinterpret_cast<uint4*>(sZ + swz_off<ROWB>(r, c)) = pk;
     }
   }
@@ -131,8 +131,9 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
     // ================================ issuer warp ================================
     // The whole warp runs this code; one elected lane executes each TMA / MMA / commit.
     {
-      const uint32_t idesc1 = idesc_f16(128, M, 1, 1, 0, 0);
-      const uint32_t idesc2 = idesc_f16(128, D, 1, 1, 0, 1);
+      constexpr int F = Op16<T16>::kFmt;
+      const uint32_t idesc1 = idesc_f16(128, M, F, F, 0, 0);
+      const uint32_t idesc2 = idesc_f16(128, D, F, F, 0, 1);
       const uint64_t dq = smem_desc<ROWB>(smem_u32(sQ));
       const uint64_t dz = smem_desc<ROWB>(smem_u32(sZ));
       const int ksteps = M / 16;
@@ -224,7 +225,7 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
           const float e0 = ex2(fmaf(__uint_as_float(r[2 * j]), sl, off));
           const float e1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), sl, off));
           sum += e0 + e1;
-          pk[j] = pack_bf16(e0, e1);
+          pk[j] = Op16<T16>::pack(e0, e1);
         }
         tmem_st16(cols + 16 * c, pk);
       }
@@ -258,7 +259,7 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         const bool keep = !a.mask || a.mask[(long long)b * a.N + tok];
         float inv = keep ? 1.f / sum : 0.f;
         float c_new = (rmax * sl + log2f(sum)) * kLn2;
-        __nv_bfloat16* yp = a.y + b * a.ys[0] + h * a.ys[1] + (long long)tok * a.ys[2];
+        uint16_t* yp = static_cast<uint16_t*>(a.y) + b * a.ys[0] + h * a.ys[1] + (long long)tok * a.ys[2];
         float w_old = 0.f;
         if (a.accumulate) {
           // this launch covers one block of the latents: y = w_old y_old + w_new y_block, C = logaddexp
@@ -277,16 +278,16 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
           for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * c + j]) * inv;
           if (a.accumulate) {
             const uint4 old = reinterpret_cast<const uint4*>(yp)[c];
-            const __nv_bfloat162* op = reinterpret_cast<const __nv_bfloat162*>(&old);
+            const uint32_t* op = reinterpret_cast<const uint32_t*>(&old);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float2 of = __bfloat1622float2(op[j]);
+              const float2 of = Op16<T16>::unpack(op[j]);
               f[2 * j] = fmaf(w_old, of.x, f[2 * j]); f[2 * j + 1] = fmaf(w_old, of.y, f[2 * j + 1]);
             }
           }
           uint4 o;
-          o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
-          o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+          o.x = Op16<T16>::pack(f[0], f[1]); o.y = Op16<T16>::pack(f[2], f[3]);
+          o.z = Op16<T16>::pack(f[4], f[5]); o.w = Op16<T16>::pack(f[6], f[7]);
           reinterpret_cast<uint4*>(yp)[c] = o;
         }
         if (a.lse_n) a.lse_n[((long long)b * a.H + h) * a.N + tok] = c_new;
@@ -301,16 +302,18 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
 // ------------------------------------------------------------------------------------------
 bool tc_scatter2_supported(const Ctx& c, int dtype) {
   // more than 256 latents run as blocks of 256, each launch merging into y and C_n (needs C_n storage)
-  return dtype == FLARE_BF16 && (c.D == 16 || c.D == 32) && c.M >= 32 && c.M <= 1024 && c.M % 32 == 0 && c.N >= 1;
+  return (dtype == FLARE_BF16 || dtype == FLARE_F16) && (c.D == 16 || c.D == 32) && c.M >= 32 && c.M <= 1024 &&
+         c.M % 32 == 0 && c.N >= 1;
 }
 
-template <int D>
+template <int D, typename T16>
 static int launch_scatter2(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask,
                            void* y, float* lse_n, cudaStream_t st) {
   CUtensorMap tmK;
   const uint64_t e = 2;
   if (c.M > 256 && !lse_n) return FLARE_EUNSUPPORTED;
-  if (!make_tile_map(&tmK, k, 1, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
+  constexpr int F = Op16<T16>::kFmt;
+  if (!make_tile_map(&tmK, k, F, D, (uint64_t)c.N, (uint64_t)c.H, (uint64_t)c.B, c.ks[2] * e, c.ks[1] * e,
                      (c.B > 1 ? c.ks[0] : c.ks[1] * c.H) * e, 128))
     return FLARE_EUNSUPPORTED;
   const bool qb = c.qs[0] != 0;
@@ -327,40 +330,38 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
   a.scale_log2 = c.scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
   a.n_splits = (int)splits; a.chunk = (int)chunk;
-  a.mask = mask; a.y = reinterpret_cast<__nv_bfloat16*>(y);
+  a.mask = mask; a.y = y;
   a.z_bh_stride = (long long)c.M * D;
   for (int i = 0; i < 3; ++i) a.ys[i] = c.ys[i];
   a.lse_n = lse_n;
   a.status = tc_status_ptr();
-  static bool attr_done = false;
   constexpr int smem = Scatter2Smem<D>::kBytes;
-  if (!attr_done) {
-    if (cudaFuncSetAttribute(k_tc_scatter2<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return FLARE_ECUDA;
-    attr_done = true;
-  }
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_scatter2<D, T16>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = splits * bh;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   for (int m0 = 0; m0 < c.M; m0 += 256) {
     const int mb = c.M - m0 < 256 ? c.M - m0 : 256;
     CUtensorMap tmQ;
     const char* qblk = static_cast<const char*>(q) + (long long)m0 * c.qs[2] * e;
-    if (!make_tile_map(&tmQ, qblk, 1, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e,
+    if (!make_tile_map(&tmQ, qblk, F, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e,
                        c.qs[1] * e, (qb ? c.qs[0] : c.qs[1] * c.H) * e, (uint32_t)mb))
       return FLARE_EUNSUPPORTED;
     a.M = mb;
     a.z32 = z32 + (long long)m0 * D;
     a.accumulate = m0 > 0 ? 1 : 0;
-    k_tc_scatter2<D><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+    k_tc_scatter2<D, T16><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
   }
   return FLARE_OK;
 }
 
-int tc_scatter2(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
+int tc_scatter2(const Ctx& c, int dtype, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
                 float* lse_n, cudaStream_t st) {
+  const bool bf = dtype == FLARE_BF16;
   switch (c.D) {
-    case 16: return launch_scatter2<16>(c, q, k, z32, mask, y, lse_n, st);
-    case 32: return launch_scatter2<32>(c, q, k, z32, mask, y, lse_n, st);
+    case 16: return bf ? launch_scatter2<16, __nv_bfloat16>(c, q, k, z32, mask, y, lse_n, st)
+                       : launch_scatter2<16, __half>(c, q, k, z32, mask, y, lse_n, st);
+    case 32: return bf ? launch_scatter2<32, __nv_bfloat16>(c, q, k, z32, mask, y, lse_n, st)
+                       : launch_scatter2<32, __half>(c, q, k, z32, mask, y, lse_n, st);
   }
   return FLARE_EUNSUPPORTED;
 }

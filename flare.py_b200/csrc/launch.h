@@ -35,7 +35,7 @@ int tc_scatter(const Ctx& c, const void* q, const void* k, const float* z32, con
                float* lse_n, cudaStream_t st);
 // decoupled-schedule scatter (one CTA per SM, two tiles in flight; D <= 32)
 bool tc_scatter2_supported(const Ctx& c, int dtype);
-int tc_scatter2(const Ctx& c, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
+int tc_scatter2(const Ctx& c, int dtype, const void* q, const void* k, const float* z32, const uint8_t* mask, void* y,
                 float* lse_n, cudaStream_t st);
 bool tc_lat_supported(const Ctx& c, int dtype);
 int tc_gather_partial(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st);
@@ -43,32 +43,31 @@ int tc_dz_partial(const Ctx& c, const void* q, const void* k, const void* dy, co
                   cudaStream_t st);
 // decoupled-schedule versions of the two latent-major passes (D <= 32)
 bool tc_lat2_supported(const Ctx& c, int dtype);
-int tc_gather_partial2(const Ctx& c, const void* q, const void* k, const void* v, float* rec, cudaStream_t st);
-int tc_dz_partial2(const Ctx& c, const void* q, const void* k, const void* dy, const float* lse_n, float* dz_part,
-                   cudaStream_t st);
+int tc_gather_partial2(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const uint8_t* mask,
+                       float* rec, cudaStream_t st);
+int tc_dz_partial2(const Ctx& c, int dtype, const void* q, const void* k, const void* dy, const uint8_t* mask,
+                   const float* lse_n, float* dz_part, cudaStream_t st);
 bool tc_bwd_supported(const Ctx& c, int dtype);
-int tc_bwd_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
-                const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                float* dq_part, const int* flag, cudaStream_t st);
+// the general tensor-core backward: bf16/fp16, mask, either softmax term, latents in blocks of 256;
+// flag (or null): run only the (b, h) whose flag is 1
+int tc_bwd_main(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                const uint8_t* mask, const float* z32, const float* dz32, const float* lse_m, const float* lse_n,
+                void* dk, void* dv, float* dq_part, const int* flag, cudaStream_t st);
 // One-exponential form of the same pass plus the on-device range check that selects, per (b, h),
 // between it (flag 0) and the exact kernel above (flag 1).
 size_t tc_bwd2_scratch_bytes(const Ctx& c);
 int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                  const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                  float* dq_part, void* scratch, const int** flag_out, cudaStream_t st);
-bool tc_bwd3_supported(const Ctx& c, int dtype);
-int tc_bwd3_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
-                   const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                   float* dq_part, const float* mu, const int* flag, cudaStream_t st);
 // the same pass in 128-latent steps (two per token tile): S^T double-buffered, T' single
 bool tc_bwd4_supported(const Ctx& c, int dtype);
 int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                    const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* dq_part, const float* mu, const int* flag, cudaStream_t st);
+// per-device host state (tc_runtime.cu)
 int tc_read_status(int* out, bool clear);
 int* tc_status_ptr();
-void tc_set_phase_counters(long long* dev_ptr);
-long long* tc_phase_counters();
 int num_sms();
+int tc_set_dyn_smem(const void* kernel, int bytes);
 
 }  // namespace flare

@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 
 namespace flare {
@@ -235,6 +236,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&t);
 }
+
+// The two 16-bit operand types of kind::f16 products.  kFmt is the format code of the instruction
+// descriptor and of make_tile_map; pack/unpack move a pair of values between fp32 and one 32-bit word.
+template <typename T> struct Op16;
+template <> struct Op16<__nv_bfloat16> {
+  static constexpr int kFmt = 1;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) { return pack_bf16(lo, hi); }
+  static __device__ __forceinline__ float2 unpack(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+};
+template <> struct Op16<__half> {
+  static constexpr int kFmt = 0;
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+  static __device__ __forceinline__ float2 unpack(uint32_t w) { return __half22float2(*reinterpret_cast<__half2*>(&w)); }
+};
 
 __device__ __forceinline__ float ex2(float x) {
   float y;

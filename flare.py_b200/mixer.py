@@ -23,7 +23,8 @@ from ._cabi import FlareProblem, check, lib, ptr, stream_of
 
 __all__ = [
     "flare_multihead_mixer", "flare_gather", "flare_scatter",
-    "mixer_forward", "mixer_backward", "make_problem", "set_kernel_path", "device_status",
+    "mixer_forward", "mixer_backward", "gather_forward", "gather_backward", "scatter_forward", "scatter_backward",
+    "make_problem", "set_kernel_path", "device_status", "pass_counts",
 ]
 
 
@@ -40,6 +41,13 @@ def device_status(clear: bool = True) -> int:
     out = C.c_int(0)
     check(lib.flare_device_status(C.byref(out), 1 if clear else 0), "flare_device_status")
     return out.value
+
+
+def pass_counts():
+    """(tensor-core passes, fp32-kernel passes) enqueued by this process so far."""
+    tc, simt = C.c_longlong(0), C.c_longlong(0)
+    check(lib.flare_pass_counts(C.byref(tc), C.byref(simt)), "flare_pass_counts")
+    return tc.value, simt.value
 
 
 def _need_cuda(*ts):
@@ -149,60 +157,9 @@ def mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale=1.0, key_mask=None):
     return dq, dk, dv
 
 
-class _MixerFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, scale, key_mask):
-        y, z32, lse_m, lse_n = mixer_forward(q, k, v, scale, key_mask)
-        ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n, key_mask)
-        ctx.scale = scale
-        return y
-
-    @staticmethod
-    def backward(ctx, dy):
-        q, k, v, y, z32, lse_m, lse_n, key_mask = ctx.saved_tensors
-        dq, dk, dv = mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, ctx.scale, key_mask)
-        return dq.to(q.dtype).reshape(q.shape), dk, dv, None, None
-
-
-def _fold_q(q):
-    # an expand()-ed q (stride 0 over the batch, pdebench/models/flare.py:136) is the shared-latent case
-    if q.dim() == 4 and q.stride(0) == 0:
-        return q[0]
-    return q
-
-
-def flare_multihead_mixer(q, k, v, scale: float = 1.0, key_mask: Optional[torch.Tensor] = None,
-                          dropout_p: float = 0.0):
-    """y[B,H,N,D] = SDPA(k, q, SDPA(q, k, v, scale), scale)   (README.md:37-53 of the reference).
-
-    q: [H,M,D] (or [B,H,M,D]); k, v: [B,H,N,D], any strides with unit stride on D.
-    key_mask: optional bool [B,N], True = token takes part (lra/models/backends.py:615-622);
-    masked tokens are ignored by the gather and their output rows are zero.
-    """
-    if dropout_p != 0.0:
-        raise NotImplementedError("attention dropout is not supported by the fused mixer (dropout_p must be 0)")
-    return _MixerFn.apply(_fold_q(q), k, v, float(scale), key_mask)
-
-
 # ------------------------------------------------------------------------------------
-# gather and scatter as separate differentiable operators
+# the two SDPA calls as separate passes (host side of flare_gather / flare_scatter)
 # ------------------------------------------------------------------------------------
-def _gather_fwd(q, k, v, scale, mask):
-    B, H, N, D = k.shape
-    M = q.shape[-2]
-    dev = k.device
-    z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
-    z = torch.empty(B, H, M, D, dtype=k.dtype, device=dev)
-    lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
-    p = make_problem(q, k, scale, v=v)
-    p.n_splits = lib.flare_pick_splits(C.byref(p))
-    rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
-    st = stream_of(k)
-    check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(mask), ptr(rec), st), "flare_gather_partial")
-    check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, ptr(z32), ptr(z), ptr(lse_m), None, st), "flare_combine")
-    return z, z32, lse_m
-
-
 def _dq_from_parts(p, part, B, H, M, D, batched, st):
     dq = torch.empty((B, H, M, D) if batched else (H, M, D), dtype=torch.float32, device=part.device)
     if batched:
@@ -212,97 +169,287 @@ def _dq_from_parts(p, part, B, H, M, D, batched, st):
     return dq
 
 
-class _GatherFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, v, scale, key_mask):
-        _need_cuda(q, k, v)
-        q, _ = _q3(q)
-        k, v = _tok(k), _tok(v)
-        mask = _mask_u8(key_mask, k.shape[0], k.shape[2], k.device)
-        with torch.cuda.device(k.device):
-            z, z32, lse_m = _gather_fwd(q, k, v, scale, mask)
-        ctx.save_for_backward(q, k, v, z32, lse_m, mask)
-        ctx.scale = scale
-        ctx.mark_non_differentiable(lse_m)
-        return z, lse_m
-
-    @staticmethod
-    def backward(ctx, dz, _dlse):
-        q, k, v, z32, lse_m, mask = ctx.saved_tensors
-        B, H, N, D = k.shape
-        M = q.shape[-2]
-        batched = q.dim() == 4
-        with torch.cuda.device(k.device):
-            dz32 = dz.to(torch.float32).contiguous()
-            dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-            dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
-            p = make_problem(q, k, ctx.scale, v=v, dk=dk, dv=dv)
-            p.n_splits = lib.flare_pick_splits(C.byref(p))
-            st = stream_of(k)
-            T = _cabi.TERM_GATHER
-            check(lib.flare_bwd_tokens(C.byref(p), T, ptr(q), ptr(k), ptr(v), None, None, ptr(mask), ptr(z32),
-                                       ptr(dz32), ptr(lse_m), None, ptr(dk), ptr(dv), None, st), "flare_bwd_tokens")
-            part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=k.device)
-            check(lib.flare_bwd_dq_partial(C.byref(p), T, ptr(q), ptr(k), ptr(v), None, ptr(mask), ptr(z32),
-                                           ptr(dz32), ptr(lse_m), None, None, ptr(part), st), "flare_bwd_dq_partial")
-            dq = _dq_from_parts(p, part, B, H, M, D, batched, st)
-        return dq.to(q.dtype), dk, dv, None, None
+def gather_forward(q, k, v, scale=1.0, key_mask=None):
+    """z (input dtype), z32, lse_m[B,H,M] via flare_gather_partial + flare_combine."""
+    _need_cuda(q, k, v)
+    q, _ = _q3(q)
+    k, v = _tok(k), _tok(v)
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    dev = k.device
+    mask = _mask_u8(key_mask, B, N, dev)
+    with torch.cuda.device(dev):
+        z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+        z = torch.empty(B, H, M, D, dtype=k.dtype, device=dev)
+        lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
+        p = make_problem(q, k, scale, v=v)
+        p.n_splits = lib.flare_pick_splits(C.byref(p))
+        rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
+        st = stream_of(k)
+        check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(mask), ptr(rec), st), "flare_gather_partial")
+        check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, ptr(z32), ptr(z), ptr(lse_m), None, st), "flare_combine")
+    return z, z32, lse_m
 
 
-class _ScatterFn(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, q, k, z, scale, key_mask):
-        _need_cuda(q, k, z)
-        q, _ = _q3(q)
-        k = _tok(k)
-        B, H, N, D = k.shape
-        mask = _mask_u8(key_mask, B, N, k.device)
-        with torch.cuda.device(k.device):
-            z32 = z.to(torch.float32).contiguous()
-            y = torch.empty_like(k)
-            if y.stride(-1) != 1:
-                y = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-            lse_n = torch.empty(B, H, N, dtype=torch.float32, device=k.device)
-            p = make_problem(q, k, scale, y=y)
-            check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), ptr(mask), ptr(y), ptr(lse_n),
-                                    stream_of(k)), "flare_scatter")
-        ctx.save_for_backward(q, k, z32, y, lse_n, mask)
-        ctx.scale = scale
-        ctx.z_dtype = z.dtype
-        return y
+def gather_backward(q, k, v, dz, z32, lse_m, scale=1.0, key_mask=None):
+    """dq (fp32), dk, dv of the gather alone (term 1 of the backward)."""
+    q, batched = _q3(q)
+    k, v = _tok(k), _tok(v)
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    mask = _mask_u8(key_mask, B, N, k.device)
+    with torch.cuda.device(k.device):
+        dz32 = dz.to(torch.float32).contiguous()
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
+        p = make_problem(q, k, scale, v=v, dk=dk, dv=dv)
+        p.n_splits = lib.flare_pick_splits(C.byref(p))
+        st = stream_of(k)
+        part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=k.device)
+        check(lib.flare_bwd_main(C.byref(p), _cabi.TERM_GATHER, ptr(q), ptr(k), ptr(v), None, None, ptr(mask), ptr(z32),
+                                 ptr(dz32), ptr(lse_m), None, ptr(dk), ptr(dv), None, ptr(part), st), "flare_bwd_main")
+        dq = _dq_from_parts(p, part, B, H, M, D, batched, st)
+    return dq, dk, dv
 
-    @staticmethod
-    def backward(ctx, dy):
-        q, k, z32, y, lse_n, mask = ctx.saved_tensors
-        B, H, N, D = k.shape
-        M = q.shape[-2]
-        batched = q.dim() == 4
-        with torch.cuda.device(k.device):
-            dy = _tok(dy)
-            dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
-            p = make_problem(q, k, ctx.scale, y=y, dy=dy, dk=dk)
-            p.n_splits = lib.flare_pick_splits(C.byref(p))
-            st = stream_of(k)
-            T = _cabi.TERM_SCATTER
-            part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=k.device)
-            dz32 = torch.empty(B, H, M, D, dtype=torch.float32, device=k.device)
-            delta = torch.empty(B, H, N, dtype=torch.float32, device=k.device)
-            check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), ptr(mask), ptr(lse_n), ptr(part), st),
-                  "flare_bwd_dz_partial")
-            check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
-            check(lib.flare_bwd_tokens(C.byref(p), T, ptr(q), ptr(k), None, ptr(dy), ptr(y), ptr(mask), ptr(z32),
-                                       None, None, ptr(lse_n), ptr(dk), None, ptr(delta), st), "flare_bwd_tokens")
-            check(lib.flare_bwd_dq_partial(C.byref(p), T, ptr(q), ptr(k), None, ptr(dy), ptr(mask), ptr(z32),
-                                           None, None, ptr(lse_n), ptr(delta), ptr(part), st), "flare_bwd_dq_partial")
-            dq = _dq_from_parts(p, part, B, H, M, D, batched, st)
-        return dq.to(q.dtype), dk, dz32.to(ctx.z_dtype), None, None
+
+def scatter_forward(q, k, z, scale=1.0, key_mask=None):
+    """y, lse_n[B,H,N] via flare_scatter."""
+    _need_cuda(q, k, z)
+    q, _ = _q3(q)
+    k = _tok(k)
+    B, H, N, D = k.shape
+    mask = _mask_u8(key_mask, B, N, k.device)
+    with torch.cuda.device(k.device):
+        z32 = z.to(torch.float32).contiguous()
+        y = torch.empty_like(k)
+        if y.stride(-1) != 1:
+            y = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        lse_n = torch.empty(B, H, N, dtype=torch.float32, device=k.device)
+        p = make_problem(q, k, scale, y=y)
+        check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), ptr(mask), ptr(y), ptr(lse_n), stream_of(k)),
+              "flare_scatter")
+    return y, lse_n
+
+
+def scatter_backward(q, k, z, dy, y, lse_n, scale=1.0, key_mask=None):
+    """dq (fp32), dk, dz (fp32) of the scatter alone (term 2 of the backward)."""
+    q, batched = _q3(q)
+    k, dy, y = _tok(k), _tok(dy), _tok(y)
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    mask = _mask_u8(key_mask, B, N, k.device)
+    with torch.cuda.device(k.device):
+        z32 = z.to(torch.float32).contiguous()
+        dk = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        p = make_problem(q, k, scale, y=y, dy=dy, dk=dk)
+        p.n_splits = lib.flare_pick_splits(C.byref(p))
+        st = stream_of(k)
+        part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=k.device)
+        dz32 = torch.empty(B, H, M, D, dtype=torch.float32, device=k.device)
+        delta = torch.empty(B, H, N, dtype=torch.float32, device=k.device)
+        check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), ptr(mask), ptr(lse_n), ptr(part), st),
+              "flare_bwd_dz_partial")
+        check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
+        check(lib.flare_bwd_main(C.byref(p), _cabi.TERM_SCATTER, ptr(q), ptr(k), None, ptr(dy), ptr(y), ptr(mask), ptr(z32),
+                                 None, None, ptr(lse_n), ptr(dk), None, ptr(delta), ptr(part), st), "flare_bwd_main")
+        dq = _dq_from_parts(p, part, B, H, M, D, batched, st)
+    return dq, dk, dz32
+
+
+# ------------------------------------------------------------------------------------
+# torch operators: opaque to torch.compile (fake kernels give the shapes), differentiable,
+# autocast-aware.  The reference runs this path under torch.compile and torch.autocast
+# (mlutils/trainer.py:135-137, 185; ablation/time_memory_bwd.py:460-470).
+# ------------------------------------------------------------------------------------
+Tensor = torch.Tensor
+
+
+def _like_tokens(k: Tensor) -> Tensor:
+    """What the kernels return for a [B,H,N,D] result: k's strides when those are addressable, else dense."""
+    e = k.element_size()
+    if k.stride(-1) == 1 and all((s * e) % 16 == 0 for s in k.stride()[:-1]):
+        out = torch.empty_like(k)
+        if out.stride(-1) == 1:
+            return out
+    return torch.empty(k.shape, dtype=k.dtype, device=k.device)
+
+
+def _dq_like(q: Tensor) -> Tensor:
+    return torch.empty(q.shape, dtype=torch.float32, device=q.device)
+
+
+@torch.library.custom_op("flare_b200::mixer_fwd", mutates_args=())
+def _op_mixer_fwd(q: Tensor, k: Tensor, v: Tensor, scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    return mixer_forward(q, k, v, scale, key_mask)
+
+
+@_op_mixer_fwd.register_fake
+def _(q, k, v, scale, key_mask):
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    f32 = dict(dtype=torch.float32, device=k.device)
+    return _like_tokens(k), torch.empty(B, H, M, D, **f32), torch.empty(B, H, M, **f32), torch.empty(B, H, N, **f32)
+
+
+@torch.library.custom_op("flare_b200::mixer_bwd", mutates_args=())
+def _op_mixer_bwd(q: Tensor, k: Tensor, v: Tensor, dy: Tensor, y: Tensor, z32: Tensor, lse_m: Tensor, lse_n: Tensor,
+                  scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    return mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask)
+
+
+@_op_mixer_bwd.register_fake
+def _(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask):
+    return _dq_like(q), _like_tokens(k), _like_tokens(v)
+
+
+def _mixer_setup(ctx, inputs, output):
+    q, k, v, scale, key_mask = inputs
+    y, z32, lse_m, lse_n = output
+    ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n, key_mask)
+    ctx.scale = scale
+
+
+def _mixer_backward(ctx, dy, _dz32, _dlm, _dln):
+    q, k, v, y, z32, lse_m, lse_n, key_mask = ctx.saved_tensors
+    dq, dk, dv = _op_mixer_bwd(q, k, v, dy, y, z32, lse_m, lse_n, ctx.scale, key_mask)
+    return dq.to(q.dtype), dk, dv, None, None
+
+
+_op_mixer_fwd.register_autograd(_mixer_backward, setup_context=_mixer_setup)
+
+
+@torch.library.custom_op("flare_b200::gather_fwd", mutates_args=())
+def _op_gather_fwd(q: Tensor, k: Tensor, v: Tensor, scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    return gather_forward(q, k, v, scale, key_mask)
+
+
+@_op_gather_fwd.register_fake
+def _(q, k, v, scale, key_mask):
+    B, H, N, D = k.shape
+    M = q.shape[-2]
+    return (torch.empty(B, H, M, D, dtype=k.dtype, device=k.device), torch.empty(B, H, M, D, dtype=torch.float32, device=k.device),
+            torch.empty(B, H, M, dtype=torch.float32, device=k.device))
+
+
+@torch.library.custom_op("flare_b200::gather_bwd", mutates_args=())
+def _op_gather_bwd(q: Tensor, k: Tensor, v: Tensor, dz: Tensor, z32: Tensor, lse_m: Tensor, scale: float,
+                   key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    return gather_backward(q, k, v, dz, z32, lse_m, scale, key_mask)
+
+
+@_op_gather_bwd.register_fake
+def _(q, k, v, dz, z32, lse_m, scale, key_mask):
+    return _dq_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), torch.empty(v.shape, dtype=v.dtype, device=v.device)
+
+
+def _gather_setup(ctx, inputs, output):
+    q, k, v, scale, key_mask = inputs
+    _z, z32, lse_m = output
+    ctx.save_for_backward(q, k, v, z32, lse_m, key_mask)
+    ctx.scale = scale
+
+
+def _gather_backward(ctx, dz, _dz32, _dlse):
+    q, k, v, z32, lse_m, key_mask = ctx.saved_tensors
+    dq, dk, dv = _op_gather_bwd(q, k, v, dz.contiguous(), z32, lse_m, ctx.scale, key_mask)
+    return dq.to(q.dtype), dk, dv, None, None
+
+
+_op_gather_fwd.register_autograd(_gather_backward, setup_context=_gather_setup)
+
+
+@torch.library.custom_op("flare_b200::scatter_fwd", mutates_args=())
+def _op_scatter_fwd(q: Tensor, k: Tensor, z: Tensor, scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor]:
+    return scatter_forward(q, k, z, scale, key_mask)
+
+
+@_op_scatter_fwd.register_fake
+def _(q, k, z, scale, key_mask):
+    B, H, N, D = k.shape
+    return _like_tokens(k), torch.empty(B, H, N, dtype=torch.float32, device=k.device)
+
+
+@torch.library.custom_op("flare_b200::scatter_bwd", mutates_args=())
+def _op_scatter_bwd(q: Tensor, k: Tensor, z: Tensor, dy: Tensor, y: Tensor, lse_n: Tensor, scale: float,
+                    key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
+    return scatter_backward(q, k, z, dy, y, lse_n, scale, key_mask)
+
+
+@_op_scatter_bwd.register_fake
+def _(q, k, z, dy, y, lse_n, scale, key_mask):
+    return _dq_like(q), torch.empty(k.shape, dtype=k.dtype, device=k.device), torch.empty(z.shape, dtype=torch.float32, device=z.device)
+
+
+def _scatter_setup(ctx, inputs, output):
+    q, k, z, scale, key_mask = inputs
+    y, lse_n = output
+    ctx.save_for_backward(q, k, z, y, lse_n, key_mask)
+    ctx.scale = scale
+
+
+def _scatter_backward(ctx, dy, _dlse):
+    q, k, z, y, lse_n, key_mask = ctx.saved_tensors
+    dq, dk, dz32 = _op_scatter_bwd(q, k, z, dy, y, lse_n, ctx.scale, key_mask)
+    return dq.to(q.dtype), dk, dz32.to(z.dtype), None, None
+
+
+_op_scatter_fwd.register_autograd(_scatter_backward, setup_context=_scatter_setup)
+
+
+# ------------------------------------------------------------------------------------
+# the public functions
+# ------------------------------------------------------------------------------------
+def _fold_q(q):
+    # an expand()-ed q (stride 0 over the batch, pdebench/models/flare.py:136) is the shared-latent case
+    if q.dim() == 4 and q.stride(0) == 0:
+        return q[0]
+    return q
+
+
+def _autocast(*ts):
+    """What SDPA does under torch.autocast: floating-point CUDA inputs are cast to the autocast dtype, so that
+    fp32 latent parameters meet half-precision projections (mlutils/trainer.py:135-137 runs every step so)."""
+    if torch.is_autocast_enabled("cuda"):
+        dt = torch.get_autocast_dtype("cuda")
+        return tuple(t.to(dt) if t is not None and t.is_cuda and t.is_floating_point() else t for t in ts)
+    return ts
+
+
+def _same_dtype(q, k, v):
+    if not (q.dtype == k.dtype == v.dtype):
+        raise TypeError(f"q, k, v must share a dtype outside torch.autocast; got {q.dtype}, {k.dtype}, {v.dtype}")
+
+
+def flare_multihead_mixer(q, k, v, scale: float = 1.0, key_mask: Optional[torch.Tensor] = None,
+                          dropout_p: float = 0.0):
+    """y[B,H,N,D] = SDPA(k, q, SDPA(q, k, v, scale), scale)   (README.md:37-53 of the reference).
+
+    q: [H,M,D] (or [B,H,M,D]); k, v: [B,H,N,D], any strides with unit stride on D.
+    key_mask: optional bool [B,N], True = token takes part (lra/models/backends.py:615-622);
+    masked tokens are ignored by the gather and their output rows are zero.
+    dropout_p: attention dropout of both SDPA calls (lra/models/backends.py:604-606) is not built: must be 0.
+    Works under torch.autocast (inputs are cast to the autocast dtype, as SDPA does) and inside
+    torch.compile (registered operators ``flare_b200::mixer_fwd`` / ``mixer_bwd``).
+    """
+    _need_cuda(q, k, v)
+    q, k, v = _autocast(_fold_q(q), k, v)
+    _same_dtype(q, k, v)
+    if dropout_p != 0.0:
+        raise NotImplementedError("attention dropout is not supported by the fused mixer (dropout_p must be 0)")
+    return _op_mixer_fwd(q, k, v, float(scale), key_mask)[0]
 
 
 def flare_gather(q, k, v, scale: float = 1.0, key_mask=None):
     """(z[B,H,M,D], lse[B,H,M]): the first SDPA call, z = softmax_N(scale q k^T) v."""
-    return _GatherFn.apply(_fold_q(q), k, v, float(scale), key_mask)
+    _need_cuda(q, k, v)
+    q, k, v = _autocast(_fold_q(q), k, v)
+    _same_dtype(q, k, v)
+    z, _z32, lse_m = _op_gather_fwd(q, k, v, float(scale), key_mask)
+    return z, lse_m.detach()
 
 
 def flare_scatter(q, k, z, scale: float = 1.0, key_mask=None):
     """y[B,H,N,D]: the second SDPA call, y = softmax_M(scale k q^T) z."""
-    return _ScatterFn.apply(_fold_q(q), k, z, float(scale), key_mask)
+    _need_cuda(q, k, z)
+    q, k, z = _autocast(_fold_q(q), k, z)
+    return _op_scatter_fwd(q, k, z, float(scale), key_mask)[0]

@@ -27,9 +27,12 @@
  *     context-parallel group use the same record and the same combine.
  *   - key_mask is uint8 [B,N] (contiguous), non-zero = keep; NULL = keep all
  *     (lra/models/backends.py:615-622).
- *   - Every call is asynchronous on `stream`, re-entrant, and returns 0 when
- *     the work was enqueued, or a negative FLARE_E* code when the request was
+ *   - Every call is asynchronous on `stream`, never synchronises the host, may
+ *     be made from several host threads and on several devices of one process
+ *     (per-device state is set up once, under a lock), and returns 0 when the
+ *     work was enqueued, or a negative FLARE_E* code when the request was
  *     rejected before any launch; flare_last_error() then describes why.
+ *     flare_gather_noalloc is the exception to re-entrancy: see there.
  */
 #ifndef FLARE_B200_H_
 #define FLARE_B200_H_
@@ -57,10 +60,13 @@ extern "C" {
 #define FLARE_TERM_SCATTER  2    /* dS2 = A (Z dY^T - delta)                    */
 #define FLARE_TERM_BOTH     3
 
-/* kernel family (flare_set_path): tensor-core kernels when the shape allows, or SIMT only */
+/* flare_set_path: a testing aid, not a second implementation.  The tensor-core kernels serve bf16 and
+ * fp16 with D in {16,32} (bf16 D = 64 in the forward passes); the fp32-arithmetic kernels serve fp32
+ * and every other shape.  SIMT forces the latter for 16-bit inputs too, TC_EXACT keeps the tensor-core
+ * kernels but always takes the general two-exponential backward. */
 #define FLARE_PATH_AUTO     0
 #define FLARE_PATH_SIMT     1
-#define FLARE_PATH_TC_EXACT 2    /* tensor-core kernels, but always the two-exponential backward */
+#define FLARE_PATH_TC_EXACT 2
 
 typedef void* flare_stream_t;    /* a cudaStream_t */
 
@@ -160,9 +166,11 @@ int flare_bwd_dq_partial(const FlareProblem* p, int terms, const void* q, const 
                          flare_stream_t stream);
 
 /* flare_bwd_tokens and flare_bwd_dq_partial in one call: dk, dv and dq_part[S][B][H][M][D] from a
- * single sweep over k, v, dy, y where the fused tensor-core kernel covers the shape, else the two
- * launches above (delta_n [B,H,N] fp32 is their scratch; it may be left unwritten).  Replaces the
- * bulk of autograd through the two SDPA calls of pdebench/models/flare.py:137-138. */
+ * single sweep over k, v, dy, y where a fused tensor-core kernel covers the problem (bf16 or fp16,
+ * D in {16,32}, up to 1024 latents; key_mask and single terms included), else the two launches above.
+ * delta_n [B,H,N] fp32 (256-byte aligned) is scratch; it may be left unwritten.  `terms` and the
+ * pointers that may be NULL are as for flare_bwd_tokens.  Stream-ordered: no host synchronisation.
+ * Replaces the bulk of autograd through the two SDPA calls of pdebench/models/flare.py:137-138. */
 int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* k, const void* v,
                    const void* dy, const void* y, const uint8_t* key_mask, const float* z32,
                    const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
@@ -232,12 +240,11 @@ int flare_triple_contract(int BH, int N, int Dx, int Dy, int Dz, int dtype, cons
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
 int flare_device_status(int* out, int clear);
 
-/* Tracing aid, no counterpart in the reference: when given a device array of 8 int64 (zeroed by
- * the caller), the fused backward kernel adds the clock cycles its issuing thread spends in each
- * phase of a step: [0] waiting for tensor-core products, [1] softmax math and stores, [2] preparing
- * the next tile's operands, [3] draining stores + CTA barrier, [4] issuing products, [5] step count.
- * NULL (the default) switches the counters off. */
-int flare_debug_phase_counters(long long* dev_counters);
+/* How many of the streaming passes (gather, scatter, dZ, main backward, per-token gradients, dQ) this
+ * process has enqueued on the tensor-core kernels and on the fp32-arithmetic kernels since the library
+ * was loaded; either pointer may be NULL.  Lets a caller (or a test) see which family served its
+ * shapes.  HOST pointers.  No counterpart in the reference. */
+int flare_pass_counts(long long* tensor_core, long long* simt);
 
 /* Measurement aid, no counterpart in the reference: launches `blocks` x 256 threads that each
  * issue 8*iters dependent-chain ex2 operations, so that the benchmark can time the exponential

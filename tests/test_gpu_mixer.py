@@ -76,20 +76,61 @@ def test_parity_fwd_bwd(fb, cuda_dev, path, dtype, B, H, N, M, D, scale):
     assert_close(got, oracle_all(q, k, v, dy, scale), TOL[dtype])
 
 
-@pytest.mark.parametrize("variant", ["FLARE_BWD3", "FLARE_NO_PIPELINE"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,H,N,M,D", [
     (1, 2, 1000, 256, 32),      # ragged last tile, two 128-latent blocks
     (2, 2, 2048, 192, 32),      # second latent block half full
     (1, 3, 700, 128, 32),       # one block
     (1, 1, 128 * 37 + 5, 256, 32),
-    (2, 1, 300, 64, 32),
+    (2, 1, 300, 64, 16),
+    (1, 2, 900, 640, 32),       # more than 256 latents: blocks of 256 that add into dk, dv
 ])
-def test_backward_kernel_variants(fb, cuda_dev, monkeypatch, variant, B, H, N, M, D):
-    """The alternative one-exponential backward kernels (selected by environment switches) against the oracle."""
-    monkeypatch.setenv(variant, "1")
-    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=torch.bfloat16, seed=11)
-    got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev)
+def test_general_tensor_core_backward(fb, cuda_dev, dtype, B, H, N, M, D):
+    """The two-exponential tensor-core backward on its own (it otherwise only takes the (b, h) the range
+    check hands it, masks, single terms and fp16)."""
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=11)
+    prev = fb.set_kernel_path("tc_exact")
+    try:
+        tc0, simt0 = fb.pass_counts()
+        got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev)
+        tc1, simt1 = fb.pass_counts()
+    finally:
+        fb.set_kernel_path(prev)
+    assert simt1 == simt0 and tc1 - tc0 == 4      # gather, scatter, dZ, main backward
     assert_close(got, oracle_all(q, k, v, dy, 1.0), 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_lra_shape_with_mask_stays_on_tensor_cores(fb, cuda_dev, dtype):
+    """The LRA configuration (out/lra/run.sh:32-93: C=128, H=8, M=128, N up to 4096) with the key-padding
+    mask every LRA batch carries (lra/models/backends.py:602-622); a smaller batch than 32 keeps the
+    oracle quick."""
+    B, H, N, M, D = 4, 8, 4096, 128, 16
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=31)
+    lens = torch.tensor([N, 3000, 1025, 130])
+    mask = torch.arange(N)[None, :] < lens[:, None]
+    tc0, simt0 = fb.pass_counts()
+    got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev, key_mask=mask)
+    tc1, simt1 = fb.pass_counts()
+    assert simt1 == simt0 and tc1 - tc0 == 4
+    assert fb.device_status() == 0
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    y = O.mixer_lra(qf, kf, vf, 1.0, mask)
+    y.backward(dy.float())
+    assert_close(got, [y.detach(), qf.grad, kf.grad, vf.grad], 2e-2)
+
+
+def test_scattered_mask_bits(fb, cuda_dev):
+    """A mask that is not a prefix: kept and dropped tokens alternate irregularly inside tiles."""
+    B, H, N, M, D = 2, 2, 1000, 96, 32
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=torch.bfloat16, seed=41)
+    mask = torch.rand(B, N, generator=torch.Generator().manual_seed(1)) < 0.6
+    mask[1, :300] = False                        # whole tiles dropped, first ones included
+    got = run_mixer(fb, q, k, v, dy, 1.0, cuda_dev, key_mask=mask)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    y = O.mixer_lra(qf, kf, vf, 1.0, mask)
+    y.backward(dy.float())
+    assert_close(got, [y.detach(), qf.grad, kf.grad, vf.grad], 2e-2)
 
 
 def test_single_token(fb, cuda_dev):
@@ -175,6 +216,31 @@ def test_gather_and_scatter_as_separate_ops(fb, cuda_dev, dtype):
     got = [y.float().cpu(), qd.grad.float().cpu(), kd.grad.float().cpu(), vd.grad.float().cpu()]
     # z is rounded to the input dtype between the two ops, as in the reference
     assert_close(got, [yr.detach(), qf.grad, kf.grad, vf.grad], tol * (1 if dtype == torch.float32 else 1.5))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_separate_ops_backward_on_tensor_cores(fb, cuda_dev, dtype):
+    """Gather-only and scatter-only backward terms (BigFLARE trains through them) at a size with several
+    token ranges, served by the general tensor-core backward."""
+    B, H, N, M, D = 1, 2, 65536, 256, 32
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=23)
+    dev = cuda_dev
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    tc0, simt0 = fb.pass_counts()
+    z, lse = fb.flare_gather(qd, kd, vd, scale=1.0)
+    z2 = z * 1.5                                  # the latents are edited between the two operators
+    y = fb.flare_scatter(qd, kd, z2, scale=1.0)
+    y.backward(dy.to(dev))
+    torch.cuda.synchronize()
+    tc1, simt1 = fb.pass_counts()
+    assert simt1 == simt0 and tc1 - tc0 == 5      # gather, scatter, dZ, scatter-term backward, gather-term backward
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    zr, _ = O.gather(qf, kf, vf, 1.0)
+    zr2 = (zr.to(dtype) * 1.5).float()            # z crosses the boundary between the two operators in `dtype`
+    yr, _ = O.scatter(qf, kf, zr2, 1.0)
+    yr.backward(dy.float())
+    got = [y.float().cpu(), qd.grad.float().cpu(), kd.grad.float().cpu(), vd.grad.float().cpu()]
+    assert_close(got, [yr.detach(), qf.grad, kf.grad, vf.grad], 3e-2)
 
 
 def test_partial_records_and_combine_match_oracle(fb, cuda_dev):
