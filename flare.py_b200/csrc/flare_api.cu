@@ -336,19 +336,19 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
       TRY(check_tok("y", y, p->y_stride, p->dtype));
       if (!lse_n) return fail(FLARE_EINVAL, "bwd_main: the scatter term needs lse_n");
     }
-    // The one-exponential kernels cover the plain case (bf16, both terms, no mask; D = 32 for any M up to
-    // 1024, D = 16 up to 256 latents).  An on-device range check picks, per (b, h), between them (flag 0)
-    // and the general two-exponential kernel (flag 1); both are launched and each returns at once on the
-    // (b, h) it does not own.  delta_n ([B,H,N] floats) is not needed by the fused kernels and doubles as
+    // The one-exponential kernel covers the plain case (bf16, both terms, no mask, D = 32, 32 to 1024
+    // latents).  An on-device range check picks, per (b, h), between it (flag 0) and the general
+    // two-exponential kernel (flag 1); both are launched and each returns at once on the (b, h) it does
+    // not own.  delta_n ([B,H,N] floats) is not needed by the fused kernels and doubles as
     // the scratch of that check.  Everything else goes to the general kernel directly.
     const int* flag = nullptr;
     int rc = FLARE_OK;
     const size_t have = (size_t)p->B * p->H * (size_t)p->N * sizeof(float);
     const bool fast = p->dtype == FLARE_BF16 && terms == FLARE_TERM_BOTH && !key_mask && g_path.load() != FLARE_PATH_TC_EXACT &&
-                      (c.D == 32 || c.M <= 256) && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
-                      have >= tc_bwd2_scratch_bytes(c);
+                      tc_bwd_fast_supported(c, p->dtype) && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
+                      have >= tc_bwd_fast_scratch_bytes(c);
     if (fast)
-      rc = tc_bwd2_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
+      rc = tc_bwd_fast_main(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, delta_n, &flag, (cudaStream_t)stream);
     if (rc == FLARE_OK)
       rc = tc_bwd_main(c, p->dtype, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, dq_part, flag, (cudaStream_t)stream);
     if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("bwd_main (tcgen05)"); }

@@ -21,8 +21,8 @@
 // This is the general tensor-core backward: bf16 or fp16, D in {16, 32}, a key-padding mask (excluded
 // tokens get P = A = 0, hence zero dK, dV and no share in dQ), either softmax term alone (the separate
 // gather / scatter operators), and more than 256 latents as blocks of 256 per launch, each block adding
-// its dK/dV to what the earlier ones wrote.  The one-exponential kernels (flare_tc_bwd2.cu,
-// flare_tc_bwd4.cu) are the fast form of its unmasked two-term bf16 case.
+// its dK/dV to what the earlier ones wrote.  The one-exponential kernels (flare_tc_bwd_range.cu,
+// flare_tc_bwd_fast.cu) are the fast form of its unmasked two-term bf16 case.
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -164,7 +164,9 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
       const int m = tid;                           // 256 threads, 256 latent slots
       float l2 = INFINITY, dl = 0.f;
       if (m < M && use_g) {                        // without the gather term P = 0 (L = +inf)
-        for (int i = 0; i < D; ++i) dl = fmaf(dzb[m * D + i], zb[m * D + i], dl);
+        // Delta_m from dZ as the tensor core sees it (rounded to the operand type): sum_n P_mn (V_n . dZ_m) then
+        // cancels against it exactly instead of leaving a rounding residue of one sign along the row
+        for (int i = 0; i < D; ++i) dl = fmaf(Op16<T16>::unpack(Op16<T16>::pack(dzb[m * D + i], 0.f)).x, zb[m * D + i], dl);
         l2 = a.lse_m[lrow + m] * kLog2e;
       }
       sLD[m] = make_float2(l2, dl);

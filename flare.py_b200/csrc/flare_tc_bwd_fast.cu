@@ -1,10 +1,9 @@
 // Main backward pass, one exponential per score, 128-latent steps.
 //
-// Same mathematics as flare_tc_bwd2.cu / flare_tc_bwd3.cu (dS = P * T', T' from one extended-
-// contraction product; the (b, h) it may run are chosen by the same on-device range check).  A step
-// u = (token tile t, 128-latent block s) is twice the size of flare_tc_bwd3.cu's, so every hand-off
-// between the softmax threads and the tensor pipe is paid half as often, and the score buffers are
-// laid out so that the two halves of a step's arithmetic need different products:
+// dS = P * T' with T' from one extended-contraction product (the mathematics and the on-device range
+// check that chooses the (b, h) this kernel may run are described in flare_tc_bwd_range.cu).  A step
+// u = (token tile t, 128-latent block s); the score buffers are laid out so that the two halves of a
+// step's arithmetic need different products:
 //
 //   tensor memory (512 columns): S^T double-buffered [0,128) [128,256); T' single [256,384);
 //   dV 384, dK 416, dQ_0 448, dQ_1 480.  Thread (token row, c) owns columns [32c, 32c+32) of a step:
@@ -32,7 +31,7 @@ namespace flare {
 
 using namespace tc;
 
-struct Bwd4Args {
+struct BwdFastArgs {
   int B, H, N, M;
   float scale, scale_log2;
   int q_batched;
@@ -53,7 +52,7 @@ struct Bwd4Args {
   int* status;
 };
 
-struct Bwd4Smem {
+struct BwdFastSmem {
   static constexpr int D = 32, ROWB = 64;
   static constexpr int kLat = 256 * ROWB;          // Q, dZ or eL*Z: all latents
   static constexpr int kExtB = 256 * 32;           // extension columns of B'
@@ -72,14 +71,14 @@ __device__ __forceinline__ void mbar_arrive4(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-constexpr int kB4Softmax = 512, kB4Helpers = 96;   // + the issuer warp
+constexpr int kBFSoftmax = 512, kBFHelpers = 96;   // + the issuer warp
 
 template <bool ACC>                               // ACC: add to the dK/dV an earlier latent block wrote
-__global__ void __launch_bounds__(kB4Softmax + kB4Helpers + 32, 1)
-k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, Bwd4Args a) {
+__global__ void __launch_bounds__(kBFSoftmax + kBFHelpers + 32, 1)
+k_tc_bwd_fast(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, BwdFastArgs a) {
   constexpr int D = 32, ROWB = 64, CPR = 4;
-  using L = Bwd4Smem;
+  using L = BwdFastSmem;
   const int split = blockIdx.x % a.n_splits;
   const int bh = blockIdx.x / a.n_splits;
   if (a.flag[bh] != 0) return;                     // the exact kernel owns this (b, h)
@@ -111,9 +110,9 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   int* abort_flag = reinterpret_cast<int*>(bars + 18);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool is_p2 = warp == kB4Softmax / 32 + 3;  // issues dV/dK/dQ products, stores lane quarter 3
-  const bool is_st = warp == kB4Softmax / 32 + 2;  // issues S^T/T' products and the TMA loads, stores lane quarter 2
-  const bool is_helper = warp == kB4Softmax / 32 || warp == kB4Softmax / 32 + 1;   // per-token operands, quarters 0, 1
+  const bool is_p2 = warp == kBFSoftmax / 32 + 3;  // issues dV/dK/dQ products, stores lane quarter 3
+  const bool is_st = warp == kBFSoftmax / 32 + 2;  // issues S^T/T' products and the TMA loads, stores lane quarter 2
+  const bool is_helper = warp == kBFSoftmax / 32 || warp == kBFSoftmax / 32 + 1;   // per-token operands, quarters 0, 1
   const int c4 = (warp >> 2) & 3;                  // column group: 32 latent columns of a step
   const int row = (warp & 3) * 32 + lane;          // token within the tile = tensor-memory lane
   const int b = bh / a.H, h = bh % a.H;
@@ -132,9 +131,9 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   if (tid == 0) {
     for (int i = 0; i < 3; ++i) mbar_init(&bar_full[i], 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_s[i], 1); mbar_init(&bar_p2[i], 1); mbar_init(&bar_pd[i], kB4Softmax); mbar_init(&bar_ge[i], 1);
+      mbar_init(&bar_s[i], 1); mbar_init(&bar_p2[i], 1); mbar_init(&bar_pd[i], kBFSoftmax); mbar_init(&bar_ge[i], 1);
     }
-    mbar_init(bar_t, 1); mbar_init(bar_tl, kB4Softmax);
+    mbar_init(bar_t, 1); mbar_init(bar_tl, kBFSoftmax);
     mbar_init(bar_q, 1); mbar_init(bar_free, 128); mbar_init(bar_tile, 1); mbar_init(bar_prep, 64);
     *abort_flag = 0;
     fence_barrier_init();
@@ -193,7 +192,9 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       const int m = tid;
       float l2 = INFINITY, dl = 0.f, el = 0.f;
       if (m < M) {
-        for (int i = 0; i < D; ++i) dl = fmaf(dzb[m * D + i], zb[m * D + i], dl);
+        // Delta_m from dZ as the tensor core sees it (rounded to bf16): sum_n P_mn (V_n . dZ_m) then cancels
+        // against it exactly instead of leaving a rounding residue of one sign along the row
+        for (int i = 0; i < D; ++i) dl = fmaf(__bfloat162float(__float2bfloat16_rn(dzb[m * D + i])), zb[m * D + i], dl);
         l2 = a.lse_m[lrow + m] * kLog2e;
         el = ex2(l2 - mu);
       }
@@ -224,6 +225,8 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     const uint8_t* tG = sTok + (tau % 3) * L::kStage + 2 * L::kT;
     const bool valid = n < n1;
     const float ec = valid ? ex2(mu - cbv * kLog2e) : 0.f;
+    // g_n = (eC_n dY_n) . Y_n with eC_n dY_n rounded to bf16 as the tensor core sees it, so that the scatter
+    // term's cancellation sum_m A_mn (Z_m . dY_n - delta_n) is free of that rounding
     float dl = 0.f;
     uint8_t* ge = sGe + (tau & 1) * L::kT;
 #pragma unroll
@@ -231,19 +234,19 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       const uint4 g4 = *reinterpret_cast<const uint4*>(tG + swz_off<ROWB>(r, c));
       const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
       const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&yv[c]);
-      float gf[8];
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 gg2 = __bfloat1622float2(gp[j]), yf = __bfloat1622float2(yp[j]);
-        gf[2 * j] = gg2.x; gf[2 * j + 1] = gg2.y;
-        dl = fmaf(gg2.x, yf.x, dl); dl = fmaf(gg2.y, yf.y, dl);
+        const __nv_bfloat162 gs = __floats2bfloat162_rn(gg2.x * ec, gg2.y * ec);
+        const float2 gsf = __bfloat1622float2(gs);
+        dl = fmaf(gsf.x, yf.x, dl); dl = fmaf(gsf.y, yf.y, dl);
+        ow[j] = *reinterpret_cast<const uint32_t*>(&gs);
       }
-      uint4 o;
-      o.x = pack_bf16(gf[0] * ec, gf[1] * ec); o.y = pack_bf16(gf[2] * ec, gf[3] * ec);
-      o.z = pack_bf16(gf[4] * ec, gf[5] * ec); o.w = pack_bf16(gf[6] * ec, gf[7] * ec);
       *reinterpret_cast<uint4*>(ge + swz_off<ROWB>(r, c)) = o;
     }
-    const float gg = valid ? ec * dl : 0.f;
+    const float gg = valid ? dl : 0.f;
     __nv_bfloat16 gh, gl;
     split_bf16_4(gg, gh, gl);
     const __nv_bfloat16 one = __float2bfloat16_rn(valid ? 1.f : 0.f);
@@ -471,7 +474,7 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
     // ================= helper warps: per-token operands of tile t+1, then dV/dK of tile t -> global =========
     // Y rows and C_n of a tile are fetched one tile before they are needed, so that the DRAM latency
     // never sits between the end of a tile and the first product of the next one.
-    const int j = tid - kB4Softmax;                // 0..63: rows j and j + 64
+    const int j = tid - kBFSoftmax;                // 0..63: rows j and j + 64
     uint4 yv0[4], yv1[4];
     float cb0 = 0.f, cb1 = 0.f;
     if (n_tiles > 1) {
@@ -595,12 +598,12 @@ k_tc_bwd4(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 }
 
 // ------------------------------------------------------------------------------------------
-bool tc_bwd4_supported(const Ctx& c, int dtype) {
+bool tc_bwd_fast_supported(const Ctx& c, int dtype) {
   // more than 256 latents run as blocks of 256 that add into dK/dV
   return dtype == FLARE_BF16 && c.D == 32 && c.M >= 32 && c.M <= 1024 && c.N >= 1 && c.terms == FLARE_TERM_BOTH;
 }
 
-int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+int tc_bwd_fast_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                    const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* dq_part, const float* mu, const int* flag, cudaStream_t st) {
   constexpr int D = 32;
@@ -612,7 +615,7 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
                          (c.B > 1 ? s[0] : s[1] * c.H) * e, 128);
   };
   if (!tokmap(&tmK, k, c.ks) || !tokmap(&tmV, v, c.vs) || !tokmap(&tmG, dy, c.dys)) return FLARE_EUNSUPPORTED;
-  Bwd4Args a;
+  BwdFastArgs a;
   a.B = c.B; a.H = c.H; a.N = c.N; a.M_total = c.M;
   a.scale = c.scale; a.scale_log2 = c.scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
@@ -624,9 +627,9 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
   for (int i = 0; i < 3; ++i) { a.ys[i] = c.ys[i]; a.dks[i] = c.dks[i]; a.dvs[i] = c.dvs[i]; }
   a.dq_part = dq_part;
   a.status = tc_status_ptr();
-  constexpr int smem = Bwd4Smem::kBytes;
-  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd4<false>), smem) != FLARE_OK) return FLARE_ECUDA;
-  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd4<true>), smem) != FLARE_OK) return FLARE_ECUDA;
+  constexpr int smem = BwdFastSmem::kBytes;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd_fast<false>), smem) != FLARE_OK) return FLARE_ECUDA;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_bwd_fast<true>), smem) != FLARE_OK) return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   for (int m0 = 0; m0 < c.M; m0 += 256) {
@@ -637,8 +640,8 @@ int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, co
                        (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
       return FLARE_EUNSUPPORTED;
     a.M = mb; a.m0 = m0;
-    if (m0 == 0) k_tc_bwd4<false><<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
-    else k_tc_bwd4<true><<<(unsigned)grid, kB4Softmax + kB4Helpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+    if (m0 == 0) k_tc_bwd_fast<false><<<(unsigned)grid, kBFSoftmax + kBFHelpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+    else k_tc_bwd_fast<true><<<(unsigned)grid, kBFSoftmax + kBFHelpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
   }
   return FLARE_OK;
 }

@@ -53,15 +53,15 @@ bool tc_bwd_supported(const Ctx& c, int dtype);
 int tc_bwd_main(const Ctx& c, int dtype, const void* q, const void* k, const void* v, const void* dy, const void* y,
                 const uint8_t* mask, const float* z32, const float* dz32, const float* lse_m, const float* lse_n,
                 void* dk, void* dv, float* dq_part, const int* flag, cudaStream_t st);
-// One-exponential form of the same pass plus the on-device range check that selects, per (b, h),
-// between it (flag 0) and the exact kernel above (flag 1).
-size_t tc_bwd2_scratch_bytes(const Ctx& c);
-int tc_bwd2_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
-                 const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
-                 float* dq_part, void* scratch, const int** flag_out, cudaStream_t st);
-// the same pass in 128-latent steps (two per token tile): S^T double-buffered, T' single
-bool tc_bwd4_supported(const Ctx& c, int dtype);
-int tc_bwd4_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+// The one-exponential form of the plain case (bf16, both terms, no mask, D = 32) behind an on-device range
+// check that selects, per (b, h), between it (flag 0) and the general kernel above (flag 1).
+size_t tc_bwd_fast_scratch_bytes(const Ctx& c);
+int tc_bwd_fast_main(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
+                     const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
+                     float* dq_part, void* scratch, const int** flag_out, cudaStream_t st);
+// the one-exponential kernel itself: 128-latent steps, S^T double-buffered, T' single, two issuing warps
+bool tc_bwd_fast_supported(const Ctx& c, int dtype);
+int tc_bwd_fast_launch(const Ctx& c, const void* q, const void* k, const void* v, const void* dy, const void* y,
                    const float* z32, const float* dz32, const float* lse_m, const float* lse_n, void* dk, void* dv,
                    float* dq_part, const float* mu, const int* flag, cudaStream_t st);
 // per-device host state (tc_runtime.cu)

@@ -22,6 +22,8 @@ import torch
 import torch.nn.functional as F
 
 HERE = Path(__file__).resolve().parent
+sys.path.insert(0, str(HERE))
+from seeded_init import fill_parameters, pde_inputs, projections  # noqa: E402
 
 
 def _load(path: Path, name: str, package: str | None = None):
@@ -129,6 +131,29 @@ def pde_model_case(ref, name, seed):
     print(name, "params", sum(v.size for v in sd.values()))
 
 
+def pde_surrogate_case(ref, name):
+    """The PDE-surrogate configuration (B=4, N=7225 = the 85 x 85 Darcy grid, C=128, 8 heads, 64 latents,
+    8 blocks; pdebench/models/flare.py:251-349) trained one step with an MSE loss, fp32 on the CPU.
+    Recorded: the loss, fingerprints of the output and of every parameter gradient (norm + 4 projections)
+    and the full gradient of every block's latent queries.  Weights and inputs are functions of names
+    and seeds (seeded_init.py), so the check rebuilds them instead of loading them."""
+    model = ref.FLAREModel(in_dim=3, out_dim=1, channel_dim=128, num_blocks=8, num_heads=8, num_latents=64)
+    fill_parameters(model)
+    x, target = pde_inputs(4, 7225, seed=0)
+    y = model(x)
+    loss = F.mse_loss(y, target)
+    loss.backward()
+    out = {"loss": np.float64(loss.item()), "y_norm": np.float64(y.detach().double().norm().item()),
+           "y_proj": projections("y", y).numpy()}
+    for pname, prm in model.named_parameters():
+        out["gnorm::" + pname] = np.float64(prm.grad.double().norm().item())
+        out["gproj::" + pname] = projections(pname, prm.grad).numpy()
+        if pname.endswith("latent_q"):
+            out["grad::" + pname] = np32(prm.grad)
+    np.savez_compressed(HERE / f"{name}.npz", **out)
+    print(name, "loss", loss.item(), "params", sum(p.numel() for p in model.parameters()))
+
+
 def lra_block_case(lra, name, seed):
     """lra FLAREBlock (lra/models/backends.py:624-672) with a key-padding mask, eval mode."""
     torch.manual_seed(seed)
@@ -155,8 +180,13 @@ def triton_ref_cases(root: Path):
     B, H, N, D = 1, 2, 96, 16
     q1, q2, k1, k2, v = (torch.randn(B, H, N, D, generator=g) for _ in range(5))
     state, o = tri.triple_attn_einsum(q1, q2, k1, k2, v)
+    # the file's own backward reference (triple.py:887-931) for a seeded upstream gradient of O
+    do = torch.randn(B, H, N, D, generator=g)
+    ctx = types.SimpleNamespace(saved_tensors=(q1, q2, k1, k2, v, o, state))
+    dq1, dq2, dk1, dk2, dv = tri.triple_attn_bwd_einsum(ctx, None, do)
     np.savez_compressed(HERE / "triple_ref.npz", q1=np32(q1), q2=np32(q2), k1=np32(k1),
-                        k2=np32(k2), v=np32(v), state=np32(state), o=np32(o))
+                        k2=np32(k2), v=np32(v), state=np32(state), o=np32(o), do=np32(do),
+                        dq1=np32(dq1), dq2=np32(dq2), dk1=np32(dk1), dk2=np32(dk2), dv=np32(dv))
     cl = _load(root / "lra/models/triton/causal_linear.py", "_ref_causal_linear")
     B, H, N, Dk, Dv = 1, 2, 128, 32, 16
     q, k = (torch.randn(B, H, N, Dk, generator=g) for _ in range(2))
@@ -181,6 +211,7 @@ def main():
     pde_mixer_case(ref, "pde_mixer_sqrt", B=1, N=80, C=64, H=4, M=24, scale=16 ** -0.5, seed=1)
     lra_mixer_case(lra, "lra_mixer_mask", B=3, N=40, C=32, H=4, M=16, scale=1.0, seed=2)
     pde_model_case(ref, "pde_model_contract", seed=0)
+    pde_surrogate_case(ref, "pde_surrogate_step")
     lra_block_case(lra, "lra_block_contract", seed=3)
     try:
         triton_ref_cases(root)

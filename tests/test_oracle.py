@@ -99,3 +99,11 @@ def test_streamed_form_equals_dense_closed_form():
     assert O.rel_l2(y, O.mixer_sdpa(q, k, v, 0.8)) < 1e-12
     for a, b in zip((dq, dk, dv), O.mixer_bwd_closed_form(q, k, v, dy, 0.8)):
         assert O.rel_l2(a, b) < 1e-12
+
+
+def test_triple_backward_matches_the_reference_einsum_backward():
+    """lra/models/triton/triple.py:887-931 (triple_attn_bwd_einsum) on the recorded inputs and upstream gradient."""
+    g = load_golden("triple_ref")
+    got = O.triple_attention_bwd(g["q1"], g["q2"], g["k1"], g["k2"], g["v"], g["do"])
+    for name, a in zip(("dq1", "dq2", "dk1", "dk2", "dv"), got):
+        assert O.rel_l2(a, g[name]) < 1e-5, name
