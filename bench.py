@@ -325,6 +325,60 @@ def run_ours(args):
     ms_step = total_ms / args.steps
     value = B * N / (ms_step * 1e-3) / 1e6
 
+    # host time per step (Python, ctypes, allocator): the launches are asynchronous, so the time the loop
+    # takes to enqueue a step without waiting for the device is what the host side costs
+    sync_all()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    host_ms = (time.perf_counter() - t0) / args.steps * 1e3
+    sync_all()
+
+    # the same step back to back for at least two seconds: the clock settles under sustained load
+    sustained = None
+    if not args.no_sustained:
+        n_sus = max(args.steps, int(2000.0 / ms_step) + 1)
+        s2 = ClockSampler(local) if rank == 0 else None
+        if s2:
+            s2.start()
+        sus_ms = timed(step, n_sus) / n_sus
+        c2 = s2.stop() if s2 else None
+        if rank == 0:
+            sustained = dict(steps=n_sus, ms_per_step=sus_ms, value=B * N / (sus_ms * 1e-3) / 1e6,
+                             sm_mhz=c2["sm_mhz"] if c2 else None, reasons=c2["reasons"] if c2 else None,
+                             ms_x_mhz=sus_ms * c2["sm_mhz"] if c2 else None)
+
+    # N > 1: the context-parallel result against the single-GPU one on a small seeded problem
+    cp_parity = None
+    if world > 1:
+        Np = 16384
+        gp = torch.Generator(device="cpu").manual_seed(4321)
+        pq = (torch.randn(H, M, D, generator=gp) * sd).to(DTYPE).to(dev)
+        pk = (torch.randn(B, H, Np, D, generator=gp) * sd).to(DTYPE).to(dev)
+        pv = (torch.randn(B, H, Np, D, generator=gp) * sd).to(DTYPE).to(dev)
+        pdy = torch.randn(B, H, Np, D, generator=gp).to(DTYPE).to(dev)
+        a0, a1 = shard_bounds(Np, world, rank, multiple=128)
+        q1, k1, v1 = (t.clone().requires_grad_(True) for t in (pq, pk, pv))
+        y1 = fb.flare_multihead_mixer(q1, k1, v1, scale=1.0)
+        y1.backward(pdy)
+        q2 = pq.clone().requires_grad_(True)
+        k2 = pk[:, :, a0:a1].contiguous().requires_grad_(True)
+        v2 = pv[:, :, a0:a1].contiguous().requires_grad_(True)
+        y2 = flare_mixer_context_parallel(q2, k2, v2, 1.0, exchange=cp_ex)
+        y2.backward(pdy[:, :, a0:a1].contiguous())
+
+        def rel(a, b):
+            a, b = a.float(), b.float()
+            return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+        errs = torch.tensor([rel(y2, y1[:, :, a0:a1]), rel(q2.grad, q1.grad), rel(k2.grad, k1.grad[:, :, a0:a1]),
+                             rel(v2.grad, v1.grad[:, :, a0:a1])], device=dev)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        cp_parity = dict(zip(("y", "dq", "dk", "dv"), errs.tolist()), tokens=Np,
+                         against="single-GPU mixer on the same tensors, max over ranks of the shard's relative L2")
+        if not all(e <= 2e-2 for e in errs.tolist()):
+            raise SystemExit(f"context-parallel parity failed: {cp_parity}")
+
     # end to end: pinned host inputs -> device, fwd+bwd, results back to pinned host memory
     hy = torch.empty_like(hk).pin_memory()
     hdk = torch.empty_like(hk).pin_memory()
@@ -425,12 +479,12 @@ def run_ours(args):
                         parallelism=("single GPU" if world == 1 else
                                      f"context parallel, N sharded over {world} ranks, exchange={cp_kind}"),
                         tokens_per_rank=Nl, l2="inputs larger than L2 (K,V,dY,Y,dK,dV 64 B x tokens x heads each); no flush",
-                        kernel_path="tcgen05 (decoupled gather/scatter/dZ, pipelined one-exponential backward behind an on-device range check); fp32 SIMT reductions"),
+                        kernel_path="tcgen05 (decoupled gather/scatter/dZ, pipelined one-exponential backward behind an on-device range check); fp32 reductions"),
             clocks=clocks,
             e2e=dict(value=B * N / (e2e_ms * 1e-3) / 1e6, unit="Mtokens/s", h2d_bytes_per_step=h2d * world,
                      d2h_bytes_per_step=d2h * world, ms_per_step=e2e_ms),
             gpu_launches=launches_per_step * args.steps,
-            roofline=roof, cpu_baseline=cpu,
+            roofline=roof, cpu_baseline=cpu, sustained=sustained, host_ms_per_step=host_ms, cp_parity=cp_parity,
         )
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -472,6 +526,65 @@ def run_causal(args):
           flush=True)
 
 
+def run_sdpa_gpu(args):
+    """Secondary line (not the headline): the kernels the reference dispatches for this path on this GPU, i.e.
+    its two F.scaled_dot_product_attention calls (README.md:49-50) and their autograd in bf16 through the
+    installed torch, on the benchmark's tensors, next to this library's time for the same problem."""
+    import torch.nn.functional as F
+    import flare_b200 as fb
+    dev = torch.device("cuda:0")
+    w = dict(WORKLOAD)
+    if args.tokens:
+        w["N"] = args.tokens
+    B, H, N, M, D = (w[x] for x in "BHNMD")
+    g = torch.Generator().manual_seed(1234)
+    sd = D ** -0.25
+    q = (torch.randn(H, M, D, generator=g) * sd).to(DTYPE).to(dev).requires_grad_(True)
+    k = (torch.randn(B, H, N, D, generator=g) * sd).to(DTYPE).to(dev).requires_grad_(True)
+    v = (torch.randn(B, H, N, D, generator=g) * sd).to(DTYPE).to(dev).requires_grad_(True)
+    dy = torch.randn(B, H, N, D, generator=g).to(DTYPE).to(dev)
+
+    def sdpa_step():
+        q.grad = k.grad = v.grad = None
+        qe = q.unsqueeze(0).expand(B, -1, -1, -1)
+        z = F.scaled_dot_product_attention(qe, k, v, scale=1.0)
+        y = F.scaled_dot_product_attention(k, qe, z, scale=1.0)
+        y.backward(dy)
+        return y
+
+    def ours_step():
+        q.grad = k.grad = v.grad = None
+        y = fb.flare_multihead_mixer(q, k, v, scale=1.0)
+        y.backward(dy)
+        return y
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    out = {}
+    for name, fn in (("sdpa", sdpa_step), ("ours", ours_step)):
+        for _ in range(max(args.warmup, 3)):
+            y = fn()
+        out[name] = timed(fn, args.steps)
+        out[name + "_y"] = y.detach().float()
+        out[name + "_dk"] = k.grad.detach().float()
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()
+    print(json.dumps(dict(
+        metric="reference GPU path: two SDPA calls + autograd, Mtokens/s", value=B * N / out["sdpa"] / 1e3, unit="Mtokens/s",
+        n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=out["sdpa"], higher_is_better=True,
+        dtype="bf16", data="synthetic", torch=torch.__version__,
+        ours_ms_per_step=out["ours"], ours_over_sdpa=out["sdpa"] / out["ours"],
+        agreement=dict(y=rel(out["ours_y"], out["sdpa_y"]), dk=rel(out["ours_dk"], out["sdpa_dk"])),
+        config=dict(workload=f"sdpa_gpu: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd"))), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -480,11 +593,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override N (profiling on a smaller case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal"],
-                    help="mixer: the headline line; causal: a secondary line for causal prefill/decode")
+    ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained leg")
+    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "sdpa_gpu"],
+                    help="mixer: the headline line; causal: a secondary line for causal prefill/decode; sdpa_gpu: "
+                         "a secondary line timing the reference's own two SDPA calls + autograd on this GPU")
     args = ap.parse_args()
     if args.workload == "causal":
         run_causal(args)
+    elif args.workload == "sdpa_gpu":
+        run_sdpa_gpu(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

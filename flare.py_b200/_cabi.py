@@ -30,7 +30,13 @@ class FlareProblem(C.Structure):
     ]
 
 
+class FlarePeers(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("bufs", C.c_void_p), ("mine", C.c_void_p),
+                ("flags", C.c_void_p), ("epoch", C.c_int32)]
+
+
 _P = C.POINTER(FlareProblem)
+_G = C.POINTER(FlarePeers)
 _vp, _i, _sz, _i64 = C.c_void_p, C.c_int, C.c_size_t, C.c_int64
 
 # name -> (restype, argtypes); must list every symbol the header declares
@@ -47,6 +53,9 @@ SIGNATURES = {
     "flare_combine": (_i, [_P, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "flare_combine_peers": (_i, [_P, _vp, _i, _vp, _vp, _vp, _vp, _vp]),
     "flare_reduce_sum_peers": (_i, [_vp, _i, _i64, _i, _vp, _vp]),
+    "flare_peer_barrier": (_i, [_G, _vp]),
+    "flare_cp_mixer_fwd": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _G, _vp]),
+    "flare_cp_mixer_bwd": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _G, _G, _vp]),
     "flare_scatter": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_bwd_dz_partial": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_reduce_sum": (_i, [_vp, _i, _i64, _i, _vp, _vp]),

@@ -360,6 +360,72 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
   return FLARE_OK;
 }
 
+int check_peers(const char* what, const FlarePeers* g) {
+  if (!g || !g->bufs || !g->mine || !g->flags) return fail(FLARE_EINVAL, "%s: incomplete peer description", what);
+  if (g->world < 1 || g->world > 32 || g->rank < 0 || g->rank >= g->world)
+    return fail(FLARE_EINVAL, "%s: rank %d of %d", what, g->rank, g->world);
+  return FLARE_OK;
+}
+
+int flare_peer_barrier(const FlarePeers* g, flare_stream_t stream) {
+  TRY(check_peers("peer_barrier", g));
+  TRY(launch_peer_barrier(g->flags, g->rank, g->world, g->epoch, (cudaStream_t)stream));
+  return after_launch("peer_barrier");
+}
+
+int flare_cp_mixer_fwd(const FlareProblem* p, const void* q, const void* k, const void* v,
+                       const uint8_t* key_mask, void* y, float* z32, float* lse_m, float* lse_n,
+                       void* workspace, size_t workspace_bytes, const FlarePeers* rec, flare_stream_t stream) {
+  TRY(check_problem(p));
+  TRY(check_peers("cp_mixer_fwd", rec));
+  if (!z32 || !lse_m) return fail(FLARE_EINVAL, "z32 and lse_m are required outputs");
+  const size_t need = flare_fwd_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need) return fail(FLARE_EWORKSPACE, "forward workspace: have %zu bytes, need %zu", workspace_bytes, need);
+  FlareProblem pp = *p;
+  pp.n_splits = flare_pick_splits(p);
+  float* part = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  TRY(flare_gather_partial(&pp, q, k, v, key_mask, part, stream));
+  TRY(flare_combine(&pp, part, pp.n_splits, nullptr, nullptr, nullptr, rec->mine, stream));
+  TRY(flare_peer_barrier(rec, stream));
+  TRY(flare_combine_peers(&pp, rec->bufs, rec->world, z32, nullptr, lse_m, nullptr, stream));
+  TRY(flare_scatter(&pp, q, k, z32, key_mask, y, lse_n, stream));
+  return FLARE_OK;
+}
+
+int flare_cp_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const void* v, const void* dy,
+                       const void* y, const uint8_t* key_mask, const float* z32, const float* lse_m,
+                       const float* lse_n, float* dq32, void* dk, void* dv, void* workspace,
+                       size_t workspace_bytes, const FlarePeers* dz, const FlarePeers* dq, flare_stream_t stream) {
+  TRY(check_problem(p));
+  TRY(check_peers("cp_mixer_bwd", dz));
+  if (dq) TRY(check_peers("cp_mixer_bwd", dq));
+  if (!dq32) return fail(FLARE_EINVAL, "dq32 is null");
+  const size_t need = flare_bwd_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need) return fail(FLARE_EWORKSPACE, "backward workspace: have %zu bytes, need %zu", workspace_bytes, need);
+  FlareProblem pp = *p;
+  pp.n_splits = flare_pick_splits(p);
+  const size_t S = (size_t)pp.n_splits;
+  const size_t rows = (size_t)p->B * p->H * p->M;
+  char* w = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255) & ~uintptr_t(255));
+  float* part = reinterpret_cast<float*>(w);      w += up256(S * rows * p->D * sizeof(float));
+  float* dz32 = reinterpret_cast<float*>(w);      w += up256(rows * p->D * sizeof(float));
+  float* delta = reinterpret_cast<float*>(w);
+  TRY(flare_bwd_dz_partial(&pp, q, k, dy, key_mask, lse_n, part, stream));
+  TRY(flare_reduce_sum(part, pp.n_splits, (int64_t)rows, p->D, dz->mine, stream));
+  TRY(flare_peer_barrier(dz, stream));
+  TRY(flare_reduce_sum_peers(dz->bufs, dz->world, (int64_t)rows, p->D, dz32, stream));
+  TRY(flare_bwd_main(&pp, FLARE_TERM_BOTH, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta, part, stream));
+  const bool shared = p->q_stride[0] == 0;
+  const int n_parts = shared ? pp.n_splits * p->B : pp.n_splits;
+  const int64_t qrows = shared ? (int64_t)p->H * p->M : (int64_t)rows;
+  TRY(flare_reduce_sum(part, n_parts, qrows, p->D, dq ? dq->mine : dq32, stream));
+  if (dq) {
+    TRY(flare_peer_barrier(dq, stream));
+    TRY(flare_reduce_sum_peers(dq->bufs, dq->world, qrows, p->D, dq32, stream));
+  }
+  return FLARE_OK;
+}
+
 int flare_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const void* v, const void* dy,
                     const void* y, const uint8_t* key_mask, const float* z32, const float* lse_m,
                     const float* lse_n, float* dq32, void* dk, void* dv, void* workspace,

@@ -25,6 +25,7 @@ int launch_combine_ptrs(const float* const* recs, int n_parts, long long rows, i
                         void* z_out, float* lse_m, float* rec_out, cudaStream_t st);
 int launch_reduce_sum_ptrs(const float* const* parts, int n_parts, long long n, float* out, cudaStream_t st);
 int launch_probe_ex2(int blocks, int iters, float* out, cudaStream_t st);
+int launch_peer_barrier(int32_t* const* flags, int rank, int world, int epoch, cudaStream_t st);
 
 
 // tcgen05 tensor-core family (flare_tc_*.cu): bf16, D in {16,32,64}, M a multiple of 32 up to 256.

@@ -15,10 +15,10 @@ enough:
 gloo in the CPU tests), so that the plumbing can be exercised without a GPU.
 ``PeerExchange`` (GPUs of one node) fuses each collective into the kernel that
 consumes it: every rank writes its record (or partial sum) into a symmetric-memory
-buffer, a barrier on the stream orders the writes, and the combine / reduce kernel
-reads all ranks' buffers through peer pointers with plain loads over NVLink
-(``flare_combine_peers``, ``flare_reduce_sum_peers``).  Ordinary loads only, no waiting
-inside the library's kernels.
+buffer, the library's bounded flag barrier orders the writes, and the combine / reduce
+kernel reads all ranks' buffers through peer pointers with plain loads over NVLink
+(``flare_cp_mixer_fwd`` / ``flare_cp_mixer_bwd``: one call per pass).  Ordinary loads
+and stores only: no multicast, no ``multimem``.
 """
 from __future__ import annotations
 
@@ -68,9 +68,12 @@ class RecordExchange:
 class PeerExchange(RecordExchange):
     """The same exchanges through symmetric memory and peer loads (one node, NVLink).
 
-    Buffers are allocated once per (name, size) and used alternately (two halves), so one barrier
-    per exchange is enough: a half is rewritten two exchanges later, after every rank has passed
-    the barrier of the exchange in between, which it reaches only after its reads.
+    Per exchange kind ("rec", "dz", "dq") and size: one symmetric allocation holding two buffers used
+    alternately and an int32[world] array of arrival flags.  The ordering barrier is the library's own
+    (``flare_peer_barrier``: release/acquire flags in peer memory, a bounded wait that records a status
+    bit instead of hanging when a peer has left); torch supplies the allocation and the rendezvous only.
+    Each exchange carries a number (``epoch``) that must advance in step on all ranks: every rank has to
+    make the same sequence of calls.
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None):
@@ -81,24 +84,43 @@ class PeerExchange(RecordExchange):
 
     def _slot(self, name: str, numel: int, device):
         key = (name, numel)
-        if key not in self._slots:
-            buf = self._symm.empty(2 * numel, dtype=torch.float32, device=device)
-            hdl = self._symm.rendezvous(buf, group=self.group if self.group is not None else dist.group.WORLD)
-            ptrs = [torch.tensor([int(p) + half * numel * 4 for p in hdl.buffer_ptrs], dtype=torch.int64, device=device)
-                    for half in (0, 1)]
-            self._slots[key] = dict(buf=buf, hdl=hdl, ptrs=ptrs, turn=0)
-        s = self._slots[key]
+        s = self._slots.get(key)
+        if s is None:
+            pad = -(-numel // 64) * 64                                   # 256-byte aligned halves
+            total = 2 * pad + 64                                          # + the flags (int32 viewed through the float buffer)
+            buf = self._symm.empty(total, dtype=torch.float32, device=device)
+            buf.zero_()
+            grp = self.group if self.group is not None else dist.group.WORLD
+            hdl = self._symm.rendezvous(buf, group=grp)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=self.group)                                # every rank's flags are zero before anyone signals
+            base = [int(x) for x in hdl.buffer_ptrs]
+            i64 = dict(dtype=torch.int64, device=device)
+            s = dict(buf=buf, hdl=hdl, pad=pad, turn=0,
+                     bufs=[torch.tensor([b + half * pad * 4 for b in base], **i64) for half in (0, 1)],
+                     flags=torch.tensor([b + 2 * pad * 4 for b in base], **i64))
+            self._slots[key] = s
+        return s
+
+    def peers(self, name: str, numel: int, device) -> _cabi.FlarePeers:
+        """The FlarePeers description of the next exchange of this kind (advances its number)."""
+        s = self._slot(name, numel, device)
         half = s["turn"] & 1
         s["turn"] += 1
-        return s["buf"][half * numel:(half + 1) * numel], s["ptrs"][half], s["hdl"]
+        g = _cabi.FlarePeers()
+        g.rank, g.world = self.rank, self.world
+        g.bufs = s["bufs"][half].data_ptr()
+        g.mine = s["buf"].data_ptr() + half * s["pad"] * 4
+        g.flags = s["flags"].data_ptr()
+        g.epoch = s["turn"]
+        return g
 
-    def exchange_buffer(self, name: str, shape, device):
-        """(this rank's buffer for the next exchange, device array of all ranks' pointers, barrier handle)."""
-        numel = 1
-        for d in shape:
-            numel *= int(d)
-        local, ptrs, hdl = self._slot(name, numel, device)
-        return local.view(*shape), ptrs, hdl
+
+def _numel(*dims):
+    n = 1
+    for d in dims:
+        n *= int(d)
+    return n
 
 
 class _CPMixerFn(torch.autograd.Function):
@@ -115,27 +137,27 @@ class _CPMixerFn(torch.autograd.Function):
             y = torch.empty_like(k)
             if y.stride(-1) != 1:
                 y = torch.empty(k.shape, dtype=k.dtype, device=dev)
-            p = make_problem(q, k, scale, v=v, y=y)
-            p.n_splits = lib.flare_pick_splits(C.byref(p))
-            rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
-            peer = isinstance(ex, PeerExchange)
-            if peer:
-                merged, rec_ptrs, hdl = ex.exchange_buffer("rec", (B, H, M, D + 2), dev)
-            else:
-                merged = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=dev)
-            check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), None, ptr(rec), st), "flare_gather_partial")
-            check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, None, None, None, ptr(merged), st), "flare_combine")
             z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
             lse_m = torch.empty(B, H, M, dtype=torch.float32, device=dev)
             lse_n = torch.empty(B, H, N, dtype=torch.float32, device=dev)
-            if peer:
-                hdl.barrier()
-                check(lib.flare_combine_peers(C.byref(p), ptr(rec_ptrs), ex.world, ptr(z32), None, ptr(lse_m), None, st),
-                      "flare_combine_peers")
+            p = make_problem(q, k, scale, v=v, y=y)
+            if isinstance(ex, PeerExchange):
+                # one call: records -> merged record in peer-visible memory -> barrier -> combine over all
+                # ranks' records (peer loads) -> scatter
+                nbytes = lib.flare_fwd_workspace_bytes(C.byref(p))
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                g = ex.peers("rec", _numel(B, H, M, D + 2), dev)
+                check(lib.flare_cp_mixer_fwd(C.byref(p), ptr(q), ptr(k), ptr(v), None, ptr(y), ptr(z32), ptr(lse_m),
+                                             ptr(lse_n), ptr(ws), nbytes, C.byref(g), st), "flare_cp_mixer_fwd")
             else:
+                p.n_splits = lib.flare_pick_splits(C.byref(p))
+                rec = torch.empty(p.n_splits, B, H, M, D + 2, dtype=torch.float32, device=dev)
+                merged = torch.empty(B, H, M, D + 2, dtype=torch.float32, device=dev)
+                check(lib.flare_gather_partial(C.byref(p), ptr(q), ptr(k), ptr(v), None, ptr(rec), st), "flare_gather_partial")
+                check(lib.flare_combine(C.byref(p), ptr(rec), p.n_splits, None, None, None, ptr(merged), st), "flare_combine")
                 allrec = ex.gather_records(merged)
                 check(lib.flare_combine(C.byref(p), ptr(allrec), ex.world, ptr(z32), None, ptr(lse_m), None, st), "flare_combine")
-            check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st), "flare_scatter")
+                check(lib.flare_scatter(C.byref(p), ptr(q), ptr(k), ptr(z32), None, ptr(y), ptr(lse_n), st), "flare_scatter")
         ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n)
         ctx.scale, ctx.ex, ctx.reduce_dq, ctx.batched = scale, ex, reduce_dq, batched
         return y
@@ -157,33 +179,28 @@ class _CPMixerFn(torch.autograd.Function):
             if dv.stride(-1) != 1:
                 dv = torch.empty(v.shape, dtype=v.dtype, device=dev)
             p = make_problem(q, k, ctx.scale, v=v, y=y, dy=dy, dk=dk, dv=dv)
-            p.n_splits = lib.flare_pick_splits(C.byref(p))
-            part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=dev)
-            dz32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
-            delta = torch.empty(B, H, N, dtype=torch.float32, device=dev)
-            T = _cabi.TERM_BOTH
-            check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st), "flare_bwd_dz_partial")
-            peer = isinstance(ex, PeerExchange)
-            if peer:
-                mine, ptrs, hdl = ex.exchange_buffer("dz", (B, H, M, D), dev)
-                check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(mine), st), "flare_reduce_sum")
-                hdl.barrier()
-                check(lib.flare_reduce_sum_peers(ptr(ptrs), ex.world, B * H * M, D, ptr(dz32), st), "flare_reduce_sum_peers")
+            dq_shape = (B, H, M, D) if ctx.batched else (H, M, D)
+            dq = torch.empty(dq_shape, dtype=torch.float32, device=dev)
+            if isinstance(ex, PeerExchange):
+                nbytes = lib.flare_bwd_workspace_bytes(C.byref(p))
+                ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                gz = ex.peers("dz", _numel(B, H, M, D), dev)
+                gq = ex.peers("dq", _numel(*dq_shape), dev) if ctx.reduce_dq else None
+                check(lib.flare_cp_mixer_bwd(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(lse_m),
+                                             ptr(lse_n), ptr(dq), ptr(dk), ptr(dv), ptr(ws), nbytes, C.byref(gz),
+                                             C.byref(gq) if gq is not None else None, st), "flare_cp_mixer_bwd")
             else:
+                p.n_splits = lib.flare_pick_splits(C.byref(p))
+                part = torch.empty(p.n_splits, B, H, M, D, dtype=torch.float32, device=dev)
+                dz32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+                delta = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+                check(lib.flare_bwd_dz_partial(C.byref(p), ptr(q), ptr(k), ptr(dy), None, ptr(lse_n), ptr(part), st), "flare_bwd_dz_partial")
                 check(lib.flare_reduce_sum(ptr(part), p.n_splits, B * H * M, D, ptr(dz32), st), "flare_reduce_sum")
                 ex.sum_(dz32)
-            check(lib.flare_bwd_main(C.byref(p), T, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32), ptr(dz32),
-                                     ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), ptr(part), st),
-                  "flare_bwd_main")
-            dq_shape = (B, H, M, D) if ctx.batched else (H, M, D)
-            n_parts, rows = (p.n_splits, B * H * M) if ctx.batched else (p.n_splits * B, H * M)
-            dq = torch.empty(dq_shape, dtype=torch.float32, device=dev)
-            if peer and ctx.reduce_dq:
-                mine, ptrs, hdl = ex.exchange_buffer("dq", dq_shape, dev)
-                check(lib.flare_reduce_sum(ptr(part), n_parts, rows, D, ptr(mine), st), "flare_reduce_sum")
-                hdl.barrier()
-                check(lib.flare_reduce_sum_peers(ptr(ptrs), ex.world, rows, D, ptr(dq), st), "flare_reduce_sum_peers")
-            else:
+                check(lib.flare_bwd_main(C.byref(p), _cabi.TERM_BOTH, ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), None, ptr(z32),
+                                         ptr(dz32), ptr(lse_m), ptr(lse_n), ptr(dk), ptr(dv), ptr(delta), ptr(part), st),
+                      "flare_bwd_main")
+                n_parts, rows = (p.n_splits, B * H * M) if ctx.batched else (p.n_splits * B, H * M)
                 check(lib.flare_reduce_sum(ptr(part), n_parts, rows, D, ptr(dq), st), "flare_reduce_sum")
                 if ctx.reduce_dq:
                     ex.sum_(dq)

@@ -137,6 +137,35 @@ int flare_combine_peers(const FlareProblem* p, const float* const* rec_ptrs, int
 int flare_reduce_sum_peers(const float* const* part_ptrs, int n_parts, int64_t rows, int width,
                            float* out, flare_stream_t stream);
 
+/* A context-parallel group on one node as the kernels see it.  Every rank owns an exchange buffer and an
+ * int32[world] array of arrival flags (zero before the first exchange) in memory its peers have mapped.
+ * An exchange: write this rank's contribution into `mine`, flare_peer_barrier, read all of `bufs` in the
+ * consuming kernel.  `epoch` numbers the exchanges of the group: the same on all ranks for one exchange,
+ * larger for every later one; a buffer may be rewritten two exchanges later (use two alternately).
+ * The barrier's wait is bounded (about half a second): on expiry bit 1 of the device status word is set
+ * and the step's result is invalid, but nothing hangs.  Each rank must run on its own GPU.
+ * No counterpart in the reference. */
+typedef struct FlarePeers {
+  int32_t rank, world;
+  const float* const* bufs;    /* DEVICE array [world] of device pointers: each rank's exchange buffer */
+  float* mine;                 /* this rank's exchange buffer (the memory bufs[rank] points to)          */
+  int32_t* const* flags;       /* DEVICE array [world] of device pointers: each rank's flag array        */
+  int32_t epoch;
+} FlarePeers;
+int flare_peer_barrier(const FlarePeers* g, flare_stream_t stream);
+
+/* flare_mixer_fwd / flare_mixer_bwd over a token axis sharded across the group: k, v, y, dy, dk, dv are this
+ * rank's shard, z32 / lse_m come out identical on every rank.  The exchanges are the merged gather record
+ * (B*H*M*(D+2) floats), dZ (B*H*M*D) and, unless `dq` is NULL, dQ (the size of dq32); each FlarePeers
+ * names buffers of at least that size.  Workspaces as for the single-GPU calls. */
+int flare_cp_mixer_fwd(const FlareProblem* p, const void* q, const void* k, const void* v,
+                       const uint8_t* key_mask, void* y, float* z32, float* lse_m, float* lse_n,
+                       void* workspace, size_t workspace_bytes, const FlarePeers* rec, flare_stream_t stream);
+int flare_cp_mixer_bwd(const FlareProblem* p, const void* q, const void* k, const void* v, const void* dy,
+                       const void* y, const uint8_t* key_mask, const float* z32, const float* lse_m,
+                       const float* lse_n, float* dq32, void* dk, void* dv, void* workspace,
+                       size_t workspace_bytes, const FlarePeers* dz, const FlarePeers* dq, flare_stream_t stream);
+
 /* Second SDPA call: y = softmax_M(k q^T) z32; lse_n may be NULL. */
 int flare_scatter(const FlareProblem* p, const void* q, const void* k, const float* z32,
                   const uint8_t* key_mask, void* y, float* lse_n, flare_stream_t stream);
@@ -236,7 +265,8 @@ int flare_triple_contract(int BH, int N, int Dx, int Dy, int Dz, int dtype, cons
                           flare_stream_t stream);
 
 /* Reads (and optionally clears) the device status word of the current device; synchronises.
- * Non-zero means a tensor-core kernel gave up on a bounded wait (bit 0) and its output is
+ * Non-zero means a kernel gave up on a bounded wait (bit 0: inside a tensor-core kernel; bit 1: a peer
+ * did not arrive at flare_peer_barrier) and the output since the last clear is
  * not valid.  No counterpart in the reference.  `out` is a HOST pointer. */
 int flare_device_status(int* out, int clear);
 

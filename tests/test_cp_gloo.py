@@ -90,3 +90,49 @@ def test_shard_bounds_cover_all_tokens():
         assert spans[0][0] == 0 and spans[-1][1] == n
         for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
             assert a1 == b0 and a0 <= a1
+
+
+def _leaver(rank, world, port, q_out):
+    """Rank 1 leaves between two steps; rank 0 must learn of it from its next exchange (an error after the
+    short group timeout), not wait forever."""
+    import datetime
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    try:
+        import __graft_entry__
+        __graft_entry__.build()
+        from flare_b200.parallel import RecordExchange
+        ex = RecordExchange()
+        rec = torch.full((1, 1, 2, 4), float(rank))
+        allrec = ex.gather_records(rec)                      # step 1: everybody is there
+        assert allrec.shape[0] == world and allrec[1].eq(1.0).all()
+        if rank == 1:
+            q_out.put((rank, "left"))
+            q_out.close()
+            q_out.join_thread()                              # the message is on its way before the process goes
+            os._exit(0)                                      # between steps, nothing in flight
+        try:
+            ex.gather_records(rec)                           # step 2: the peer is gone
+            q_out.put((rank, "no error"))
+        except Exception as e:
+            q_out.put((rank, "detected"))
+    except Exception as e:  # pragma: no cover
+        q_out.put((rank, repr(e)))
+
+
+def test_a_rank_that_leaves_between_steps_is_detected():
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, 2, port, q_out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = dict(q_out.get(timeout=120) for _ in procs)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+    assert results == {1: "left", 0: "detected"}, results
