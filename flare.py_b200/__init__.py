@@ -9,9 +9,11 @@ from .mixer import (device_status, pass_counts, flare_gather, flare_multihead_mi
                     mixer_forward, set_kernel_path)
 from .triple import causal_linear, triple_attention
 from .modules import FLARE, FLAREBlock, FLAREModel, ResidualMLP
+from .cp_train import ContextParallel, ShardedPointCloud, cp_train_step, enable_context_parallel
 
 __all__ = [
     "flare_multihead_mixer", "flare_gather", "flare_scatter", "mixer_forward", "mixer_backward",
     "set_kernel_path", "device_status", "pass_counts", "flare_causal_prefill", "flare_causal_decode", "causal_state_init", "triple_attention",
     "causal_linear", "FLARE", "FLAREBlock", "FLAREModel", "ResidualMLP",
+    "ContextParallel", "ShardedPointCloud", "cp_train_step", "enable_context_parallel",
 ]

@@ -14,7 +14,8 @@
 // use, it uses fewer (same result up to fp32 summation order, less parallelism).  All calls share
 // the one array and it keeps the previous call's records: nothing in it has to start at zero
 // (each call overwrites every record it later reads), but two calls that overlap on the GPU --
-// different streams, or different host threads -- race on it and must be serialised by the caller.
+// different streams, or different host threads -- race on it and must be serialised by the caller; that
+// includes the very first call on a device, which also fills the per-device address table below.
 // The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
 // that device current); make that first call outside any stream capture.
 #include <cstdarg>

@@ -57,9 +57,11 @@ def _need_cuda(*ts):
 
 
 def _tok(t: torch.Tensor) -> torch.Tensor:
-    """A [B,H,N,D] tensor the kernels can address: unit stride on D, 16-byte aligned rows."""
+    """A [B,H,N,D] tensor the kernels can address: unit stride on D, 16-byte aligned rows, no broadcast
+    (stride 0) dimension -- a TMA tensor map cannot describe one."""
     e = t.element_size()
-    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all((s * e) % 16 == 0 for s in t.stride()[:-1])
+    ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and \
+        all((s * e) % 16 == 0 and (s != 0 or n == 1) for s, n in zip(t.stride()[:-1], t.shape[:-1]))
     return t if ok else t.contiguous()
 
 

@@ -91,6 +91,16 @@ class _FlareCore(nn.Module):
         # [C, M], reinterpreted (not transposed) as [H, M, D] at use: keeps checkpoints compatible
         self.latent_q = nn.Parameter(torch.empty(channel_dim, num_latents))
         nn.init.normal_(self.latent_q, mean=0.0, std=0.1)
+        self.cp = None      # a cp_train.ContextParallel when the token axis is sharded over ranks
+
+    def _mix(self, q, k, v, key_mask=None, dropout_p=0.0):
+        if self.cp is not None:
+            if key_mask is not None or dropout_p:
+                raise NotImplementedError("the context-parallel mixer takes neither a mask nor dropout")
+            from .parallel import flare_mixer_context_parallel
+            # the latent gradient joins the other replicated weights in the group-wide gradient sum
+            return flare_mixer_context_parallel(q, k, v, self.attn_scale, exchange=self.cp.exchange, reduce_dq=False)
+        return flare_multihead_mixer(q, k, v, scale=self.attn_scale, key_mask=key_mask, dropout_p=dropout_p)
 
     def _latents(self):
         return self.latent_q.view(self.num_heads, self.num_latents, self.head_dim)
@@ -126,7 +136,7 @@ class FLARE(_FlareCore):
             y = F.softmax(scores.transpose(-2, -1), dim=-1) @ z
         else:
             scores = None
-            y = flare_multihead_mixer(q, k, v, scale=self.attn_scale)
+            y = self._mix(q, k, v)
         return self.out_proj(_merge_heads(y)), scores
 
 
@@ -171,6 +181,7 @@ class FLAREModel(nn.Module):
                        v_proj_mlp_ratio=v_proj_mlp_ratio, num_layers_ffn=num_layers_ffn,
                        ffn_mlp_ratio=ffn_mlp_ratio, qk_norm=qk_norm)
             for _ in range(num_blocks))
+        self.checkpoint_blocks = False      # recompute each block in the backward pass (cp_train.enable_context_parallel)
         self.initialize_weights()
 
     def initialize_weights(self):
@@ -190,7 +201,11 @@ class FLAREModel(nn.Module):
         collected = []
         h = self.in_proj(x)
         for blk in self.blocks:
-            h, s = blk(h, return_scores=return_scores)
+            if self.checkpoint_blocks and self.training and not return_scores and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                h, s = checkpoint(blk, h, use_reentrant=False)
+            else:
+                h, s = blk(h, return_scores=return_scores)
             collected.append(s)
         out = self.out_proj(h)
         return (out, collected) if return_scores else out
@@ -217,8 +232,7 @@ class LraFLARE(_FlareCore):
         if self.rope is not None:
             k = self.rope(k)
         drop = self.attn_drop_p if self.training else 0.0
-        y = flare_multihead_mixer(self._latents(), k, v, scale=self.attn_scale, key_mask=attention_mask,
-                                  dropout_p=drop)
+        y = self._mix(self._latents(), k, v, key_mask=attention_mask, dropout_p=drop)
         y = self.out_proj(_merge_heads(y))
         return F.dropout(y, p=self.proj_drop_p if self.training else 0.0)
 

@@ -216,7 +216,10 @@ def flare_mixer_context_parallel(q, k_local, v_local, scale: float = 1.0,
     tokens.  With ``reduce_dq`` the latent gradient is summed over the group inside the
     backward; pass False when a DDP-style reducer over the same group already does it.
     """
+    from .mixer import _autocast, _same_dtype
     ex = exchange or RecordExchange(group)
     if q.dim() == 4 and q.stride(0) == 0:
         q = q[0]
+    q, k_local, v_local = _autocast(q, k_local, v_local)
+    _same_dtype(q, k_local, v_local)
     return _CPMixerFn.apply(q, k_local, v_local, float(scale), ex, reduce_dq)

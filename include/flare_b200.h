@@ -215,7 +215,8 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
  * Outputs as flare_combine: z32 fp32 [B,H,M,D], z_out in p->dtype, lse_m fp32 [B,H,M]; any may be
  * NULL but not all.  All calls share the array: calls that overlap on the GPU (other streams,
  * other host threads) race and must be serialised by the caller.  The first call on a device
- * resolves the array's device address and should be made outside any stream capture. */
+ * resolves the array's device address and should be made outside any stream capture; like every call
+ * of this entry point it must not run concurrently with another one. */
 #define FLARE_NOALLOC_SCRATCH_BYTES (16u << 20)
 int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, const void* v,
                          const uint8_t* key_mask, float* z32, void* z_out, float* lse_m,

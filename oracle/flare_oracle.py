@@ -36,7 +36,7 @@ import torch.nn.functional as F
 __all__ = [
     "mixer_sdpa", "mixer_explicit", "mixer_lra", "gather", "scatter",
     "mixer_fwd_stats", "mixer_bwd_closed_form", "mixer_fwd_bwd_streamed", "gather_partials",
-    "lse_combine", "causal_dense", "causal_recurrent", "causal_chunked",
+    "lse_combine", "causal_dense", "causal_recurrent", "causal_chunked", "causal_bwd_autograd", "causal_bwd_chunked",
     "triple_attention", "triple_attention_bwd", "causal_linear", "rel_l2",
 ]
 
@@ -299,6 +299,86 @@ def causal_chunked(q, k, v, scale: float = 1.0, chunk: int = 64):
         a0 = a[..., None] * a0 + E @ vv
         m0 = mu
     return torch.cat(out, dim=2), (m0, l0, a0)
+
+
+def causal_bwd_autograd(q, k, v, dy, scale: float = 1.0):
+    """dq, dk, dv of causal FLARE by autograd through the dense masked-softmax form (small N)."""
+    q = q.detach().clone().requires_grad_(True)
+    k = k.detach().clone().requires_grad_(True)
+    v = v.detach().clone().requires_grad_(True)
+    causal_dense(q, k, v, scale).backward(dy)
+    return q.grad, k.grad, v.grad
+
+
+def causal_bwd_chunked(q, k, v, dy, scale: float = 1.0, chunk: int = 64):
+    """dq, dk, dv of causal FLARE as a reverse scan over chunks: the algorithm of the CUDA backward.
+
+    Forward states (m, l, acc) at the chunk starts come from the same exclusive log-sum-exp prefix the
+    prefill uses.  Walking the chunks from the last to the first, the suffix state
+    R_m = sum_{t > chunk} G_tm g_t (M x D) and r_m = -sum_{t > chunk} G_tm (g_t . z_tm), G = A / l, is
+    carried relative to the running maximum mu of the chunk that produced it, so that every factor that
+    multiplies it is at most one.  Inside a chunk (E' = e^{S - mu}, l' = a l0 + cumsum E', G' = A / l',
+    X_nt = v_n . g_t, c_mt = g_t . z_tm = (a (acc0 g^T) + E' triu(X)) / l'):
+        dS2 = A (c - delta),  delta_t = sum_m A_mt c_mt
+        dV  = E'^T Rin + tril(G'^T E')^T-masked g
+        dS1 = E' (Rin V^T + rin + G' tril(X^T) - revcumsum(G' c))
+        dQ += scale dS K,  dK = scale dS^T Q.
+    """
+    B, H, N, D = k.shape
+    qe = _expand_q(q, B)
+    M = qe.shape[2]
+    bounds = [(c0, min(N, c0 + chunk)) for c0 in range(0, N, chunk)]
+    # forward: exclusive prefix of the per-chunk records
+    m, l, acc = gather_partials(q, k, v, scale, bounds)
+    starts = []
+    m0 = torch.full((B, H, M), float("-inf"), dtype=k.dtype)
+    l0 = torch.zeros(B, H, M, dtype=k.dtype)
+    a0 = torch.zeros(B, H, M, D, dtype=k.dtype)
+    for c in range(len(bounds)):
+        starts.append((m0, l0, a0))
+        mn = torch.maximum(m0, m[c])
+        wa = torch.where(torch.isfinite(m0), torch.exp(m0 - mn), torch.zeros_like(mn))
+        wc = torch.where(torch.isfinite(m[c]), torch.exp(m[c] - mn), torch.zeros_like(mn))
+        l0 = wa * l0 + wc * l[c]
+        a0 = wa[..., None] * a0 + wc[..., None] * acc[c]
+        m0 = mn
+    dq = torch.zeros_like(qe)
+    dk, dv = torch.zeros_like(k), torch.zeros_like(v)
+    Rh = torch.zeros(B, H, M, D, dtype=k.dtype)
+    rh = torch.zeros(B, H, M, dtype=k.dtype)
+    nu = torch.full((B, H, M), float("inf"), dtype=k.dtype)
+    for c in reversed(range(len(bounds))):
+        n0, n1 = bounds[c]
+        kk, vv, gg = k[:, :, n0:n1], v[:, :, n0:n1], dy[:, :, n0:n1]
+        T = n1 - n0
+        m0, l0, a0 = starts[c]
+        S = scale * (qe @ kk.transpose(-2, -1))                    # [B,H,M,T]
+        mu = torch.maximum(m0, S.max(-1).values)
+        a = torch.where(torch.isfinite(m0), torch.exp(m0 - mu), torch.zeros_like(mu))
+        E = torch.exp(S - mu[..., None])
+        lp = (a * l0)[..., None] + torch.cumsum(E, dim=-1)
+        A = torch.softmax(S, dim=-2)
+        G = A / lp
+        X = vv @ gg.transpose(-2, -1)                               # [B,H,T(n),T(t)]
+        cm = (a[..., None] * (a0 @ gg.transpose(-2, -1)) + E @ torch.triu(X)) / lp      # c_mt
+        delta = (A * cm).sum(-2, keepdim=True)
+        dS2 = A * (cm - delta)
+        w = torch.where(torch.isfinite(nu), torch.exp(mu - nu), torch.zeros_like(mu))  # rescale the carry-in
+        Rin, rin = w[..., None] * Rh, w * rh
+        W = G.transpose(-2, -1) @ E                                 # [B,H,T(t),T(n)]
+        dv[:, :, n0:n1] = E.transpose(-2, -1) @ Rin + torch.tril(W).transpose(-2, -1) @ gg
+        Gc = G * cm
+        rev = torch.flip(torch.cumsum(torch.flip(Gc, [-1]), dim=-1), [-1])             # sum_{t >= n}
+        de = Rin @ vv.transpose(-2, -1) + rin[..., None] + G @ torch.tril(X.transpose(-2, -1)) - rev
+        dS = E * de + dS2
+        dq += scale * (dS @ kk)
+        dk[:, :, n0:n1] = scale * (dS.transpose(-2, -1) @ qe)
+        Rh = Rin + G @ gg
+        rh = rin - Gc.sum(-1)
+        nu = mu
+    if q.dim() == 3:
+        dq = dq.sum(0)
+    return dq, dk, dv
 
 
 # ---------------------------------------------------------------------------

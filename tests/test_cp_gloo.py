@@ -14,6 +14,9 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+from oracle import flare_oracle as O  # noqa: E402
+
 ROOT = Path(__file__).resolve().parents[1]
 
 
@@ -136,3 +139,52 @@ def test_a_rank_that_leaves_between_steps_is_detected():
             if p.is_alive():
                 p.terminate()
     assert results == {1: "left", 0: "detected"}, results
+
+
+def _glue_worker(rank, world, port, q_out):
+    """The training glue without the mixer: sharded synthetic data, the global-mean loss and the group-wide
+    gradient sum give, on a pointwise model with replicated weights, the gradient of the unsharded loss."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import __graft_entry__
+        __graft_entry__.build()
+        from flare_b200.cp_train import ContextParallel, ShardedPointCloud
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(5, 8), torch.nn.Tanh(), torch.nn.Linear(8, 2)).double()
+        cp = ContextParallel(bucket_bytes=256)                       # several buckets even for this tiny model
+        N = 1000
+        shards = [ShardedPointCloud(N, 2, 2, r, world, seed=3, device="cpu", dtype=torch.float64, multiple=8) for r in range(world)]
+        assert shards[0].n0 == 0 and shards[-1].n1 == N and all(a.n1 == b.n0 for a, b in zip(shards, shards[1:]))
+        x, t = shards[rank].sample(0)
+        n_global = cp.global_count(t.numel(), "cpu")
+        assert n_global == N * 2
+        loss_local = (model(x) - t).square().sum() / n_global
+        loss_local.backward()
+        cp.reduce_gradients(model)
+        # the unsharded problem, rebuilt from every rank's shard
+        xs, ts = zip(*(sh.sample(0) for sh in shards))
+        ref = torch.nn.Sequential(torch.nn.Linear(5, 8), torch.nn.Tanh(), torch.nn.Linear(8, 2)).double()
+        ref.load_state_dict(model.state_dict())
+        torch.nn.functional.mse_loss(ref(torch.cat(xs, 1)), torch.cat(ts, 1)).backward()
+        for a, b in zip(model.parameters(), ref.parameters()):
+            assert O.rel_l2(a.grad, b.grad) < 1e-12
+        q_out.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        q_out.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_training_glue_among_cpu_ranks():
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_glue_worker, args=(r, 3, port, q_out)) for r in range(3)]
+    for p in procs:
+        p.start()
+    results = [q_out.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(msg == "ok" for _, msg in results), results

@@ -129,3 +129,81 @@ def test_peer_barrier_gives_up_when_the_peer_never_arrives(cuda_dev):
     assert flags[1, 0].item() == 1                         # the signal to the peer was sent
     assert fb.device_status() == 0                         # cleared, and the device still answers
     assert torch.ones(4, device=dev).sum().item() == 4.0
+
+
+def _model_worker(rank, world, port, q_out, exchange):
+    """A FLAREModel whose points are sharded over the ranks, trained one step with the context-parallel glue,
+    against the same model on one GPU with all the points (built from the ranks' shards)."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import flare_b200 as fb
+        from oracle import flare_oracle as O
+        torch.manual_seed(0)
+        kw = dict(in_dim=5, out_dim=2, channel_dim=64, num_blocks=2, num_heads=2, num_latents=64)
+        model = fb.FLAREModel(**kw).to(dev)
+        ref = fb.FLAREModel(**kw).to(dev)
+        ref.load_state_dict(model.state_dict())
+        cp = fb.ContextParallel(exchange=exchange)
+        fb.enable_context_parallel(model, cp, checkpoint_blocks=True)
+        N = 3000
+        shards = [fb.ShardedPointCloud(N, 2, 2, r, world, seed=11, device=dev, multiple=128) for r in range(world)]
+        x, t = shards[rank].sample(0)
+        opt = torch.optim.SGD(model.parameters(), lr=0.0)             # keeps the weights: gradients are compared
+        model.train()
+        n_global = cp.global_count(t.numel(), dev)
+        loss_local = (model(x) - t).square().sum() / n_global
+        loss_local.backward()
+        cp.reduce_gradients(model)
+        xs, ts = zip(*(sh.sample(0) for sh in shards))                # every rank rebuilds the unsharded sample
+        loss_ref = torch.nn.functional.mse_loss(ref(torch.cat(xs, 1)), torch.cat(ts, 1))
+        loss_ref.backward()
+        loss = loss_local.detach().clone()
+        dist.all_reduce(loss)
+        problems = []
+        if abs(loss.item() - loss_ref.item()) > 1e-5 * abs(loss_ref.item()):
+            problems.append(("loss", loss.item(), loss_ref.item()))
+        for (n, a), b in zip(model.named_parameters(), ref.parameters()):
+            e = O.rel_l2(a.grad.cpu(), b.grad.cpu())
+            if e > 2e-4:
+                problems.append((n, e))
+        # and the step function end to end under bf16 autocast
+        opt2 = torch.optim.SGD(model.parameters(), lr=1e-3)
+        l2 = fb.cp_train_step(model, opt2, x, t, cp, autocast_dtype=torch.bfloat16, clip_grad_norm=1.0)
+        if not torch.isfinite(l2) or abs(l2.item() - loss_ref.item()) > 5e-2 * abs(loss_ref.item()):
+            problems.append(("autocast step loss", l2.item(), loss_ref.item()))
+        if fb.device_status():
+            problems.append("device status")
+        assert not problems, problems
+        q_out.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        import traceback
+        q_out.put((rank, repr(e) + traceback.format_exc()[-600:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange", ["collective", "peer"])
+def test_sharded_model_step_equals_the_unsharded_one(cuda_dev, exchange):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import __graft_entry__
+    __graft_entry__.build()
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_model_worker, args=(r, 2, port, q_out, exchange)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = [q_out.get(timeout=300) for _ in procs]
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    assert all(msg == "ok" for _, msg in results), results

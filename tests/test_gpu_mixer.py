@@ -344,3 +344,57 @@ def test_full_size_properties(fb, cuda_dev):
     assert torch.equal(tc2[0], tc[0])
     for n, a, b in zip(("dq", "dk", "dv"), tc2[1:], tc[1:]):
         assert torch.equal(a.float(), b.float() * 2), n
+
+
+# ------------------------------------------------------------------------------------------------
+# the call-site variants of the reference that share this path
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_shared_latents_expanded_over_heads(fb, cuda_dev, dtype):
+    """BigFLARE's shared_latents (pdebench/models/flare_ablations.py:100-101): one [M,D] latent set expanded
+    (stride 0) over the heads; its gradient is the sum over heads."""
+    B, H, N, M, D = 2, 4, 700, 64, 32
+    _, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=51)
+    q1 = (torch.randn(1, M, D, generator=torch.Generator().manual_seed(52)) * D ** -0.25).to(dtype)
+    dev = cuda_dev
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q1, k, v))
+    tc0, simt0 = fb.pass_counts()
+    y = fb.flare_multihead_mixer(qd.expand(H, -1, -1).unsqueeze(0).expand(B, -1, -1, -1), kd, vd)
+    y.backward(dy.to(dev))
+    torch.cuda.synchronize()
+    tc1, simt1 = fb.pass_counts()
+    if dtype == torch.bfloat16:
+        assert simt1 == simt0 and tc1 - tc0 == 4
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q1, k, v))
+    yr = O.mixer_sdpa(qf.expand(H, -1, -1), kf, vf, 1.0)
+    yr.backward(dy.float())
+    got = [y.float().cpu(), qd.grad.float().cpu(), kd.grad.float().cpu(), vd.grad.float().cpu()]
+    assert got[1].shape == (1, M, D)
+    assert_close(got, [yr.detach(), qf.grad, kf.grad, vf.grad], TOL[dtype])
+
+
+def test_qk_norm_and_output_gate_variants(fb, cuda_dev):
+    """qk_norm (pdebench/models/flare.py:130-132: a LayerNorm over D on q and k in front of the two calls) and
+    the sigmoid output gate of pdebench/models/unloopy.py:98-101: both stay in torch around the operator and
+    must differentiate through it."""
+    torch.manual_seed(3)
+    B, N, C, H, M = 2, 300, 64, 4, 32
+    D = C // H
+    dev = cuda_dev
+    att = fb.FLARE(channel_dim=C, num_heads=H, num_latents=M, qk_norm=True).to(dev)
+    gate = torch.nn.Linear(C, C).to(dev)
+    x = torch.randn(B, N, C, device=dev, requires_grad=True)
+
+    def run(fused):
+        x.grad = None
+        att.zero_grad(set_to_none=True)
+        gate.zero_grad(set_to_none=True)
+        y, _ = att(x, return_scores=not fused)              # the materialising branch is plain torch (attn_scale = 1)
+        out = (y * gate(x).sigmoid()).square().mean()
+        out.backward()
+        return out.item(), x.grad.clone(), att.latent_q.grad.clone(), att.k_norm.weight.grad.clone()
+
+    a, b = run(True), run(False)
+    assert abs(a[0] - b[0]) <= 1e-5 * abs(b[0])
+    for u, w in zip(a[1:], b[1:]):
+        assert O.rel_l2(u.cpu(), w.cpu()) <= 1e-4

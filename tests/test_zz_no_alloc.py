@@ -48,10 +48,10 @@ def _existing_path(cabi, make_problem, q, k, v, scale):
     return z32, lse
 
 
-def _noalloc(cabi, make_problem, q, k, v, scale):
+def _noalloc(cabi, make_problem, q, k, v, scale, n_splits=0):
     B, H, N, D = k.shape
     M = q.shape[-2]
-    p = make_problem(q, k, scale, v=v)
+    p = make_problem(q, k, scale, v=v, n_splits=n_splits)
     z32 = torch.full((B, H, M, D), float("nan"), dtype=torch.float32, device=k.device)
     z = torch.empty(B, H, M, D, dtype=k.dtype, device=k.device)
     lse = torch.full((B, H, M), float("nan"), dtype=torch.float32, device=k.device)
@@ -78,6 +78,26 @@ def test_two_calls_in_a_row_match_the_workspace_entry_points(env, cuda_dev, dtyp
         # and against the CPU oracle, like every other parity test
         z_o, L_o = O.gather(q.float(), k.float(), v.float(), scale)
         assert O.rel_l2(z32.cpu(), z_o) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_more_ranges_asked_for_than_fit(env, cuda_dev, dtype):
+    """B=8, H=8, M=256, D=32: one record set is 2.1 MiB, seven fit in the 16 MiB array.  Asking for 16
+    token ranges makes the entry point fall back to 7; N = 2000 rounds each range up to 384 tokens, so
+    only 6 of the 7 are non-empty and the last one must come out as a neutral record, not as whatever
+    the previous call left there (large finite records, written first on purpose)."""
+    cabi, make_problem = env
+    B, H, N, M, D = 8, 8, 2000, 256, 32
+    big_q, big_k, big_v, _ = O.make_inputs(B, H, 4000, M, D, dtype=dtype, seed=5)
+    _noalloc(cabi, make_problem, (big_q * 3).to(cuda_dev), (big_k * 3).to(cuda_dev), (big_v * 100).to(cuda_dev), 1.0)
+    q, k, v, _ = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=6)
+    qd, kd, vd = (t.to(cuda_dev) for t in (q, k, v))
+    z_ref, lse_ref = _existing_path(cabi, make_problem, qd, kd, vd, 1.0)
+    z32, z, lse = _noalloc(cabi, make_problem, qd, kd, vd, 1.0, n_splits=16)
+    tol = TOL[dtype]
+    assert torch.isfinite(z32).all() and torch.isfinite(lse).all()
+    assert O.rel_l2(z32, z_ref) <= tol
+    assert O.rel_l2(lse, lse_ref) <= max(tol * 1e-2, 1e-6)
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused(env, cuda_dev):
