@@ -585,6 +585,65 @@ def run_sdpa_gpu(args):
         config=dict(workload=f"sdpa_gpu: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd"))), flush=True)
 
 
+def run_cp_encoder(args):
+    """Secondary line: the context-parallel FLARE encoder as a training step -- 3-D point cloud (3 coordinates
+    + 4 channels), hidden 256, 8 heads (D = 32), 512 latents, 4 blocks, bf16 autocast, MSE, per-block activation
+    checkpointing, the points sharded over the ranks.  16,777,216 points on 8 GPUs; with fewer ranks the same
+    2,097,152 points per rank unless --tokens says otherwise."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import __graft_entry__
+    if rank == 0:
+        __graft_entry__.build()
+    dist.barrier()
+    import flare_b200 as fb
+    n_points = args.tokens or (2_097_152 * world)
+    torch.manual_seed(0)
+    model = fb.FLAREModel(in_dim=7, out_dim=1, channel_dim=256, num_blocks=4, num_heads=8, num_latents=512).to(dev)
+    kind = os.environ.get("FLARE_CP_EXCHANGE", "peer" if world > 1 else "collective")
+    cp = fb.ContextParallel(exchange=kind)
+    fb.enable_context_parallel(model, cp, checkpoint_blocks=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4)
+    data = fb.ShardedPointCloud(n_points, 4, 1, rank, world, seed=0, device=dev)
+    x, t = data.sample(0)
+
+    def step():
+        return fb.cp_train_step(model, opt, x, t, cp, autocast_dtype=torch.bfloat16, clip_grad_norm=1.0)
+
+    for _ in range(max(args.warmup, 1)):
+        loss = step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        loss = step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    peak = torch.tensor([torch.cuda.max_memory_allocated(dev) / 2 ** 30], device=dev)
+    dist.all_reduce(peak, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(json.dumps(dict(
+            metric="context-parallel FLARE encoder training step, Mpoints/s", value=n_points / ms.item() / 1e3,
+            unit="Mpoints/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 1), ms_per_step=ms.item(),
+            higher_is_better=True, scaling="weak" if not args.tokens else "strong", dtype="bf16", data="synthetic",
+            loss=loss.item(), peak_memory_gib=peak.item(), status=fb.device_status(),
+            config=dict(workload=f"cp_encoder: N={n_points} points, C=256 H=8 D=32 M=512, 4 blocks, bf16 autocast, "
+                                 f"AdamW, per-block checkpointing", points_per_rank=data.n1 - data.n0, exchange=kind))),
+              flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -594,7 +653,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override N (profiling on a smaller case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained leg")
-    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "sdpa_gpu"],
+    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "sdpa_gpu", "cp_encoder"],
                     help="mixer: the headline line; causal: a secondary line for causal prefill/decode; sdpa_gpu: "
                          "a secondary line timing the reference's own two SDPA calls + autograd on this GPU")
     args = ap.parse_args()
@@ -602,6 +661,8 @@ def main():
         run_causal(args)
     elif args.workload == "sdpa_gpu":
         run_sdpa_gpu(args)
+    elif args.workload == "cp_encoder":
+        run_cp_encoder(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

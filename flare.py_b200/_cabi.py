@@ -27,6 +27,7 @@ class FlareProblem(C.Structure):
         ("q_stride", C.c_int64 * 3), ("k_stride", C.c_int64 * 3), ("v_stride", C.c_int64 * 3),
         ("y_stride", C.c_int64 * 3), ("dy_stride", C.c_int64 * 3), ("dk_stride", C.c_int64 * 3),
         ("dv_stride", C.c_int64 * 3),
+        ("dropout_p", C.c_float), ("dropout_seed", C.c_uint64),
     ]
 
 

@@ -19,7 +19,36 @@ struct Ctx {
   int chunk;             // tokens per range (multiple of 128)
   int terms;
   long long qs[3], ks[3], vs[3], ys[3], dys[3], dks[3], dvs[3];
+  float drop_p;                      // attention dropout probability (0 = off)
+  unsigned long long drop_seed;
 };
+
+// Attention dropout: the keep decision of one softmax weight is a hash of (which softmax, b*H+h, m, n) and
+// the seed -- any kernel, whatever its orientation, and the host can recompute it.  `which`: 1 = gather
+// weights P_mn, 2 = scatter weights A_mn.
+struct DropArgs {
+  uint32_t seed_lo, seed_hi;
+  uint32_t thresh;                   // keep iff hash >= thresh; thresh = p * 2^32
+  float inv_keep;                    // 1 / (1 - p)
+  int on;
+};
+inline DropArgs make_drop(float p, unsigned long long seed) {
+  DropArgs d;
+  d.seed_lo = (uint32_t)seed; d.seed_hi = (uint32_t)(seed >> 32);
+  const double t = (double)p * 4294967296.0;
+  d.thresh = t >= 4294967295.0 ? 4294967295u : (uint32_t)t;
+  d.inv_keep = p < 1.f ? 1.f / (1.f - p) : 0.f;
+  d.on = p > 0.f ? 1 : 0;
+  return d;
+}
+// row = (which * BH + bh) * M + m
+__host__ __device__ __forceinline__ uint32_t drop_hash(uint32_t n, uint32_t row, uint32_t seed_lo, uint32_t seed_hi) {
+  uint32_t x = (n * 0x9E3779B1u) ^ seed_lo;
+  const uint32_t y = (row * 0x85EBCA77u) ^ seed_hi;
+  x ^= y + 0x165667B1u + (x << 6) + (x >> 2);
+  x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+  return x;
+}
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }

@@ -34,6 +34,7 @@ int check_problem(const FlareProblem* p) {
     return fail(FLARE_EUNSUPPORTED, "head dim %d not in {8,16,32,64,128}", p->D);
   if (!(p->scale > 0.f)) return fail(FLARE_EINVAL, "scale must be > 0");
   if (p->n_splits < 0) return fail(FLARE_EINVAL, "n_splits < 0");
+  if (!(p->dropout_p >= 0.f) || p->dropout_p >= 1.f) return fail(FLARE_EINVAL, "dropout_p must be in [0, 1)");
   if ((long long)p->B * p->H > 65535) return fail(FLARE_EUNSUPPORTED, "B*H > 65535");
   return FLARE_OK;
 }
@@ -75,6 +76,8 @@ Ctx make_ctx(const FlareProblem* p, int terms = FLARE_TERM_BOTH) {
   c.chunk = (int)(((per + 127) / 128) * 128);
   if (c.chunk < 128) c.chunk = 128;
   c.terms = terms;
+  c.drop_p = p->dropout_p;
+  c.drop_seed = p->dropout_seed;
   for (int i = 0; i < 3; ++i) {
     c.qs[i] = p->q_stride[i]; c.ks[i] = p->k_stride[i]; c.vs[i] = p->v_stride[i];
     c.ys[i] = p->y_stride[i]; c.dys[i] = p->dy_stride[i]; c.dks[i] = p->dk_stride[i];
@@ -135,6 +138,9 @@ int flare_gather_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("v", v, p->v_stride, p->dtype));
   if (!rec) return fail(FLARE_EINVAL, "rec is null");
   Ctx c = make_ctx(p);
+  const bool drop = p->dropout_p > 0.f;
+  if (drop && (g_path.load() == FLARE_PATH_SIMT || !tc_lat2_supported(c, p->dtype)))
+    return fail(FLARE_EUNSUPPORTED, "attention dropout needs the tensor-core kernels (bf16/fp16, D in {16,32})");
   if (g_path.load() != FLARE_PATH_SIMT && (tc_lat2_supported(c, p->dtype) || (!key_mask && tc_lat_supported(c, p->dtype)))) {
     // head dims 16 and 32: the decoupled-schedule kernel; 64 (bf16, no mask): the first-generation one
     const int rc = tc_lat2_supported(c, p->dtype) ? tc_gather_partial2(c, p->dtype, q, k, v, key_mask, rec, (cudaStream_t)stream)
@@ -182,6 +188,8 @@ int flare_scatter(const FlareProblem* p, const void* q, const void* k, const flo
   if (!z32) return fail(FLARE_EINVAL, "z32 is null");
   if (p->N == 0) return FLARE_OK;
   Ctx c = make_ctx(p);
+  if (p->dropout_p > 0.f && (g_path.load() == FLARE_PATH_SIMT || !tc_scatter2_supported(c, p->dtype)))
+    return fail(FLARE_EUNSUPPORTED, "attention dropout needs the tensor-core kernels (bf16/fp16, D in {16,32}, M a multiple of 32)");
   if (g_path.load() != FLARE_PATH_SIMT && (tc_scatter_supported(c, p->dtype) || tc_scatter2_supported(c, p->dtype))) {
     const int rc = tc_scatter2_supported(c, p->dtype) ? tc_scatter2(c, p->dtype, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream)
                                                       : tc_scatter(c, q, k, z32, key_mask, y, lse_n, (cudaStream_t)stream);
@@ -203,6 +211,8 @@ int flare_bwd_dz_partial(const FlareProblem* p, const void* q, const void* k, co
   TRY(check_tok("dy", dy, p->dy_stride, p->dtype));
   if (!lse_n || !dz_part) return fail(FLARE_EINVAL, "lse_n or dz_part is null");
   Ctx c = make_ctx(p);
+  if (p->dropout_p > 0.f && (g_path.load() == FLARE_PATH_SIMT || !tc_lat2_supported(c, p->dtype)))
+    return fail(FLARE_EUNSUPPORTED, "attention dropout needs the tensor-core kernels (bf16/fp16, D in {16,32})");
   if (g_path.load() != FLARE_PATH_SIMT && (tc_lat2_supported(c, p->dtype) || (!key_mask && tc_lat_supported(c, p->dtype)))) {
     const int rc = tc_lat2_supported(c, p->dtype)
                        ? tc_dz_partial2(c, p->dtype, q, k, dy, key_mask, lse_n, dz_part, (cudaStream_t)stream)
@@ -344,7 +354,7 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
     const int* flag = nullptr;
     int rc = FLARE_OK;
     const size_t have = (size_t)p->B * p->H * (size_t)p->N * sizeof(float);
-    const bool fast = p->dtype == FLARE_BF16 && terms == FLARE_TERM_BOTH && !key_mask && g_path.load() != FLARE_PATH_TC_EXACT &&
+    const bool fast = p->dtype == FLARE_BF16 && terms == FLARE_TERM_BOTH && !key_mask && !(p->dropout_p > 0.f) && g_path.load() != FLARE_PATH_TC_EXACT &&
                       tc_bwd_fast_supported(c, p->dtype) && delta_n && (reinterpret_cast<uintptr_t>(delta_n) & 255) == 0 &&
                       have >= tc_bwd_fast_scratch_bytes(c);
     if (fast)
@@ -354,6 +364,8 @@ int flare_bwd_main(const FlareProblem* p, int terms, const void* q, const void* 
     if (rc == FLARE_OK) { ++g_tc_passes; return after_launch("bwd_main (tcgen05)"); }
     if (rc != FLARE_EUNSUPPORTED) return fail(rc, "bwd_main (tcgen05): launch setup failed");
   }
+  if (p->dropout_p > 0.f)
+    return fail(FLARE_EUNSUPPORTED, "attention dropout needs the tensor-core kernels (bf16/fp16, D in {16,32}, M <= 1024)");
   if (use_s && !delta_n) return fail(FLARE_EINVAL, "bwd_main: delta_n scratch is null");
   TRY(flare_bwd_tokens(p, terms, q, k, v, dy, y, key_mask, z32, dz32, lse_m, lse_n, dk, dv, delta_n, stream));
   TRY(flare_bwd_dq_partial(p, terms, q, k, v, dy, key_mask, z32, dz32, lse_m, lse_n, delta_n, dq_part, stream));

@@ -48,6 +48,7 @@ struct BwdArgs {
   int M_total, m0;             // this launch covers latents [m0, m0 + M) of M_total
   int terms;                   // FLARE_TERM_GATHER | FLARE_TERM_SCATTER
   const uint8_t* mask;         // [B,N] key-padding mask (non-zero = keep) or null
+  DropArgs drop;               // attention dropout: P' = D1 P / (1-p) feeds dV, A' = D2 A / (1-p); dS uses the masks too
   int* status;
   const int* flag;             // [B*H] or null: run only the (b, h) whose flag is 1
 };
@@ -223,6 +224,9 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
     __syncthreads();
     const float2 cd = sCD[st * 128 + row];
     const float c2n = cd.x, deln = cd.y, bias = sBias[st * 128 + row];
+    const uint32_t ntok = (uint32_t)(tok0 + row);
+    const uint32_t drow_g = (uint32_t)(1 * a.B * a.H + bh) * (uint32_t)a.M_total;     // gather weights' rows
+    const uint32_t drow_s = (uint32_t)(2 * a.B * a.H + bh) * (uint32_t)a.M_total;     // scatter weights' rows
 
     for (int j = 0; j < n_mblk; ++j) {
       if (tid == 0) {
@@ -263,18 +267,31 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
         for (int e = 0; e < 8; ++e) {
           const float4 l4 = *reinterpret_cast<const float4*>(&ld[16 * i + 2 * e]);   // {L2,Dl} x 2
           const float x0 = fmaf(__uint_as_float(rs[2 * e]), sl, bias), x1 = fmaf(__uint_as_float(rs[2 * e + 1]), sl, bias);
-          const float p0 = ex2(x0 - l4.x), p1 = ex2(x1 - l4.z);
+          float p0 = ex2(x0 - l4.x), p1 = ex2(x1 - l4.z);
+          float t10 = __uint_as_float(r1[2 * e]), t11 = __uint_as_float(r1[2 * e + 1]);
+          float t20 = __uint_as_float(r2[2 * e]), t21 = __uint_as_float(r2[2 * e + 1]);
+          float pv0 = p0, pv1 = p1;                 // the weights dV sees
+          if (a.drop.on) {
+            // z = (D1 P / (1-p)) V and y = (D2 A / (1-p))^T z: the upstream factors dZ V^T and Z dY^T pass the
+            // same masks before Delta_m = dZ_m . Z_m and delta_n = dY_n . Y_n are subtracted
+            const uint32_t mcol = (uint32_t)(a.m0 + j * 128 + colb + 16 * i + 2 * e);
+            const float k10 = drop_hash(ntok, drow_g + mcol, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? a.drop.inv_keep : 0.f;
+            const float k11 = drop_hash(ntok, drow_g + mcol + 1, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? a.drop.inv_keep : 0.f;
+            const float k20 = drop_hash(ntok, drow_s + mcol, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? a.drop.inv_keep : 0.f;
+            const float k21 = drop_hash(ntok, drow_s + mcol + 1, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? a.drop.inv_keep : 0.f;
+            pv0 *= k10; pv1 *= k11; t10 *= k10; t11 *= k11; t20 *= k20; t21 *= k21;
+          }
           float s0 = 0.f, s1 = 0.f;
           if (use_s) {
             const float a0 = ex2(x0 - c2n), a1 = ex2(x1 - c2n);
-            s0 = a0 * (__uint_as_float(r2[2 * e]) - deln);
-            s1 = a1 * (__uint_as_float(r2[2 * e + 1]) - deln);
+            s0 = a0 * (t20 - deln);
+            s1 = a1 * (t21 - deln);
           }
           if (use_g) {
-            s0 = fmaf(p0, __uint_as_float(r1[2 * e]) - l4.y, s0);
-            s1 = fmaf(p1, __uint_as_float(r1[2 * e + 1]) - l4.w, s1);
+            s0 = fmaf(p0, t10 - l4.y, s0);
+            s1 = fmaf(p1, t11 - l4.w, s1);
           }
-          pp[e] = Op16<T16>::pack(p0, p1);
+          pp[e] = Op16<T16>::pack(pv0, pv1);
           pd[e] = Op16<T16>::pack(s0, s1);
         }
         tmem_st8(lane_base + cS + colb + 8 * i, pp);
@@ -405,6 +422,7 @@ static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v,
   a.dq_part = dq_part;
   a.terms = c.terms;
   a.mask = mask;
+  a.drop = make_drop(c.drop_p, c.drop_seed);
   a.status = tc_status_ptr();
   a.flag = flag;
   constexpr int smem = BwdSmem<D>::kBytes;

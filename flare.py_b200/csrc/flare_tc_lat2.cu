@@ -45,6 +45,7 @@ struct Lat2Args {
   int* status;
   int c_bulk;                  // MODE 1: C_n rows may be fetched with 16-byte-aligned bulk copies
   const uint8_t* mask;         // [B,N] key-padding mask (non-zero = keep) or null
+  DropArgs drop;               // attention dropout of this pass's softmax weights
 };
 
 constexpr int kLat2Stages = 4;
@@ -75,9 +76,10 @@ constexpr int kLat2Softmax = 256;
 
 // One chunk of 16 score columns of one row: P = 2^(S sl - m) (MODE 0) or 2^(S sl - C2) (MODE 1, C2 = C log2e),
 // packed to 16-bit pairs; the two running sums take alternate columns.  kbits: keep bit of each column.
-template <int MODE, bool MASKED, typename T16>
+// DROP: the packed weights (not the sums) additionally pass the dropout mask of row `drow`, tokens n16 .. n16 + 15.
+template <int MODE, bool MASKED, bool DROP, typename T16>
 __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_run, const float* c16, uint32_t kbits,
-                                           uint32_t* pk, float& s0, float& s1) {
+                                           uint32_t* pk, float& s0, float& s1, const DropArgs& dr, uint32_t drow, uint32_t n16) {
   float cv[16];
   if (MODE == 1) {
 #pragma unroll
@@ -102,6 +104,10 @@ __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_
       if (!(kbits & (2u << (2 * j)))) e1 = 0.f;
     }
     s0 += e0; s1 += e1;
+    if (DROP) {
+      e0 = drop_hash(n16 + 2 * j, drow, dr.seed_lo, dr.seed_hi) >= dr.thresh ? e0 * dr.inv_keep : 0.f;
+      e1 = drop_hash(n16 + 2 * j + 1, drow, dr.seed_lo, dr.seed_hi) >= dr.thresh ? e1 * dr.inv_keep : 0.f;
+    }
     pk[j] = Op16<T16>::pack(e0, e1);
   }
 }
@@ -111,9 +117,9 @@ __device__ __forceinline__ void lat2_chunk(const uint32_t* r, float sl, float m_
 // never lands on score columns that are still to be loaded (P sits in the lower half of the 64
 // columns on even tiles, in the upper half on odd ones).  Registers are indexed statically; only
 // addresses depend on the direction.  keep: one bit per column of this thread's 64.
-template <int MODE, bool MASKED, typename T16>
+template <int MODE, bool MASKED, bool DROP, typename T16>
 __device__ __forceinline__ float lat2_row(uint32_t s_cols, uint32_t p_cols, int p, float sl, float m_run,
-                                          const float* c64, uint64_t keep) {
+                                          const float* c64, uint64_t keep, const DropArgs& dr, uint32_t drow, uint32_t n64) {
   uint32_t ra[16], rb[16], pk[8];
   float s0 = 0.f, s1 = 0.f;
   const int c0 = p ? 3 : 0, dc = p ? -1 : 1;
@@ -121,23 +127,23 @@ __device__ __forceinline__ float lat2_row(uint32_t s_cols, uint32_t p_cols, int 
   tmem_ld16(s_cols + 16 * c0, ra);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + dc), rb);
-  lat2_chunk<MODE, MASKED, T16>(ra, sl, m_run, c64 + 16 * c0, kb(c0), pk, s0, s1);
+  lat2_chunk<MODE, MASKED, DROP, T16>(ra, sl, m_run, c64 + 16 * c0, kb(c0), pk, s0, s1, dr, drow, n64 + 16 * c0);
   tmem_st8(p_cols + 8 * c0, pk);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + 2 * dc), ra);
-  lat2_chunk<MODE, MASKED, T16>(rb, sl, m_run, c64 + 16 * (c0 + dc), kb(c0 + dc), pk, s0, s1);
+  lat2_chunk<MODE, MASKED, DROP, T16>(rb, sl, m_run, c64 + 16 * (c0 + dc), kb(c0 + dc), pk, s0, s1, dr, drow, n64 + 16 * (c0 + dc));
   tmem_st8(p_cols + 8 * (c0 + dc), pk);
   tmem_wait_ld();
   tmem_ld16(s_cols + 16 * (c0 + 3 * dc), rb);
-  lat2_chunk<MODE, MASKED, T16>(ra, sl, m_run, c64 + 16 * (c0 + 2 * dc), kb(c0 + 2 * dc), pk, s0, s1);
+  lat2_chunk<MODE, MASKED, DROP, T16>(ra, sl, m_run, c64 + 16 * (c0 + 2 * dc), kb(c0 + 2 * dc), pk, s0, s1, dr, drow, n64 + 16 * (c0 + 2 * dc));
   tmem_st8(p_cols + 8 * (c0 + 2 * dc), pk);
   tmem_wait_ld();
-  lat2_chunk<MODE, MASKED, T16>(rb, sl, m_run, c64 + 16 * (c0 + 3 * dc), kb(c0 + 3 * dc), pk, s0, s1);
+  lat2_chunk<MODE, MASKED, DROP, T16>(rb, sl, m_run, c64 + 16 * (c0 + 3 * dc), kb(c0 + 3 * dc), pk, s0, s1, dr, drow, n64 + 16 * (c0 + 3 * dc));
   tmem_st8(p_cols + 8 * (c0 + 3 * dc), pk);
   return s0 + s1;
 }
 
-template <int D, int MODE, typename T16>
+template <int D, int MODE, typename T16, bool DROP>
 __global__ void __launch_bounds__(kLat2Softmax + 32, 2)
 k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, Lat2Args a) {
@@ -347,6 +353,8 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   } else {
     // ================================ softmax threads ================================
     const float sl = a.scale_log2;
+    // dropout row of this thread's latent: gather weights (which = 1) in MODE 0, scatter weights (2) in MODE 1
+    const uint32_t drow = ((uint32_t)((MODE == 0 ? 1 : 2) * a.B * a.H + bh) * (uint32_t)a.M + (uint32_t)lat);
     float m_run = (MODE == 0) ? -INFINITY : 0.f, l_run = 0.f, qn = 0.f;
     if (MODE == 0) {
       // |q_m| of this thread's latent row (both halves compute the same value)
@@ -430,8 +438,10 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 
       // ---- one exponential per score; P packed inside this thread's own columns ----------------
       const float* c64 = sC + st * 128 + 64 * half;
-      if (!masked) l_run += lat2_row<MODE, false, T16>(s_cols, p_cols, p, sl, m_run, c64, keep);
-      else         l_run += lat2_row<MODE, true, T16>(s_cols, p_cols, p, sl, m_run, c64, keep);
+      const uint32_t n64 = (uint32_t)(tile0 + 64 * half);
+      if (DROP)         l_run += lat2_row<MODE, true, true, T16>(s_cols, p_cols, p, sl, m_run, c64, keep, a.drop, drow, n64);
+      else if (!masked) l_run += lat2_row<MODE, false, false, T16>(s_cols, p_cols, p, sl, m_run, c64, keep, a.drop, drow, n64);
+      else              l_run += lat2_row<MODE, true, false, T16>(s_cols, p_cols, p, sl, m_run, c64, keep, a.drop, drow, n64);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_l2(&bar_sm[p]);
@@ -501,11 +511,15 @@ static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v
   a.status = tc_status_ptr();
   a.c_bulk = (MODE == 1 && lse_n && (reinterpret_cast<uintptr_t>(lse_n) & 15) == 0 && (c.N & 3) == 0) ? 1 : 0;
   a.mask = mask;
+  a.drop = make_drop(c.drop_p, c.drop_seed);
   constexpr int smem = Lat2Smem<D>::kBytes;
-  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_lat2<D, MODE, T16>), smem) != FLARE_OK) return FLARE_ECUDA;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_lat2<D, MODE, T16, false>), smem) != FLARE_OK ||
+      tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_lat2<D, MODE, T16, true>), smem) != FLARE_OK)
+    return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * a.n_mblk * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  k_tc_lat2<D, MODE, T16><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
+  if (a.drop.on) k_tc_lat2<D, MODE, T16, true><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
+  else k_tc_lat2<D, MODE, T16, false><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
   return FLARE_OK;
 }
 

@@ -36,6 +36,8 @@ struct Scatter2Args {
   float* lse_n;                // [B,H,N] or null
   long long z_bh_stride;       // floats between the z32 blocks of consecutive (b, h)
   int accumulate;              // 1: merge with the y / lse_n a previous latent block left (log-sum-exp weights)
+  int m0, M_total;             // this launch covers latents [m0, m0 + M) of M_total
+  DropArgs drop;               // attention dropout of the scatter weights A
   int* status;
 };
 
@@ -45,7 +47,7 @@ struct Scatter2Smem {
   static constexpr int kQ = 256 * ROWB;
   static constexpr int kZ = 256 * ROWB;
   static constexpr int kK = 128 * ROWB;
-  static constexpr int kBytes = kQ + kZ + 3 * kK + (2 * 4 * 128 + 2 * 4 * 128 + 2 * 128) * 4 + 1024 + 256;
+  static constexpr int kBytes = kQ + kZ + 3 * kK + (2 * 4 * 128 + 2 * 4 * 128 + 2 * 128 + 16) * 4 + 1024 + 256;
 };
 
 __device__ __forceinline__ void mbar_arrive_s2(uint64_t* bar) {
@@ -57,7 +59,7 @@ __device__ __forceinline__ void named_bar_sync_s2(int id, int nthreads) {
 
 constexpr int kS2Softmax = 512, kS2Epilogue = 128;
 
-template <int D, typename T16>
+template <int D, typename T16, bool DROP>
 __global__ void __launch_bounds__(kS2Softmax + kS2Epilogue + 32, 1)
 k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ, Scatter2Args a) {
   constexpr int ROWB = 2 * D;
@@ -70,7 +72,8 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
   float* sMaxQ = reinterpret_cast<float*>(sK + 3 * L::kK);   // [2][4][128] quarter-row maxima
   float* sSum = sMaxQ + 2 * 4 * 128;               // [2][4][128] quarter-row sums
   float* sRowMax = sSum + 2 * 4 * 128;             // [2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sRowMax + 2 * 128);
+  float* sQmax = sRowMax + 2 * 128;                // [16] per-warp max |q_m|^2
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sQmax + 16);
   uint64_t* bar_full = bars;                       // [3]
   uint64_t* bar_s = bars + 3;                      // [2] S^T(t) complete
   uint64_t* bar_sm = bars + 5;                     // [2] softmax(t) done (512 arrivals)
@@ -198,33 +201,87 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
     const int nv = max(0, min(128, M - 128 * hf)); // valid columns of this half: multiple of 32
     const float sl = a.scale_log2;
     const uint32_t cols = lane_base + 256 * grp + 128 * hf;
+    // max_m |q_m| sl over the latents of this launch (every softmax thread computes it: 2 rows each, then
+    // through shared memory)
+    float qmax_sl;
+    {
+      mbar_wait(bar_q, 0, a.status, abort_flag);
+      float mx2 = 0.f;
+      for (int r = tid; r < M; r += kS2Softmax) {
+        float q2 = 0.f;
+#pragma unroll
+        for (int c = 0; c < ROWB / 16; ++c) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(sQ + swz_off<ROWB>(r, c));
+          const uint32_t* qp = reinterpret_cast<const uint32_t*>(&q4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = Op16<T16>::unpack(qp[j]); q2 = fmaf(f.x, f.x, q2); q2 = fmaf(f.y, f.y, q2); }
+        }
+        mx2 = fmaxf(mx2, q2);
+      }
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) mx2 = fmaxf(mx2, __shfl_xor_sync(0xffffffffu, mx2, o));
+      if (lane == 0) sQmax[warp] = mx2;
+      named_bar_sync_s2(9, kS2Softmax);
+      float m = 0.f;
+      for (int w = 0; w < kS2Softmax / 32; ++w) m = fmaxf(m, sQmax[w]);
+      qmax_sl = sqrtf(m) * sl * 1.0001f;
+    }
     for (int t = grp; t < T; t += 2) {
       const int p = grp;
       mbar_wait(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
-      float mx = -INFINITY;
-      for (int c = 0; c < nv / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(cols + 32 * c, r);
-        tmem_wait_ld();
+      // Row maximum.  Every score of this token obeys |S_mn| sl <= |k_n| max_m |q_m| sl (Cauchy-Schwarz): when
+      // that bound is small the exponentials cannot overflow or vanish without any shift, and the pass over
+      // the scores that finds the maximum is skipped (rmax = 0).  The two threads of a row see the same
+      // bound and the two warps that share 32 rows take the same branch.
+      float rmax = 0.f;
+      float kn2 = 0.f;
+      {
+        const uint8_t* kr = sK + (t % 3) * L::kK;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+        for (int c = 0; c < ROWB / 16; ++c) {
+          const uint4 k4 = *reinterpret_cast<const uint4*>(kr + swz_off<ROWB>(row, c));
+          const uint32_t* kp = reinterpret_cast<const uint32_t*>(&k4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) { const float2 f = Op16<T16>::unpack(kp[j]); kn2 = fmaf(f.x, f.x, kn2); kn2 = fmaf(f.y, f.y, kn2); }
+        }
       }
-      float* mq = sMaxQ + ((t >> 1) & 1) * 512 + p * 256;      // [tile-of-group parity][group][half][row]
-      mq[hf * 128 + row] = mx;
-      named_bar_sync_s2(1 + p * 4 + (warp & 3), 64);           // the two warps that share these rows
-      const float rmax = fmaxf(mx, mq[(hf ^ 1) * 128 + row]);
+      // unshifted weights lie in [2^-bound, 2^bound]: far inside bf16's range; fp16 (largest value 2^16,
+      // full precision down to 2^-14) gets a tighter bound
+      constexpr float kBound = Op16<T16>::kFmt == 0 ? 8.f : 48.f;
+      const bool exact = sqrtf(kn2) * qmax_sl > kBound;
+      if (__any_sync(0xffffffffu, exact)) {
+        float mx = -INFINITY;
+        for (int c = 0; c < nv / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(cols + 32 * c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(r[j]));
+        }
+        float* mq = sMaxQ + ((t >> 1) & 1) * 512 + p * 256;      // [tile-of-group parity][group][half][row]
+        mq[hf * 128 + row] = mx;
+        named_bar_sync_s2(1 + p * 4 + (warp & 3), 64);           // the two warps that share these rows
+        rmax = fmaxf(mx, mq[(hf ^ 1) * 128 + row]);
+      }
       const float off = -rmax * sl;
       float sum = 0.f;
+      const uint32_t ntok = (uint32_t)(n0 + t * 128 + row);
+      const uint32_t drow0 = (uint32_t)(2 * a.B * a.H + bh) * (uint32_t)a.M_total + (uint32_t)(a.m0 + 128 * hf);
       for (int c = 0; c < nv / 32; ++c) {
         uint32_t r[32], pk[16];
         tmem_ld32(cols + 32 * c, r);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const float e0 = ex2(fmaf(__uint_as_float(r[2 * j]), sl, off));
-          const float e1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), sl, off));
+          float e0 = ex2(fmaf(__uint_as_float(r[2 * j]), sl, off));
+          float e1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), sl, off));
           sum += e0 + e1;
+          if (DROP) {                              // the row sum normalises before the dropout mask applies
+            const uint32_t dr = drow0 + 32 * c + 2 * j;
+            e0 = drop_hash(ntok, dr, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? e0 * a.drop.inv_keep : 0.f;
+            e1 = drop_hash(ntok, dr + 1, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? e1 * a.drop.inv_keep : 0.f;
+          }
           pk[j] = Op16<T16>::pack(e0, e1);
         }
         tmem_st16(cols + 16 * c, pk);
@@ -335,8 +392,11 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
   for (int i = 0; i < 3; ++i) a.ys[i] = c.ys[i];
   a.lse_n = lse_n;
   a.status = tc_status_ptr();
+  a.drop = make_drop(c.drop_p, c.drop_seed);
   constexpr int smem = Scatter2Smem<D>::kBytes;
-  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_scatter2<D, T16>), smem) != FLARE_OK) return FLARE_ECUDA;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_scatter2<D, T16, false>), smem) != FLARE_OK ||
+      tc_set_dyn_smem(reinterpret_cast<const void*>(&k_tc_scatter2<D, T16, true>), smem) != FLARE_OK)
+    return FLARE_ECUDA;
   const long long grid = splits * bh;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
   for (int m0 = 0; m0 < c.M; m0 += 256) {
@@ -346,10 +406,11 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
     if (!make_tile_map(&tmQ, qblk, F, D, (uint64_t)mb, (uint64_t)c.H, (uint64_t)(qb ? c.B : 1), c.qs[2] * e,
                        c.qs[1] * e, (qb ? c.qs[0] : c.qs[1] * c.H) * e, (uint32_t)mb))
       return FLARE_EUNSUPPORTED;
-    a.M = mb;
+    a.M = mb; a.m0 = m0; a.M_total = c.M;
     a.z32 = z32 + (long long)m0 * D;
     a.accumulate = m0 > 0 ? 1 : 0;
-    k_tc_scatter2<D, T16><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+    if (a.drop.on) k_tc_scatter2<D, T16, true><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+    else k_tc_scatter2<D, T16, false><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
   }
   return FLARE_OK;
 }

@@ -74,7 +74,8 @@ def _q3(q: torch.Tensor) -> Tuple[torch.Tensor, bool]:
     return _tok(q), q.dim() == 4
 
 
-def make_problem(q, k, scale: float, n_splits: int = 0, v=None, y=None, dy=None, dk=None, dv=None) -> FlareProblem:
+def make_problem(q, k, scale: float, n_splits: int = 0, v=None, y=None, dy=None, dk=None, dv=None,
+                 dropout_p: float = 0.0, dropout_seed: int = 0) -> FlareProblem:
     B, H, N, D = k.shape
     if q.dim() == 3:
         Hq, M, Dq = q.shape
@@ -93,6 +94,8 @@ def make_problem(q, k, scale: float, n_splits: int = 0, v=None, y=None, dy=None,
     p.dtype = _cabi.DTYPE_CODE[k.dtype]
     p.scale = float(scale)
     p.n_splits = int(n_splits)
+    p.dropout_p = float(dropout_p)
+    p.dropout_seed = int(dropout_seed) & 0xFFFFFFFFFFFFFFFF
     p.q_stride[:] = qs
     p.k_stride[:] = k.stride()[:3]
     for name, t in (("v_stride", v), ("y_stride", y), ("dy_stride", dy), ("dk_stride", dk), ("dv_stride", dv)):
@@ -109,7 +112,7 @@ def _mask_u8(key_mask, B, N, device):
     return key_mask.to(device=device, dtype=torch.uint8).contiguous()
 
 
-def mixer_forward(q, k, v, scale=1.0, key_mask=None):
+def mixer_forward(q, k, v, scale=1.0, key_mask=None, dropout_p=0.0, dropout_seed=0):
     """y, z32[B,H,M,D], lse_m[B,H,M], lse_n[B,H,N] via flare_mixer_fwd."""
     _need_cuda(q, k, v)
     if not (q.dtype == k.dtype == v.dtype):
@@ -126,7 +129,7 @@ def mixer_forward(q, k, v, scale=1.0, key_mask=None):
         z32 = torch.empty(B, H, M, D, dtype=torch.float32, device=k.device)
         lse_m = torch.empty(B, H, M, dtype=torch.float32, device=k.device)
         lse_n = torch.empty(B, H, N, dtype=torch.float32, device=k.device)
-        p = make_problem(q, k, scale, v=v, y=y)
+        p = make_problem(q, k, scale, v=v, y=y, dropout_p=dropout_p, dropout_seed=dropout_seed)
         nbytes = lib.flare_fwd_workspace_bytes(C.byref(p))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
         check(lib.flare_mixer_fwd(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(mask), ptr(y), ptr(z32),
@@ -134,7 +137,7 @@ def mixer_forward(q, k, v, scale=1.0, key_mask=None):
     return y, z32, lse_m, lse_n
 
 
-def mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale=1.0, key_mask=None):
+def mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale=1.0, key_mask=None, dropout_p=0.0, dropout_seed=0):
     """dq (fp32, [H,M,D] or [B,H,M,D]), dk, dv via flare_mixer_bwd."""
     _need_cuda(q, k, v, dy, y)
     q, batched = _q3(q)
@@ -150,7 +153,7 @@ def mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale=1.0, key_mask=None):
         if dv.stride(-1) != 1:
             dv = torch.empty(v.shape, dtype=v.dtype, device=v.device)
         dq = torch.empty((B, H, M, D) if batched else (H, M, D), dtype=torch.float32, device=k.device)
-        p = make_problem(q, k, scale, v=v, y=y, dy=dy, dk=dk, dv=dv)
+        p = make_problem(q, k, scale, v=v, y=y, dy=dy, dk=dk, dv=dv, dropout_p=dropout_p, dropout_seed=dropout_seed)
         nbytes = lib.flare_bwd_workspace_bytes(C.byref(p))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=k.device)
         check(lib.flare_mixer_bwd(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(dy), ptr(y), ptr(mask), ptr(z32),
@@ -281,12 +284,13 @@ def _dq_like(q: Tensor) -> Tensor:
 
 
 @torch.library.custom_op("flare_b200::mixer_fwd", mutates_args=())
-def _op_mixer_fwd(q: Tensor, k: Tensor, v: Tensor, scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
-    return mixer_forward(q, k, v, scale, key_mask)
+def _op_mixer_fwd(q: Tensor, k: Tensor, v: Tensor, scale: float, key_mask: Optional[Tensor], dropout_p: float,
+                  dropout_seed: int) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
+    return mixer_forward(q, k, v, scale, key_mask, dropout_p, dropout_seed)
 
 
 @_op_mixer_fwd.register_fake
-def _(q, k, v, scale, key_mask):
+def _(q, k, v, scale, key_mask, dropout_p, dropout_seed):
     B, H, N, D = k.shape
     M = q.shape[-2]
     f32 = dict(dtype=torch.float32, device=k.device)
@@ -295,26 +299,26 @@ def _(q, k, v, scale, key_mask):
 
 @torch.library.custom_op("flare_b200::mixer_bwd", mutates_args=())
 def _op_mixer_bwd(q: Tensor, k: Tensor, v: Tensor, dy: Tensor, y: Tensor, z32: Tensor, lse_m: Tensor, lse_n: Tensor,
-                  scale: float, key_mask: Optional[Tensor]) -> Tuple[Tensor, Tensor, Tensor]:
-    return mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask)
+                  scale: float, key_mask: Optional[Tensor], dropout_p: float, dropout_seed: int) -> Tuple[Tensor, Tensor, Tensor]:
+    return mixer_backward(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask, dropout_p, dropout_seed)
 
 
 @_op_mixer_bwd.register_fake
-def _(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask):
+def _(q, k, v, dy, y, z32, lse_m, lse_n, scale, key_mask, dropout_p, dropout_seed):
     return _dq_like(q), _like_tokens(k), _like_tokens(v)
 
 
 def _mixer_setup(ctx, inputs, output):
-    q, k, v, scale, key_mask = inputs
+    q, k, v, scale, key_mask, dropout_p, dropout_seed = inputs
     y, z32, lse_m, lse_n = output
     ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n, key_mask)
-    ctx.scale = scale
+    ctx.scale, ctx.dropout = scale, (dropout_p, dropout_seed)
 
 
 def _mixer_backward(ctx, dy, _dz32, _dlm, _dln):
     q, k, v, y, z32, lse_m, lse_n, key_mask = ctx.saved_tensors
-    dq, dk, dv = _op_mixer_bwd(q, k, v, dy, y, z32, lse_m, lse_n, ctx.scale, key_mask)
-    return dq.to(q.dtype), dk, dv, None, None
+    dq, dk, dv = _op_mixer_bwd(q, k, v, dy, y, z32, lse_m, lse_n, ctx.scale, key_mask, *ctx.dropout)
+    return dq.to(q.dtype), dk, dv, None, None, None, None
 
 
 _op_mixer_fwd.register_autograd(_mixer_backward, setup_context=_mixer_setup)
@@ -422,23 +426,46 @@ def _same_dtype(q, k, v):
         raise TypeError(f"q, k, v must share a dtype outside torch.autocast; got {q.dtype}, {k.dtype}, {v.dtype}")
 
 
+_dropout_calls = 0
+
+
+def next_dropout_seed() -> int:
+    """A new 64-bit seed per call, reproducible from torch.manual_seed and the order of the calls."""
+    global _dropout_calls
+    _dropout_calls += 1
+    x = (torch.initial_seed() * 0x9E3779B97F4A7C15 + _dropout_calls * 0xD1B54A32D192ED03) & 0xFFFFFFFFFFFFFFFF
+    x ^= x >> 31
+    x = (x * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    x ^= x >> 29
+    return x & 0x7FFFFFFFFFFFFFFF
+
+
 def flare_multihead_mixer(q, k, v, scale: float = 1.0, key_mask: Optional[torch.Tensor] = None,
-                          dropout_p: float = 0.0):
+                          dropout_p: float = 0.0, dropout_seed: Optional[int] = None):
     """y[B,H,N,D] = SDPA(k, q, SDPA(q, k, v, scale), scale)   (README.md:37-53 of the reference).
 
     q: [H,M,D] (or [B,H,M,D]); k, v: [B,H,N,D], any strides with unit stride on D.
     key_mask: optional bool [B,N], True = token takes part (lra/models/backends.py:615-622);
     masked tokens are ignored by the gather and their output rows are zero.
-    dropout_p: attention dropout of both SDPA calls (lra/models/backends.py:604-606) is not built: must be 0.
+    dropout_p: attention dropout of both SDPA calls (lra/models/backends.py:604-606): each softmax weight is
+    dropped with this probability after normalisation and the rest scaled by 1/(1-p), independently in the
+    gather and in the scatter; the masks come from a counter hash of torch's seed (``torch.manual_seed``) and
+    the number of dropout calls made so far, not from torch's Philox stream (equal in distribution, not bit
+    for bit).  ``dropout_seed`` fixes the masks explicitly.  16-bit dtypes with D in {16, 32} only.
     Works under torch.autocast (inputs are cast to the autocast dtype, as SDPA does) and inside
     torch.compile (registered operators ``flare_b200::mixer_fwd`` / ``mixer_bwd``).
     """
     _need_cuda(q, k, v)
     q, k, v = _autocast(_fold_q(q), k, v)
     _same_dtype(q, k, v)
-    if dropout_p != 0.0:
-        raise NotImplementedError("attention dropout is not supported by the fused mixer (dropout_p must be 0)")
-    return _op_mixer_fwd(q, k, v, float(scale), key_mask)[0]
+    if not 0.0 <= dropout_p < 1.0:
+        raise ValueError(f"dropout_p must be in [0, 1), got {dropout_p}")
+    seed = 0
+    if dropout_p > 0.0:
+        if k.dtype == torch.float32:
+            raise NotImplementedError("attention dropout runs on the tensor-core kernels: bf16 or fp16 inputs (or autocast)")
+        seed = next_dropout_seed() if dropout_seed is None else int(dropout_seed)
+    return _op_mixer_fwd(q, k, v, float(scale), key_mask, float(dropout_p), seed)[0]
 
 
 def flare_gather(q, k, v, scale: float = 1.0, key_mask=None):

@@ -82,6 +82,14 @@ typedef struct FlareProblem {
   int64_t dy_stride[3];
   int64_t dk_stride[3];
   int64_t dv_stride[3];
+  /* Attention dropout of both SDPA calls (dropout_p of lra/models/backends.py:604-606): every softmax
+   * weight is zeroed with probability dropout_p and the survivors are scaled by 1/(1-dropout_p), after
+   * the normalisation, independently in the gather (weights P) and in the scatter (weights A).  The
+   * keep decision of element (call, b, h, m, n) is a hash of those indices and dropout_seed, so the
+   * backward passes regenerate the masks of the forward from the same two numbers.  0 = off.  Served by
+   * the tensor-core kernels only (16-bit dtype, D in {16,32}); refused with FLARE_EUNSUPPORTED elsewhere. */
+  float    dropout_p;
+  uint64_t dropout_seed;
 } FlareProblem;
 
 int         flare_version(void);

@@ -34,7 +34,7 @@ import torch
 import torch.nn.functional as F
 
 __all__ = [
-    "mixer_sdpa", "mixer_explicit", "mixer_lra", "gather", "scatter",
+    "mixer_sdpa", "mixer_explicit", "mixer_lra", "dropout_keep_masks", "mixer_dropout", "gather", "scatter",
     "mixer_fwd_stats", "mixer_bwd_closed_form", "mixer_fwd_bwd_streamed", "gather_partials",
     "lse_combine", "causal_dense", "causal_recurrent", "causal_chunked", "causal_bwd_autograd", "causal_bwd_chunked",
     "triple_attention", "triple_attention_bwd", "causal_linear", "rel_l2",
@@ -101,6 +101,44 @@ def mixer_lra(q, k, v, scale: float = 1.0, key_mask: Optional[torch.Tensor] = No
     """
     z, _ = gather(q, k, v, scale, key_mask)
     y, _ = scatter(q, k, z, scale)
+    if key_mask is not None:
+        y = y * key_mask[:, None, :, None].to(y.dtype)
+    return y
+
+
+def dropout_keep_masks(B, H, M, N, p: float, seed: int):
+    """The keep masks the CUDA kernels draw for attention dropout, recomputed on the host: element
+    (which, b, h, m, n) is kept iff hash(n, (which*B*H + b*H + h)*M + m, seed) >= p * 2^32 (32-bit
+    wrap-around arithmetic; which = 1 for the gather weights, 2 for the scatter weights).
+    Returns two bool tensors [B,H,M,N]."""
+    import numpy as np
+    u = np.uint32
+    seed_lo, seed_hi = u(seed & 0xFFFFFFFF), u((seed >> 32) & 0xFFFFFFFF)
+    thresh = min(int(p * 4294967296.0), 4294967295)
+    n = np.arange(N, dtype=np.uint32)[None, :]
+    out = []
+    with np.errstate(over="ignore"):
+        for which in (1, 2):
+            rows = (np.arange(B * H, dtype=np.uint32)[:, None] + u(which * B * H)) * u(M) + np.arange(M, dtype=np.uint32)[None, :]
+            row = rows.reshape(-1, 1)
+            x = (n * u(0x9E3779B1)) ^ seed_lo
+            y = (row * u(0x85EBCA77)) ^ seed_hi
+            x = x ^ (y + u(0x165667B1) + (x << u(6)) + (x >> u(2)))
+            x ^= x >> u(16); x *= u(0x85EBCA6B); x ^= x >> u(13); x *= u(0xC2B2AE35); x ^= x >> u(16)
+            out.append(torch.from_numpy((x >= u(thresh)).reshape(B, H, M, N)))
+    return out[0], out[1]
+
+
+def mixer_dropout(q, k, v, scale: float, keep1, keep2, p: float, key_mask: Optional[torch.Tensor] = None):
+    """The two SDPA calls with dropout_p = p (lra/models/backends.py:604-606) for GIVEN keep masks: dropout
+    acts on the normalised softmax weights, survivors scaled by 1/(1-p)."""
+    qe = _expand_q(q, k.shape[0])
+    s = scale * (qe @ k.transpose(-2, -1))
+    sg = s if key_mask is None else s.masked_fill(~key_mask[:, None, None, :], float("-inf"))
+    P = torch.softmax(sg, dim=-1) * keep1 / (1.0 - p)
+    z = P @ v
+    A = torch.softmax(s, dim=-2) * keep2 / (1.0 - p)
+    y = A.transpose(-2, -1) @ z
     if key_mask is not None:
         y = y * key_mask[:, None, :, None].to(y.dtype)
     return y

@@ -21,9 +21,9 @@ def test_mixer_operator_shapes_on_fake_tensors(dtype):
         y = fb.flare_multihead_mixer(q.unsqueeze(0).expand(B, -1, -1, -1), k, v, scale=0.5)
         assert y.shape == (B, H, N, D) and y.dtype == dtype and y.requires_grad
         assert y.stride() == k.stride()                      # 'b h n d -> b n (h d)' stays a free view
-        y0, z32, lse_m, lse_n = ops.mixer_fwd(q, k, v, 0.5, None)
+        y0, z32, lse_m, lse_n = ops.mixer_fwd(q, k, v, 0.5, None, 0.0, 0)
         assert z32.shape == (B, H, M, D) and lse_m.shape == (B, H, M) and lse_n.shape == (B, H, N)
-        dq, dk, dv = ops.mixer_bwd(q, k, v, torch.empty_like(y0), y0, z32, lse_m, lse_n, 0.5, None)
+        dq, dk, dv = ops.mixer_bwd(q, k, v, torch.empty_like(y0), y0, z32, lse_m, lse_n, 0.5, None, 0.0, 0)
         assert dq.shape == q.shape and dq.dtype == torch.float32
         assert dk.shape == k.shape and dk.stride() == k.stride() and dv.dtype == dtype
 
@@ -61,5 +61,9 @@ def test_autocast_casts_the_latents_like_sdpa(monkeypatch):
         assert y.dtype == torch.float16 and y.requires_grad
         with pytest.raises(TypeError):
             fb.flare_multihead_mixer(q, k, v)                                    # no autocast: dtypes must agree
+        y = fb.flare_multihead_mixer(q.half(), k, v, dropout_p=0.1)               # dropout: a seed is drawn on the host
+        assert y.shape == k.shape
         with pytest.raises(NotImplementedError):
-            fb.flare_multihead_mixer(q.half(), k, v, dropout_p=0.1)
+            fb.flare_multihead_mixer(q, k.float(), v.float(), dropout_p=0.1)      # fp32 has no dropout kernels
+        with pytest.raises(ValueError):
+            fb.flare_multihead_mixer(q.half(), k, v, dropout_p=1.0)

@@ -107,3 +107,16 @@ def test_triple_backward_matches_the_reference_einsum_backward():
     got = O.triple_attention_bwd(g["q1"], g["q2"], g["k1"], g["k2"], g["v"], g["do"])
     for name, a in zip(("dq1", "dq2", "dk1", "dk2", "dv"), got):
         assert O.rel_l2(a, g[name]) < 1e-5, name
+
+
+def test_dropout_masks_have_the_right_rate_and_are_independent():
+    keep1, keep2 = O.dropout_keep_masks(2, 3, 16, 4096, 0.3, seed=12345)
+    assert keep1.shape == (2, 3, 16, 4096)
+    for kmask in (keep1, keep2):
+        assert abs(kmask.float().mean().item() - 0.7) < 5e-3
+        rows = kmask.float().mean(-1)
+        assert (rows - 0.7).abs().max() < 0.04                      # every (b, h, m) row on its own
+    agree = (keep1 == keep2).float().mean().item()
+    assert abs(agree - (0.7 * 0.7 + 0.3 * 0.3)) < 5e-3              # the two softmaxes draw independent masks
+    k1b, _ = O.dropout_keep_masks(2, 3, 16, 4096, 0.3, seed=12346)
+    assert abs((keep1 == k1b).float().mean().item() - 0.58) < 5e-3  # another seed, another mask
