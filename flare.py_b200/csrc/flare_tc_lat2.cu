@@ -163,8 +163,8 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   uint32_t* sKeep = reinterpret_cast<uint32_t*>(sKmax + 16);   // [NS][4] keep bits of the tile's 128 tokens
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKeep + 16);
   uint64_t* bar_full = bars;                       // [NS]
-  uint64_t* bar_s = bars + NS;                     // [2] S(t) complete
-  uint64_t* bar_pv = bar_s + 2;                    // [2] P(t) V(t) complete
+  uint64_t* bar_s = bars + NS;                     // [2][2] S(t), score columns of half hf, complete: bar_s[2 (t&1) + hf]
+  uint64_t* bar_pv = bar_s + 4;                    // [2] P(t) V(t) complete
   uint64_t* bar_sm = bar_pv + 2;                   // [2] softmax(t) done (256 arrivals)
   uint64_t* bar_k = bar_sm + 2;                    // [2] tile norm bound of tile t written (MODE 0)
   uint64_t* bar_q = bar_k + 2;
@@ -197,7 +197,7 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) mbar_init(&bar_full[i], 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_s[i], 1); mbar_init(&bar_pv[i], 1); mbar_init(&bar_sm[i], kLat2Softmax); mbar_init(&bar_k[i], 1);
+      mbar_init(&bar_s[2 * i], 1); mbar_init(&bar_s[2 * i + 1], 1); mbar_init(&bar_pv[i], 1); mbar_init(&bar_sm[i], kLat2Softmax); mbar_init(&bar_k[i], 1);
     }
     mbar_init(bar_q, 1);
     *abort_flag = 0;
@@ -298,6 +298,7 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
         mma_commit(&bar_s[0]);
+        mma_commit(&bar_s[1]);
       }
       __syncwarp();
     }
@@ -308,29 +309,39 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
       tile_cscale(0);
       if (T > 1) { mbar_wait(&bar_full[1], 0, a.status, abort_flag); tile_cscale(1); }
     }
+    // One half of the score product of tile t1 (64 token columns): S region of the tile + 64 hf.
+    const uint32_t idesc_h = idesc_f16(128, 64, F, F, 0, 0);
+    auto issue_s_half = [&](int t1, int hf) {
+      const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + (t1 % NS) * L::kT + hf * 64 * ROWB));
+      const uint32_t sb = tmem + ((t1 & 1) ? 96 : 0) + 64 * hf;
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_h, kk > 0);
+        mma_commit(&bar_s[2 * (t1 & 1) + hf]);
+      }
+      __syncwarp();
+    };
     for (int t = 0; t < T; ++t) {
       const int p = t & 1;
+      // The score regions of consecutive tiles overlap in 32 columns only ([96,128)), which belong to one half of
+      // either tile.  The half of S(t+1) that does not touch them (columns [160,224) after an even tile, [0,64)
+      // after an odd one) is issued as soon as P(t-1) V(t-1) has completed -- while the softmax threads are
+      // still on tile t -- and the other half once they are done: half of the threads find their scores
+      // waiting, the others cover the product's latency with the first half's exponentials still running.
+      if (t >= 1) mbar_wait_hot(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
+      const int early = p ? 0 : 1;                 // half of tile t+1 that is free of S(t)
+      if (t + 1 < T) {
+        mbar_wait_hot(&bar_full[(t + 1) % NS], (uint32_t)((t + 1) / NS) & 1, a.status, abort_flag);
+        tc_fence_after();
+        issue_s_half(t + 1, early);
+      }
       mbar_wait_hot(&bar_sm[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);     // P(t) written, S(t) consumed
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
-      if (t >= 1) {
-        // P(t-1) V(t-1) complete: its packed P columns may be overwritten by S(t+1), and the
-        // stage of tile t-1 may take tile t+3
-        mbar_wait_hot(&bar_pv[p ^ 1], (uint32_t)((t - 1) >> 1) & 1, a.status, abort_flag);
-      }
+      // the stage of tile t-1 may take tile t+3 (its V was read by P(t-1) V(t-1))
       if (t + NS - 1 < T && elect_one()) load_tile(t + NS - 1);
       __syncwarp();
       tc_fence_after();
-      if (t + 1 < T) {
-        mbar_wait_hot(&bar_full[(t + 1) % NS], (uint32_t)((t + 1) / NS) & 1, a.status, abort_flag);
-        const uint64_t dk = smem_desc<ROWB>(smem_u32(sK + ((t + 1) % NS) * L::kT));
-        const uint32_t sb = tmem + (p ? 0 : 96);                                    // region of tile t+1
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) mma_ss(sb, dq + 2 * kk, dk + 2 * kk, idesc_s, kk > 0);
-          mma_commit(&bar_s[p ^ 1]);
-        }
-        __syncwarp();
-      }
+      if (t + 1 < T) issue_s_half(t + 1, early ^ 1);
       {
         const uint64_t dv = smem_desc<ROWB>(smem_u32(sV + (t % NS) * L::kT));
         const uint32_t p0 = tmem + (p ? 128 : 0), p1 = tmem + (p ? 192 : 64);       // packed P of the two halves
@@ -394,7 +405,7 @@ k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUten
         bound = qn * sqrtf(sKmax[st]);             // >= every score of this row in the tile, log2 units
       }
 
-      mbar_wait_hot(&bar_s[p], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
+      mbar_wait_hot(&bar_s[2 * p + half], (uint32_t)(t >> 1) & 1, a.status, abort_flag);
       tc_fence_after();
       const uint64_t keep = (uint64_t)sKeep[st * 4 + 2 * half] | ((uint64_t)sKeep[st * 4 + 2 * half + 1] << 32);
       const bool masked = keep != ~0ull;
