@@ -265,7 +265,7 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         rmax = fmaxf(mx, mq[(hf ^ 1) * 128 + row]);
       }
       const float off = -rmax * sl;
-      float sum = 0.f;
+      float2 sum2 = make_float2(0.f, 0.f);
       const uint32_t ntok = (uint32_t)(n0 + t * 128 + row);
       const uint32_t drow0 = (uint32_t)(2 * a.B * a.H + bh) * (uint32_t)a.M_total + (uint32_t)(a.m0 + 128 * hf);
       for (int c = 0; c < nv / 32; ++c) {
@@ -274,9 +274,11 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          float e0 = ex2(fmaf(__uint_as_float(r[2 * j]), sl, off));
-          float e1 = ex2(fmaf(__uint_as_float(r[2 * j + 1]), sl, off));
-          sum += e0 + e1;
+          // two scores per instruction (packed fp32 multiply-add and add)
+          const float2 x2 = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), make_float2(sl, sl),
+                                       make_float2(off, off));
+          float e0 = ex2(x2.x), e1 = ex2(x2.y);
+          sum2 = __fadd2_rn(sum2, make_float2(e0, e1));
           if (DROP) {                              // the row sum normalises before the dropout mask applies
             const uint32_t dr = drow0 + 32 * c + 2 * j;
             e0 = drop_hash(ntok, dr, a.drop.seed_lo, a.drop.seed_hi) >= a.drop.thresh ? e0 * a.drop.inv_keep : 0.f;
@@ -286,7 +288,7 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         }
         tmem_st16(cols + 16 * c, pk);
       }
-      sSum[(p * 2 + hf) * 128 + row] = sum;
+      sSum[(p * 2 + hf) * 128 + row] = sum2.x + sum2.y;
       if (hf == 0) sRowMax[p * 128 + row] = rmax;
       tmem_wait_st();
       tc_fence_before();
