@@ -277,7 +277,7 @@ def run_ours(args):
         if cp_kind == "peer":
             try:
                 cp_ex = PeerExchange()
-                cp_ex.exchange_buffer("probe", (16,), dev)      # forces the symmetric-memory rendezvous now
+                cp_ex.prepare_mixer(B, H, M, D, dev)            # the symmetric-memory rendezvous happens here
             except Exception as e:                              # no symmetric memory on this box: NCCL collectives
                 print(f"[bench] peer-memory exchange unavailable ({e!r}); using NCCL", file=sys.stderr, flush=True)
                 cp_kind, cp_ex = "nccl", None
@@ -302,12 +302,48 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # N > 1: the step recorded in a CUDA graph.  A rank's share of the step shrinks with N while the host's
+    # cost to enqueue it does not; the recorded sequence (two steps, see GraphedStep) is replayed instead.
+    # It has an exchange object of its own, so eager steps may run between replays.
+    graphed = None
+    if world > 1 and cp_kind == "peer" and not args.no_graph:
+        from flare_b200.parallel import GraphedStep
+        try:
+            g_ex = PeerExchange()
+            g_ex.prepare_mixer(B, H, M, D, dev)
+
+            def graph_step():
+                q.grad = k.grad = v.grad = None
+                y = flare_mixer_context_parallel(q, k, v, 1.0, exchange=g_ex)
+                y.backward(dy)
+                return y
+
+            graphed = GraphedStep(graph_step)
+        except Exception as e:
+            print(f"[bench] CUDA-graph capture of the step failed ({e!r}); eager launches", file=sys.stderr, flush=True)
+            graphed = None
+        ok = torch.tensor([1 if graphed is not None else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)               # all ranks must agree
+        if ok.item() == 0:
+            graphed = None
+
+    def run_steps(n):
+        if graphed is not None:
+            for _ in range(n // 2):
+                graphed.replay()
+            n = n % 2
+        for _ in range(n):
+            step()
+
     def timed(fn, steps):
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            fn()
+        if fn is step:
+            run_steps(steps)
+        else:
+            for _ in range(steps):
+                fn()
         e1.record()
         sync_all()
         ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
@@ -329,8 +365,7 @@ def run_ours(args):
     # takes to enqueue a step without waiting for the device is what the host side costs
     sync_all()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
+    run_steps(args.steps)
     host_ms = (time.perf_counter() - t0) / args.steps * 1e3
     sync_all()
 
@@ -468,16 +503,17 @@ def run_ours(args):
 
     if rank == 0:
         # forward: gather, combine, scatter; backward: dZ partial, reduce, range check (2 kernels),
-        # one-exponential main kernel, flag-gated exact kernel, dQ reduce; the context-parallel
-        # forward has a second combine over the ranks' records
-        launches_per_step = 10 + (1 if world > 1 else 0)
+        # one-exponential main kernel, flag-gated exact kernel, dQ reduce.  Context parallel over peer memory:
+        # each of the three exchanges adds the barrier kernel and the kernel that reads all ranks' buffers
+        launches_per_step = 10 if world == 1 else (16 if cp_kind == "peer" else 11)
         line = dict(
             metric=METRIC, value=value, unit="Mtokens/s", n_gpus=world, steps=args.steps, warmup=max(args.warmup, 3),
             ms_per_step=ms_step, higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16",
             data="synthetic",
             config=dict(workload=f"mixer_1M: B={B} H={H} N={N} M={M} D={D} bf16 fwd+bwd",
                         parallelism=("single GPU" if world == 1 else
-                                     f"context parallel, N sharded over {world} ranks, exchange={cp_kind}"),
+                                     f"context parallel, N sharded over {world} ranks, exchange={cp_kind}"
+                                     + (", step replayed from a CUDA graph" if graphed is not None else "")),
                         tokens_per_rank=Nl, l2="inputs larger than L2 (K,V,dY,Y,dK,dV 64 B x tokens x heads each); no flush",
                         kernel_path="tcgen05 (decoupled gather/scatter/dZ, pipelined one-exponential backward behind an on-device range check); fp32 reductions"),
             clocks=clocks,
@@ -653,6 +689,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override N (profiling on a smaller case)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained leg")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "sdpa_gpu", "cp_encoder"],
                     help="mixer: the headline line; causal: a secondary line for causal prefill/decode; sdpa_gpu: "
                          "a secondary line timing the reference's own two SDPA calls + autograd on this GPU")

@@ -425,6 +425,10 @@ struct PartsPtrs {
   __device__ __forceinline__ const float* at(int p) const { return ptrs[p]; }
 };
 
+// One warp per latent row.  The statistics (m_p, l_p) are read with one load per lane (parts spread over
+// the lanes, reduced by shuffles), the accumulators with lane = d and several parts' loads in flight: the
+// kernel's time is the latency of its dependent loads, not their volume.  The order of every sum is fixed
+// (shuffle tree over the lanes, then ascending parts), so equal inputs give equal bits on every rank.
 template <typename Parts>
 __global__ void __launch_bounds__(kThreads)
 k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
@@ -435,20 +439,41 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
   if (row >= rows) return;
   const int W = D + 2;
   float mx = -INFINITY;
-  for (int p = 0; p < n_parts; ++p) mx = fmaxf(mx, parts.at(p)[row * W + D]);
+  for (int p0 = 0; p0 < n_parts; p0 += 32) {
+    const int p = p0 + lane;
+    if (p < n_parts) mx = fmaxf(mx, parts.at(p)[row * W + D]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float lt = 0.f;
-  for (int p = 0; p < n_parts; ++p) {
-    const float m = parts.at(p)[row * W + D];
-    const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
-    lt = fmaf(w, parts.at(p)[row * W + D + 1], lt);
+  for (int p0 = 0; p0 < n_parts; p0 += 32) {
+    const int p = p0 + lane;
+    float t = 0.f;
+    if (p < n_parts) {
+      const float m = parts.at(p)[row * W + D];
+      const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
+      t = w * parts.at(p)[row * W + D + 1];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    lt += t;
   }
   const float inv = 1.f / lt;
   for (int d = lane; d < D; d += 32) {
     float a = 0.f;
-    for (int p = 0; p < n_parts; ++p) {
-      const float m = parts.at(p)[row * W + D];
-      const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
-      a = fmaf(w, parts.at(p)[row * W + d], a);
+    for (int p0 = 0; p0 < n_parts; p0 += 8) {
+      float mv[8], av[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const bool in = p0 + j < n_parts;
+        mv[j] = in ? parts.at(p0 + j)[row * W + D] : -INFINITY;
+        av[j] = in ? parts.at(p0 + j)[row * W + d] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float w = (mv[j] == -INFINITY) ? 0.f : expf(mv[j] - mx);
+        a = fmaf(w, av[j], a);
+      }
     }
     if (rec_out) rec_out[row * W + d] = a;
     const float z = a * inv;
@@ -465,13 +490,20 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
   }
 }
 
+// out[i] = sum over parts, ascending; eight loads in flight per thread
 template <typename Parts>
 __global__ void __launch_bounds__(256)
 k_reduce_sum(Parts parts, int n_parts, long long n, float* __restrict__ out) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float a = 0.f;
-  for (int p = 0; p < n_parts; ++p) a += parts.at(p)[i];
+  for (int p0 = 0; p0 < n_parts; p0 += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = p0 + j < n_parts ? parts.at(p0 + j)[i] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a += v[j];
+  }
   out[i] = a;
 }
 

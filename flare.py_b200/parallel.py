@@ -32,7 +32,7 @@ from . import _cabi
 from ._cabi import check, lib, ptr, stream_of
 from .mixer import _need_cuda, _q3, _tok, make_problem
 
-__all__ = ["RecordExchange", "PeerExchange", "flare_mixer_context_parallel", "shard_bounds"]
+__all__ = ["RecordExchange", "PeerExchange", "GraphedStep", "flare_mixer_context_parallel", "shard_bounds"]
 
 
 def shard_bounds(n_tokens: int, world: int, rank: int, multiple: int = 1):
@@ -72,8 +72,8 @@ class PeerExchange(RecordExchange):
     alternately and an int32[world] array of arrival flags.  The ordering barrier is the library's own
     (``flare_peer_barrier``: release/acquire flags in peer memory, a bounded wait that records a status
     bit instead of hanging when a peer has left); torch supplies the allocation and the rendezvous only.
-    Each exchange carries a number (``epoch``) that must advance in step on all ranks: every rank has to
-    make the same sequence of calls.
+    The barrier numbers the exchanges itself on the device, so a step can be recorded in a CUDA graph and
+    replayed (``GraphedStep``); every rank has to make the same sequence of calls.
     """
 
     def __init__(self, group: Optional[dist.ProcessGroup] = None):
@@ -81,6 +81,17 @@ class PeerExchange(RecordExchange):
         import torch.distributed._symmetric_memory as symm_mem
         self._symm = symm_mem
         self._slots = {}
+
+    def prepare(self, name: str, numel: int, device) -> None:
+        """Allocate and rendezvous the buffers of one exchange kind now (a collective call: every rank makes
+        it; not possible while a CUDA graph is being recorded)."""
+        self._slot(name, numel, device)
+
+    def prepare_mixer(self, B: int, H: int, M: int, D: int, device, batched_q: bool = False) -> None:
+        """The three exchanges of one context-parallel mixer step."""
+        self.prepare("rec", _numel(B, H, M, D + 2), device)
+        self.prepare("dz", _numel(B, H, M, D), device)
+        self.prepare("dq", _numel(B, H, M, D) if batched_q else _numel(H, M, D), device)
 
     def _slot(self, name: str, numel: int, device):
         key = (name, numel)
@@ -112,7 +123,7 @@ class PeerExchange(RecordExchange):
         g.bufs = s["bufs"][half].data_ptr()
         g.mine = s["buf"].data_ptr() + half * s["pad"] * 4
         g.flags = s["flags"].data_ptr()
-        g.epoch = s["turn"]
+        g.epoch = 0                                                   # numbered on the device
         return g
 
 
@@ -223,3 +234,36 @@ def flare_mixer_context_parallel(q, k_local, v_local, scale: float = 1.0,
     q, k_local, v_local = _autocast(q, k_local, v_local)
     _same_dtype(q, k_local, v_local)
     return _CPMixerFn.apply(q, k_local, v_local, float(scale), ex, reduce_dq)
+
+
+class GraphedStep:
+    """Two consecutive calls of ``step_fn`` recorded in one CUDA graph.
+
+    At eight ranks a million-token mixer step is a fraction of a millisecond of device work per rank,
+    less than the host needs to enqueue its dozen launches through Python; replaying a recorded launch
+    sequence removes that.  Two steps are recorded because a ``PeerExchange`` alternates between the two
+    halves of its buffers from one exchange of a kind to the next: the pair restores the parity, so
+    replays can follow each other.  ``step_fn`` must use tensors that stay alive and a ``PeerExchange`` of
+    its own (prepared beforehand with ``prepare_mixer``) that nothing outside the graph uses.  No autograd
+    graph of an earlier eager step over the same leaf tensors may be alive when recording starts (drop or
+    detach its outputs): its gradient accumulators are tied to the stream they were created on.
+    """
+
+    def __init__(self, step_fn, warmup: int = 2):
+        dev = torch.cuda.current_device()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2 * ((warmup + 1) // 2)):                 # an even number: the halves stay in step
+                step_fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            step_fn()
+            self.result = step_fn()
+        self.steps_per_replay = 2
+
+    def replay(self):
+        self.graph.replay()
+        return self.result

@@ -157,8 +157,11 @@ typedef struct FlarePeers {
   int32_t rank, world;
   const float* const* bufs;    /* DEVICE array [world] of device pointers: each rank's exchange buffer */
   float* mine;                 /* this rank's exchange buffer (the memory bufs[rank] points to)          */
-  int32_t* const* flags;       /* DEVICE array [world] of device pointers: each rank's flag array        */
-  int32_t epoch;
+  int32_t* const* flags;       /* DEVICE array [world] of device pointers: each rank's flag array,
+                                  int32[world + 1], zero before the first exchange                        */
+  int32_t epoch;               /* number of this exchange: 1, 2, 3 ... alike on every rank; or 0 on every
+                                  exchange: the barrier then counts for itself in flags[rank][world], and a
+                                  recorded launch sequence (a CUDA graph) can be replayed unchanged        */
 } FlarePeers;
 int flare_peer_barrier(const FlarePeers* g, flare_stream_t stream);
 

@@ -33,8 +33,27 @@ def test_every_declared_symbol_is_exported(cabi):
 
 def test_version_and_struct_layout(cabi):
     assert cabi.lib.flare_version() >= 100
-    # 8 x 4-byte fields then 7 x 3 x int64
-    assert C.sizeof(cabi.FlareProblem) == 32 + 7 * 24
+    # 8 x 4-byte fields, 7 x 3 x int64, then the dropout probability (float, padded) and seed (uint64)
+    assert C.sizeof(cabi.FlareProblem) == 32 + 7 * 24 + 16
+
+
+def test_struct_sizes_match_the_header_as_a_c_compiler_sees_it(cabi, tmp_path):
+    """The ctypes mirrors against sizeof/offsetof of the C declarations (gcc on the public header)."""
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "sizes.c"
+    src.write_text(
+        '#include <stdio.h>\n#include <stddef.h>\n#include "flare_b200.h"\n'
+        'int main(void) { printf("%zu %zu %zu %zu %zu\\n", sizeof(FlareProblem), offsetof(FlareProblem, dropout_p),\n'
+        '  offsetof(FlareProblem, dropout_seed), sizeof(FlarePeers), offsetof(FlarePeers, epoch)); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.check_call(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)])
+    got = [int(x) for x in subprocess.check_output([str(exe)]).split()]
+    want = [C.sizeof(cabi.FlareProblem), cabi.FlareProblem.dropout_p.offset, cabi.FlareProblem.dropout_seed.offset,
+            C.sizeof(cabi.FlarePeers), cabi.FlarePeers.epoch.offset]
+    assert got == want
 
 
 def _problem(cabi, **kw):

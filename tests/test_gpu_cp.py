@@ -105,6 +105,81 @@ def test_two_ranks_peer_memory_exchange(cuda_dev):
     _run(2, "peer")
 
 
+def _graph_worker(rank, world, port, q_out, exchange):
+    """The step recorded in a CUDA graph (two steps per graph) and replayed gives, bit for bit, what eager
+    launches give, replay after replay, also with eager steps in between."""
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import flare_b200 as fb
+        from flare_b200.parallel import GraphedStep, PeerExchange, flare_mixer_context_parallel, shard_bounds
+        from oracle import flare_oracle as O
+        B, H, N, M, D = 1, 4, 4096, 128, 32
+        q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=torch.bfloat16, seed=11)
+        n0, n1 = shard_bounds(N, world, rank, multiple=128)
+        qd = q.to(dev).requires_grad_(True)
+        kd = k[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
+        vd = v[:, :, n0:n1].contiguous().to(dev).requires_grad_(True)
+        dyd = dy[:, :, n0:n1].contiguous().to(dev)
+        ex_eager, ex_graph = PeerExchange(), PeerExchange()
+        ex_graph.prepare_mixer(B, H, M, D, dev)
+
+        def step(ex):
+            qd.grad = kd.grad = vd.grad = None
+            y = flare_mixer_context_parallel(qd, kd, vd, 1.0, exchange=ex)
+            y.backward(dyd)
+            return y
+
+        # (nothing of the eager step's autograd graph may stay alive into the recording: its gradient
+        # accumulators belong to the stream they were made on)
+        y0 = step(ex_eager).detach()
+        want = [t.clone() for t in (y0, qd.grad, kd.grad, vd.grad)]
+        gs = GraphedStep(lambda: step(ex_graph))
+        problems = []
+        for it in range(3):
+            y = gs.replay()
+            torch.cuda.synchronize()
+            got = (y.detach(), qd.grad, kd.grad, vd.grad)
+            for name, a, b_ in zip(("y", "dq", "dk", "dv"), got, want):
+                if not torch.equal(a, b_):
+                    problems.append((it, name, O.rel_l2(a.float().cpu(), b_.float().cpu())))
+            if it == 0:
+                step(ex_eager).detach_()                    # eager steps between replays use their own buffers
+        if fb.device_status():
+            problems.append("device status")
+        assert not problems, problems
+        q_out.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        q_out.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_step_replayed_from_a_cuda_graph(cuda_dev):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import __graft_entry__
+    __graft_entry__.build()
+    ctx = mp.get_context("spawn")
+    q_out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_graph_worker, args=(r, 2, port, q_out, "peer")) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        results = [q_out.get(timeout=300) for _ in procs]
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    assert all(msg == "ok" for _, msg in results), results
+
+
 def test_peer_barrier_gives_up_when_the_peer_never_arrives(cuda_dev):
     """One rank alone in a group described as two: the flag of the absent peer never changes, the barrier
     kernel runs out of its bounded wait, records bit 1 in the status word and returns; the context stays
@@ -116,7 +191,7 @@ def test_peer_barrier_gives_up_when_the_peer_never_arrives(cuda_dev):
     from flare_b200 import _cabi
     dev = cuda_dev
     fb.device_status()                                     # clear
-    flags = torch.zeros(2, 2, dtype=torch.int32, device=dev)       # "rank 0" and a peer whose array nobody writes
+    flags = torch.zeros(2, 3, dtype=torch.int32, device=dev)       # "rank 0" and a peer whose array nobody writes (world + 1 slots each)
     buf = torch.zeros(16, device=dev)
     flag_ptrs = torch.tensor([flags[0].data_ptr(), flags[1].data_ptr()], dtype=torch.int64, device=dev)
     buf_ptrs = torch.tensor([buf.data_ptr(), buf.data_ptr()], dtype=torch.int64, device=dev)
