@@ -107,4 +107,26 @@ __device__ __forceinline__ float group_sum(float x) {
   return x;
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_dep() may be scheduled while the kernel
+// before it in the stream is still running; its first statement, grid_dep_sync(), waits until that kernel
+// has completed and its writes are visible, and lets the kernel after it be scheduled in turn.  What is
+// hidden is the launch latency between consecutive kernels (a few microseconds each, a tenth of a
+// context-parallel step at eight ranks).  Rules: every thread executes grid_dep_sync() before its first
+// global-memory access and before any early return (a grid whose blocks all left without waiting would let
+// its successor overtake the predecessor), and only kernels that do so are launched with launch_dep().
+__device__ __forceinline__ void grid_dep_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);   // a failure stays in the last-error state the caller checks
+}
+
 }  // namespace flare

@@ -18,6 +18,7 @@ constexpr int kErrPeerTimeout = 2;
 
 __global__ void __launch_bounds__(32)
 k_peer_barrier(int32_t* const* __restrict__ flags, int rank, int world, int epoch, int* __restrict__ status) {
+  grid_dep_sync();
   const int r = threadIdx.x;
   // epoch 0: the barrier numbers itself with a count kept behind this rank's own flags (slot [world]); every
   // rank's count advances alike because every rank runs the same sequence of barriers.  A launch sequence
@@ -48,7 +49,7 @@ k_peer_barrier(int32_t* const* __restrict__ flags, int rank, int world, int epoc
 }
 
 int launch_peer_barrier(int32_t* const* flags, int rank, int world, int epoch, cudaStream_t st) {
-  k_peer_barrier<<<1, 32, 0, st>>>(flags, rank, world, epoch, tc_status_ptr());
+  launch_dep(k_peer_barrier, dim3(1), dim3(32), 0, st, flags, rank, world, epoch, tc_status_ptr());
   return FLARE_OK;
 }
 

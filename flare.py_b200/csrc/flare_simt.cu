@@ -434,6 +434,7 @@ __global__ void __launch_bounds__(kThreads)
 k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
           float* __restrict__ z32, void* __restrict__ z_out, float* __restrict__ lse_m,
           float* __restrict__ rec_out) {
+  grid_dep_sync();
   const long long row = (long long)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   if (row >= rows) return;
@@ -494,6 +495,7 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
 template <typename Parts>
 __global__ void __launch_bounds__(256)
 k_reduce_sum(Parts parts, int n_parts, long long n, float* __restrict__ out) {
+  grid_dep_sync();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float a = 0.f;
@@ -583,13 +585,13 @@ int simt_bwd_tokens(const Ctx& c, int dtype, const void* q, const void* k, const
 int launch_combine(const float* rec, int n_parts, long long rows, int D, int dtype, float* z32,
                    void* z_out, float* lse_m, float* rec_out, cudaStream_t st) {
   const int rpb = kThreads / 32;
-  k_combine<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(PartsStrided{rec, rows * (D + 2)}, n_parts, rows, D,
-                                                                    dtype, z32, z_out, lse_m, rec_out);
+  launch_dep(k_combine<PartsStrided>, dim3((unsigned)((rows + rpb - 1) / rpb)), dim3(kThreads), 0, st, PartsStrided{rec, rows * (D + 2)},
+             n_parts, rows, D, dtype, z32, z_out, lse_m, rec_out);
   return FLARE_OK;
 }
 
 int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st) {
-  k_reduce_sum<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(PartsStrided{parts, n}, n_parts, n, out);
+  launch_dep(k_reduce_sum<PartsStrided>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, PartsStrided{parts, n}, n_parts, n, out);
   return FLARE_OK;
 }
 
@@ -598,13 +600,13 @@ int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, 
 int launch_combine_ptrs(const float* const* recs, int n_parts, long long rows, int D, int dtype, float* z32,
                         void* z_out, float* lse_m, float* rec_out, cudaStream_t st) {
   const int rpb = kThreads / 32;
-  k_combine<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(PartsPtrs{recs}, n_parts, rows, D, dtype, z32, z_out,
-                                                                    lse_m, rec_out);
+  launch_dep(k_combine<PartsPtrs>, dim3((unsigned)((rows + rpb - 1) / rpb)), dim3(kThreads), 0, st, PartsPtrs{recs}, n_parts, rows, D,
+             dtype, z32, z_out, lse_m, rec_out);
   return FLARE_OK;
 }
 
 int launch_reduce_sum_ptrs(const float* const* parts, int n_parts, long long n, float* out, cudaStream_t st) {
-  k_reduce_sum<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(PartsPtrs{parts}, n_parts, n, out);
+  launch_dep(k_reduce_sum<PartsPtrs>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, PartsPtrs{parts}, n_parts, n, out);
   return FLARE_OK;
 }
 

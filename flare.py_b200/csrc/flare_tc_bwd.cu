@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(256, 1)
 k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
          const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG,
          const __grid_constant__ CUtensorMap tmY, BwdArgs a) {
+  grid_dep_sync();
   constexpr int ROWB = 2 * D;
   constexpr int CPR = ROWB / 16;
   using L = BwdSmem<D>;
@@ -439,8 +440,8 @@ static int launch_bwd(const Ctx& c, const void* q, const void* k, const void* v,
                        (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
       return FLARE_EUNSUPPORTED;
     a.M = mb; a.m0 = m0;
-    if (m0 == 0) k_tc_bwd<D, T16, false><<<(unsigned)grid, 256, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
-    else k_tc_bwd<D, T16, true><<<(unsigned)grid, 256, smem, st>>>(tmQ, tmK, tmV, tmG, tmY, a);
+    if (m0 == 0) launch_dep(k_tc_bwd<D, T16, false>, dim3((unsigned)grid), dim3(256), smem, st, tmQ, tmK, tmV, tmG, tmY, a);
+    else launch_dep(k_tc_bwd<D, T16, true>, dim3((unsigned)grid), dim3(256), smem, st, tmQ, tmK, tmV, tmG, tmY, a);
   }
   return FLARE_OK;
 }

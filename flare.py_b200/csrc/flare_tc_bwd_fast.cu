@@ -77,6 +77,7 @@ template <bool ACC>                               // ACC: add to the dK/dV an ea
 __global__ void __launch_bounds__(kBFSoftmax + kBFHelpers + 32, 1)
 k_tc_bwd_fast(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmG, BwdFastArgs a) {
+  grid_dep_sync();
   constexpr int D = 32, ROWB = 64, CPR = 4;
   using L = BwdFastSmem;
   const int split = blockIdx.x % a.n_splits;
@@ -640,8 +641,8 @@ int tc_bwd_fast_launch(const Ctx& c, const void* q, const void* k, const void* v
                        (qb ? c.qs[0] : c.qs[1] * c.H) * e, 256))
       return FLARE_EUNSUPPORTED;
     a.M = mb; a.m0 = m0;
-    if (m0 == 0) k_tc_bwd_fast<false><<<(unsigned)grid, kBFSoftmax + kBFHelpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
-    else k_tc_bwd_fast<true><<<(unsigned)grid, kBFSoftmax + kBFHelpers + 32, smem, st>>>(tmQ, tmK, tmV, tmG, a);
+    if (m0 == 0) launch_dep(k_tc_bwd_fast<false>, dim3((unsigned)grid), dim3(kBFSoftmax + kBFHelpers + 32), smem, st, tmQ, tmK, tmV, tmG, a);
+    else launch_dep(k_tc_bwd_fast<true>, dim3((unsigned)grid), dim3(kBFSoftmax + kBFHelpers + 32), smem, st, tmQ, tmK, tmV, tmG, a);
   }
   return FLARE_OK;
 }

@@ -32,6 +32,7 @@ constexpr int kRangeParts = 64;
 
 __global__ void __launch_bounds__(256)
 k_bwd_range_c(const float* __restrict__ lse_n, int N, float* __restrict__ part /*[BH][parts][2]*/) {
+  grid_dep_sync();
   const int bh = blockIdx.y, p = blockIdx.x;
   const float* c = lse_n + (long long)bh * N;
   float mx = -INFINITY, mn = INFINITY;
@@ -58,6 +59,7 @@ k_bwd_range_c(const float* __restrict__ lse_n, int N, float* __restrict__ part /
 __global__ void __launch_bounds__(256)
 k_bwd_range_final(const float* __restrict__ lse_m, int M, const float* __restrict__ part,
                   float* __restrict__ mu_out, int* __restrict__ flag_out) {
+  grid_dep_sync();
   const int bh = blockIdx.x;
   float lmx = -INFINITY, lmn = INFINITY, cmx = -INFINITY, cmn = INFINITY;
   for (int i = threadIdx.x; i < M; i += blockDim.x) {
@@ -109,8 +111,8 @@ int tc_bwd_fast_main(const Ctx& c, const void* q, const void* k, const void* v, 
   float* part = reinterpret_cast<float*>(w);  w += (bh * kRangeParts * 2 * sizeof(float) + 255) & ~size_t(255);
   float* mu = reinterpret_cast<float*>(w);    w += (bh * sizeof(float) + 255) & ~size_t(255);
   int* flag = reinterpret_cast<int*>(w);
-  k_bwd_range_c<<<dim3(kRangeParts, (unsigned)bh), 256, 0, st>>>(lse_n, c.N, part);
-  k_bwd_range_final<<<(unsigned)bh, 256, 0, st>>>(lse_m, c.M, part, mu, flag);
+  launch_dep(k_bwd_range_c, dim3(kRangeParts, (unsigned)bh), dim3(256), 0, st, lse_n, c.N, part);
+  launch_dep(k_bwd_range_final, dim3((unsigned)bh), dim3(256), 0, st, lse_m, c.M, part, mu, flag);
   *flag_out = flag;
   return tc_bwd_fast_launch(c, q, k, v, dy, y, z32, dz32, lse_m, lse_n, dk, dv, dq_part, mu, flag, st);
 }

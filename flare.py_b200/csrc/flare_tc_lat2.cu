@@ -147,6 +147,7 @@ template <int D, int MODE, typename T16, bool DROP>
 __global__ void __launch_bounds__(kLat2Softmax + 32, 2)
 k_tc_lat2(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
           const __grid_constant__ CUtensorMap tmV, Lat2Args a) {
+  grid_dep_sync();
   constexpr int ROWB = 2 * D;
   constexpr int CPR = ROWB / 16;
   constexpr int NS = kLat2Stages;
@@ -529,8 +530,8 @@ static int launch_lat2(const Ctx& c, const void* q, const void* k, const void* v
     return FLARE_ECUDA;
   const long long grid = (long long)c.n_splits * a.n_mblk * c.B * c.H;
   if (grid > 0x7fffffffLL) return FLARE_EUNSUPPORTED;
-  if (a.drop.on) k_tc_lat2<D, MODE, T16, true><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
-  else k_tc_lat2<D, MODE, T16, false><<<(unsigned)grid, kLat2Softmax + 32, smem, st>>>(tmQ, tmK, tmV, a);
+  if (a.drop.on) launch_dep(k_tc_lat2<D, MODE, T16, true>, dim3((unsigned)grid), dim3(kLat2Softmax + 32), smem, st, tmQ, tmK, tmV, a);
+  else launch_dep(k_tc_lat2<D, MODE, T16, false>, dim3((unsigned)grid), dim3(kLat2Softmax + 32), smem, st, tmQ, tmK, tmV, a);
   return FLARE_OK;
 }
 

@@ -62,6 +62,7 @@ constexpr int kS2Softmax = 512, kS2Epilogue = 128;
 template <int D, typename T16, bool DROP>
 __global__ void __launch_bounds__(kS2Softmax + kS2Epilogue + 32, 1)
 k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmQ, Scatter2Args a) {
+  grid_dep_sync();
   constexpr int ROWB = 2 * D;
   using L = Scatter2Smem<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -411,8 +412,8 @@ static int launch_scatter2(const Ctx& c, const void* q, const void* k, const flo
     a.M = mb; a.m0 = m0; a.M_total = c.M;
     a.z32 = z32 + (long long)m0 * D;
     a.accumulate = m0 > 0 ? 1 : 0;
-    if (a.drop.on) k_tc_scatter2<D, T16, true><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
-    else k_tc_scatter2<D, T16, false><<<(unsigned)grid, kS2Softmax + kS2Epilogue + 32, smem, st>>>(tmK, tmQ, a);
+    if (a.drop.on) launch_dep(k_tc_scatter2<D, T16, true>, dim3((unsigned)grid), dim3(kS2Softmax + kS2Epilogue + 32), smem, st, tmK, tmQ, a);
+    else launch_dep(k_tc_scatter2<D, T16, false>, dim3((unsigned)grid), dim3(kS2Softmax + kS2Epilogue + 32), smem, st, tmK, tmQ, a);
   }
   return FLARE_OK;
 }
