@@ -66,6 +66,8 @@ SIGNATURES = {
     "flare_causal_workspace_bytes": (_sz, [_P]),
     "flare_causal_prefill": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_causal_decode": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "flare_causal_bwd_workspace_bytes": (_sz, [_P]),
+    "flare_causal_bwd": (_i, [_P, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_causal_linear_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "flare_causal_linear": (_i, [_i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "flare_triple_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

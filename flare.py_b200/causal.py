@@ -4,7 +4,8 @@ The reference links this path (README.md:60) without shipping code; the semantic
 figs/flare_decoder.py:211-250.  ``y_t = softmax_M(S[:, t]) . z_t`` with
 ``z_t = softmax_{n <= t}(S) v`` and ``S = scale * q k^T``.  The state is one record per latent,
 ``[B, H, M, D + 2] = (acc[D], m, l)`` in fp32, the same record the non-causal gather writes per token
-range; ``causal_state_init`` gives the empty one.  Forward only (serving path).
+range; ``causal_state_init`` gives the empty one.  ``flare_causal_mixer`` is the differentiable form for
+training (a whole sequence from an empty prefix); prefill with a carried state and decode are forward only.
 """
 from __future__ import annotations
 
@@ -15,7 +16,7 @@ import torch
 from ._cabi import check, lib, ptr, stream_of
 from .mixer import _need_cuda, _q3, _tok, make_problem
 
-__all__ = ["causal_state_init", "flare_causal_prefill", "flare_causal_decode"]
+__all__ = ["causal_state_init", "flare_causal_prefill", "flare_causal_decode", "flare_causal_mixer"]
 
 
 def causal_state_init(B: int, H: int, M: int, D: int, device) -> torch.Tensor:
@@ -61,3 +62,40 @@ def flare_causal_decode(q, k, v, state, scale: float = 1.0):
         check(lib.flare_causal_decode(C.byref(p), ptr(q), ptr(k), ptr(v), ptr(y), ptr(state), stream_of(k)),
               "flare_causal_decode")
     return y
+
+
+class _CausalMixerFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale):
+        y, _ = flare_causal_prefill(q, k, v, scale)
+        ctx.save_for_backward(q, k, v)
+        ctx.scale = scale
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        q, k, v = ctx.saved_tensors
+        q3, _ = _q3(q)
+        kk, vv, dy = _tok(k), _tok(v), _tok(dy)
+        B, H, N, D = kk.shape
+        M = q3.shape[-2]
+        dev = kk.device
+        with torch.cuda.device(dev):
+            dk = torch.empty(kk.shape, dtype=kk.dtype, device=dev)
+            dv = torch.empty(vv.shape, dtype=vv.dtype, device=dev)
+            dq32 = torch.empty(B, H, M, D, dtype=torch.float32, device=dev)
+            p = make_problem(q3, kk, ctx.scale, v=vv, dy=dy, dk=dk, dv=dv)
+            ws = torch.empty(lib.flare_causal_bwd_workspace_bytes(C.byref(p)), dtype=torch.uint8, device=dev)
+            check(lib.flare_causal_bwd(C.byref(p), ptr(q3), ptr(kk), ptr(vv), ptr(dy), ptr(dq32), ptr(dk), ptr(dv),
+                                       ptr(ws), stream_of(kk)), "flare_causal_bwd")
+        # one latent gradient per (b, h): shared latents sum over the batch; a batch made by expand() gets the
+        # per-batch gradients, which autograd folds back itself
+        dq = dq32.sum(0) if q.dim() == 3 else dq32
+        return dq.to(q.dtype), dk, dv, None
+
+
+def flare_causal_mixer(q, k, v, scale: float = 1.0):
+    """Causal FLARE over a whole sequence, differentiable in q, k, v: token t sees the latent summary of
+    tokens 0..t only.  q [H,M,D] (or [B,H,M,D]), k, v [B,H,N,D]; returns y [B,H,N,D]."""
+    _need_cuda(q, k, v)
+    return _CausalMixerFn.apply(q, k, v, float(scale))

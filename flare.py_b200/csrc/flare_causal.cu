@@ -344,6 +344,18 @@ int run_walk(const FlareProblem* p, const CausalArgs& a, int n_cta_x, cudaStream
 
 }  // namespace
 
+namespace flare {
+// pass 2 for the backward (flare_causal_bwd.cu), which needs the same chunk-start records
+int launch_causal_scan(float* rec, int n_chunks, long long rows, int D, const float* state_in, float* state_out,
+                       cudaStream_t st) {
+  const int rpb = kThreads / 32;
+  k_causal_scan<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(rec, n_chunks, rows, D, state_in, state_out);
+  const cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal scan: %s", cudaGetErrorString(e));
+  return FLARE_OK;
+}
+}  // namespace flare
+
 extern "C" {
 
 size_t flare_causal_workspace_bytes(const FlareProblem* p) {

@@ -250,6 +250,16 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
 int flare_causal_decode(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
                         float* state, flare_stream_t stream);
 
+/* Backward of flare_causal_prefill from an empty prefix: dq32 [B][H][M][D] fp32 (one latent gradient per
+ * (b, h): sum over b when the latents are shared), dk, dv with dk_stride / dv_stride, from dy (dy_stride).
+ * A reverse scan over 128-token chunks on the forward's own chunk-start records, which it rebuilds in
+ * `workspace` (flare_causal_bwd_workspace_bytes(p) bytes); fp32 arithmetic.  D in {16,32,64},
+ * M * D <= 8192.  No reference code exists for this path: the algorithm is checked against autograd
+ * through the dense definition (oracle/flare_oracle.py: causal_bwd_chunked, causal_bwd_autograd). */
+size_t flare_causal_bwd_workspace_bytes(const FlareProblem* p);
+int flare_causal_bwd(const FlareProblem* p, const void* q, const void* k, const void* v, const void* dy,
+                     float* dq32, void* dk, void* dv, float* workspace, flare_stream_t stream);
+
 /* Causal linear attention, Y_t = Q_t . sum_{n<=t} K_n^T V_n / N (lra/models/triton/causal_linear.py:23-145;
  * reference form :317-336; forward only, as there).  q, k: [B,H,N,Dk]; v, y: [B,H,N,Dv]; strides in
  * elements for dims (b, h, n), unit stride on the last dim.  workspace:

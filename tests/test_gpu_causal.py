@@ -118,3 +118,77 @@ def test_serving_shape_split_prefill(cuda_dev):
     z_a = st_all[..., :D] / st_all[..., D + 1:D + 2]
     z_b = st[..., :D] / st[..., D + 1:D + 2]
     assert ((z_a - z_b).norm() / z_a.norm()).item() <= 2e-2
+
+
+# ---------------------------------------------------------------------------------------------------------
+# backward (flare_causal_mixer): against autograd through the dense definition and the chunked restatement
+# ---------------------------------------------------------------------------------------------------------
+def _fb():
+    import flare_b200 as fb
+    return fb
+
+
+def _bwd_case(fb, dev, B, H, N, M, D, dtype, scale, seed):
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=dtype, seed=seed)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    y = fb.flare_causal_mixer(qd, kd, vd, scale)
+    y.backward(dy.to(dev))
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    return (q, k, v, dy), (y.detach().cpu(), qd.grad.cpu(), kd.grad.cpu(), vd.grad.cpu())
+
+
+@pytest.mark.parametrize("B,H,N,M,D", [(1, 2, 96, 16, 16), (2, 2, 300, 32, 32), (1, 1, 257, 64, 64), (1, 2, 129, 128, 64)])
+def test_backward_matches_autograd_of_the_dense_definition(cuda_dev, B, H, N, M, D):
+    """fp32 kernel against fp64 autograd through causal_dense: ragged ends (N not a multiple of 32 or 128),
+    one to three chunks, every supported head dim."""
+    fb = _fb()
+    (q, k, v, dy), (y, dq, dk, dv) = _bwd_case(fb, cuda_dev, B, H, N, M, D, torch.float32, 0.8, seed=21)
+    qf, kf, vf, dyf = (t.double() for t in (q, k, v, dy))
+    dq_ref, dk_ref, dv_ref = O.causal_bwd_autograd(qf, kf, vf, dyf, 0.8)
+    assert O.rel_l2(y.double(), O.causal_dense(qf, kf, vf, 0.8)) <= 1e-5
+    assert O.rel_l2(dq.double(), dq_ref) <= 1e-4
+    assert O.rel_l2(dk.double(), dk_ref) <= 1e-4
+    assert O.rel_l2(dv.double(), dv_ref) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-4), (torch.bfloat16, 3e-2), (torch.float16, 5e-3)])
+def test_backward_long_sequence_against_the_chunked_restatement(cuda_dev, dtype, tol):
+    """N = 2000 (16 chunks, ragged last one), latents shared by two batch entries: the carried suffix state
+    crosses many chunk boundaries.  The yardstick is the oracle's reverse chunk scan in fp64 on the same
+    rounded inputs (itself pinned to autograd on small cases in the CPU suite)."""
+    fb = _fb()
+    B, H, N, M, D = 2, 2, 2000, 32, 32
+    (q, k, v, dy), (y, dq, dk, dv) = _bwd_case(fb, cuda_dev, B, H, N, M, D, dtype, 1.0, seed=22)
+    qf, kf, vf, dyf = (t.double() for t in (q, k, v, dy))
+    dq_ref, dk_ref, dv_ref = O.causal_bwd_chunked(qf, kf, vf, dyf, 1.0, chunk=64)
+    assert O.rel_l2(dq.double(), dq_ref) <= tol
+    assert O.rel_l2(dk.double(), dk_ref) <= tol
+    assert O.rel_l2(dv.double(), dv_ref) <= tol
+
+
+def test_backward_with_growing_logits(cuda_dev):
+    """Keys whose norm grows along the sequence: the running maxima rise by tens of units from chunk to
+    chunk, so the carried suffix state is rescaled by tiny factors and early tokens' weights underflow
+    relative to late maxima -- finite results that match the fp64 restatement."""
+    fb = _fb()
+    B, H, N, M, D = 1, 2, 640, 32, 32
+    q, k, v, dy = O.make_inputs(B, H, N, M, D, dtype=torch.float32, seed=23)
+    k = k * torch.linspace(0.5, 6.0, N).view(1, 1, N, 1)
+    qd, kd, vd = (t.to(cuda_dev).requires_grad_(True) for t in (q, k, v))
+    y = fb.flare_causal_mixer(qd, kd, vd, 1.0)
+    y.backward(dy.to(cuda_dev))
+    qf, kf, vf, dyf = (t.double() for t in (q, k, v, dy))
+    dq_ref, dk_ref, dv_ref = O.causal_bwd_chunked(qf, kf, vf, dyf, 1.0, chunk=32)
+    for got, ref in ((qd.grad, dq_ref), (kd.grad, dk_ref), (vd.grad, dv_ref)):
+        assert torch.isfinite(got).all()
+        assert O.rel_l2(got.cpu().double(), ref) <= 2e-4
+
+
+def test_backward_refuses_what_it_cannot_hold(cuda_dev):
+    fb = _fb()
+    q, k, v, dy = O.make_inputs(1, 1, 64, 64, 128, dtype=torch.float32, seed=1)   # forward: fine; backward: D = 128
+    qd, kd, vd = (t.to(cuda_dev).requires_grad_(True) for t in (q, k, v))
+    y = fb.flare_causal_mixer(qd, kd, vd, 1.0)
+    with pytest.raises(RuntimeError, match="causal_bwd"):
+        y.backward(dy.to(cuda_dev))
