@@ -555,9 +555,19 @@ def run_causal(args):
     k1, v1 = k[:, :, :1].contiguous(), v[:, :, :1].contiguous()
     fb.flare_causal_decode(q, k1, v1, st, 1.0)
     us = timed(lambda: fb.flare_causal_decode(q, k1, v1, st, 1.0), max(args.steps, 20)) * 1e3
+    # training step of the same layer: forward + backward through flare_causal_mixer
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    dy = torch.randn(B, H, N, D, generator=g).bfloat16().to(dev)
+
+    def train_step():
+        qg.grad = kg.grad = vg.grad = None
+        fb.flare_causal_mixer(qg, kg, vg, 1.0).backward(dy)
+
+    train_step()
+    train_ms = timed(train_step, max(2, min(args.steps, 5)))
     print(json.dumps(dict(metric="causal FLARE prefill Mtokens/s", value=B * N / ms / 1e3, unit="Mtokens/s", n_gpus=1,
                           steps=args.steps, warmup=max(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
-                          dtype="bf16", data="synthetic", decode_step_us=us,
+                          dtype="bf16", data="synthetic", decode_step_us=us, fwd_bwd_ms=train_ms,
                           config=dict(workload=f"causal_prefill: B={B} H={H} N={N} M={M} D={D} bf16, one layer's mixer"))),
           flush=True)
 
