@@ -64,6 +64,44 @@ __device__ __forceinline__ float exp_or_zero(float from, float to) {   // e^{fro
   return from == -INFINITY ? 0.f : expf(from - to);
 }
 
+// out(r, c) = sum_k A(r, k) B(k, c) for r < R, c < Cn: every thread a TR x TC register tile, so that one pair of
+// shared-memory loads feeds TR * TC / (TR + TC) multiply-adds instead of half of one.  A thread's rows are
+// rt, rt + nr, ... and its columns ct, ct + nc, ...: neighbouring threads read neighbouring columns of B.
+template <int TR, int TC, typename FA, typename FB, typename FS>
+__device__ __forceinline__ void tile_mm(int R, int Cn, int Kn, FA A, FB B, FS store) {
+  const int nr = (R + TR - 1) / TR, nc = (Cn + TC - 1) / TC;
+  for (int tile = threadIdx.x; tile < nr * nc; tile += kThreads) {
+    const int rt = tile / nc, ct = tile % nc;
+    int rr[TR], cc[TC];
+#pragma unroll
+    for (int i = 0; i < TR; ++i) rr[i] = min(rt + i * nr, R - 1);
+#pragma unroll
+    for (int j = 0; j < TC; ++j) cc[j] = min(ct + j * nc, Cn - 1);
+    float acc[TR][TC];
+#pragma unroll
+    for (int i = 0; i < TR; ++i)
+#pragma unroll
+      for (int j = 0; j < TC; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+    for (int k = 0; k < Kn; ++k) {
+      float av[TR], bv[TC];
+#pragma unroll
+      for (int i = 0; i < TR; ++i) av[i] = A(rr[i], k);
+#pragma unroll
+      for (int j = 0; j < TC; ++j) bv[j] = B(k, cc[j]);
+#pragma unroll
+      for (int i = 0; i < TR; ++i)
+#pragma unroll
+        for (int j = 0; j < TC; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < TR; ++i)
+#pragma unroll
+      for (int j = 0; j < TC; ++j)
+        if (rt + i * nr < R && ct + j * nc < Cn) store(rt + i * nr, ct + j * nc, acc[i][j]);
+  }
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
 k_causal_bwd(CausalBwdArgs a) {
@@ -124,14 +162,8 @@ k_causal_bwd(CausalBwdArgs a) {
   };
   // S_mt = scale q_m . k_t into sE; -inf for the tokens past cnt
   auto scores = [&](int cnt) {
-    for (int i = tid; i < M * kSub; i += kThreads) {
-      const int m = i / kSub, t = i % kSub;
-      const float* qr = sQ + m * DP;
-      const float* kr = sK + t * DP;
-      float s = 0.f;
-      _Pragma("unroll 16") for (int dd = 0; dd < D; ++dd) s = fmaf(qr[dd], kr[dd], s);
-      sE[m * kTP + t] = t < cnt ? s * a.scale : -INFINITY;
-    }
+    tile_mm<4, 4>(M, kSub, D, [&](int m, int dd) { return sQ[m * DP + dd]; }, [&](int dd, int t) { return sK[t * DP + dd]; },
+                  [&](int m, int t, float s) { sE[m * kTP + t] = t < cnt ? s * a.scale : -INFINITY; });
   };
 
   const int chunks = (a.N + kChunk - 1) / kChunk;
@@ -163,12 +195,8 @@ k_causal_bwd(CausalBwdArgs a) {
         out[m * W + D] = mu; out[m * W + D + 1] = l;
       }
       __syncthreads();
-      for (int i = tid; i < MD; i += kThreads) {
-        const int m = i / D, dd = i % D;
-        float acc = sAa[m] * st[m * W + dd];
-        _Pragma("unroll 8") for (int t = 0; t < kSub; ++t) acc = fmaf(sE[m * kTP + t], sV[t * DP + dd], acc);
-        out[m * W + dd] = acc;
-      }
+      tile_mm<4, 4>(M, D, kSub, [&](int m, int t) { return sE[m * kTP + t]; }, [&](int t, int dd) { return sV[t * DP + dd]; },
+                    [&](int m, int dd, float x) { out[m * W + dd] = fmaf(sAa[m], st[m * W + dd], x); });
       __syncthreads();
     }
 
@@ -218,28 +246,19 @@ k_causal_bwd(CausalBwdArgs a) {
         sRin[m] *= w;
         sNu[m] = w;                                // kept until the rows of R are rescaled below
       }
-      for (int i = tid; i < kSub * kSub; i += kThreads) {
-        const int n = i / kSub, t = i % kSub;
-        const float* vr = sV + n * DP;
-        const float* gr = sG + t * DP;
-        float x = 0.f;
-        _Pragma("unroll 16") for (int dd = 0; dd < D; ++dd) x = fmaf(vr[dd], gr[dd], x);
-        sX[n * kTP + t] = x;
-      }
+      tile_mm<2, 2>(kSub, kSub, D, [&](int n, int dd) { return sV[n * DP + dd]; }, [&](int dd, int t) { return sG[t * DP + dd]; },
+                    [&](int n, int t, float x) { sX[n * kTP + t] = x; });
       __syncthreads();
       for (int i = tid; i < MD; i += kThreads) sRh[(i / D) * DP + i % D] *= sNu[i / D];
       // c_mt
-      for (int i = tid; i < M * kSub; i += kThreads) {
-        const int m = i / kSub, t = i % kSub;
-        const float* gr = sG + t * DP;
-        const float* ar = st + m * W;
-        float c0 = 0.f;
-        _Pragma("unroll 16") for (int dd = 0; dd < D; ++dd) c0 = fmaf(ar[dd], gr[dd], c0);
-        float c1 = 0.f;
-        _Pragma("unroll 4") for (int n = 0; n <= t; ++n) c1 = fmaf(sE[m * kTP + n], sX[n * kTP + t], c1);
-        const float l = sLp[m * kTP + t];
-        sC[m * kTP + t] = l > 0.f ? (sAa[m] * c0 + c1) / l : 0.f;
-      }
+      // (one product over the concatenated axis [d | n]: a_m acc0_m against g_t, then E_mn against X_nt for n <= t)
+      tile_mm<4, 4>(M, kSub, D + kSub,
+                    [&](int m, int kk) { return kk < D ? sAa[m] * st[m * W + kk] : sE[m * kTP + kk - D]; },
+                    [&](int kk, int t) { return kk < D ? sG[t * DP + kk] : (kk - D <= t ? sX[(kk - D) * kTP + t] : 0.f); },
+                    [&](int m, int t, float x) {
+                      const float l = sLp[m * kTP + t];
+                      sC[m * kTP + t] = l > 0.f ? x / l : 0.f;
+                    });
       __syncthreads();
       for (int m = tid; m < M; m += kThreads) sNu[m] = sMu[m];       // the carry leaves this sub-chunk relative to its mu
       // delta_t = sum_m A_mt c_mt (A = G l);  W_tn = sum_m G_mt E_mn
@@ -248,55 +267,59 @@ k_causal_bwd(CausalBwdArgs a) {
         _Pragma("unroll 8") for (int m = 0; m < M; ++m) dl = fmaf(sGm[m * kTP + t] * sLp[m * kTP + t], sC[m * kTP + t], dl);
         sDelta[t] = dl;
       }
-      for (int i = tid; i < kSub * kSub; i += kThreads) {
-        const int t = i / kSub, n = i % kSub;
-        float w = 0.f;
-        _Pragma("unroll 8") for (int m = 0; m < M; ++m) w = fmaf(sGm[m * kTP + t], sE[m * kTP + n], w);
-        sW[t * kTP + n] = w;
-      }
+      tile_mm<2, 2>(kSub, kSub, M, [&](int t, int m) { return sGm[m * kTP + t]; }, [&](int m, int n) { return sE[m * kTP + n]; },
+                    [&](int t, int n, float w) { sW[t * kTP + n] = w; });
       __syncthreads();
       // dv_n = sum_m E_mn Rin_m + sum_{t >= n} W_tn g_t
-      for (int i = tid; i < cnt * D; i += kThreads) {
-        const int n = i / D, dd = i % D;
-        float acc = 0.f;
-        _Pragma("unroll 8") for (int m = 0; m < M; ++m) acc = fmaf(sE[m * kTP + n], sRh[m * DP + dd], acc);
-        _Pragma("unroll 4") for (int t = n; t < cnt; ++t) acc = fmaf(sW[t * kTP + n], sG[t * DP + dd], acc);
-        dvp[(long long)(s0 + n) * a.dvs[2] + dd] = from_f32<T>(acc);
-      }
+      tile_mm<2, 4>(cnt, D, M + cnt,
+                    [&](int n, int kk) { return kk < M ? sE[kk * kTP + n] : (kk - M >= n ? sW[(kk - M) * kTP + n] : 0.f); },
+                    [&](int kk, int dd) { return kk < M ? sRh[kk * DP + dd] : sG[(kk - M) * DP + dd]; },
+                    [&](int n, int dd, float x) { dvp[(long long)(s0 + n) * a.dvs[2] + dd] = from_f32<T>(x); });
       // de_mn = Rin_m . v_n + rin_m + sum_{t >= n} G_mt (X_nt - c_mt);  dS = E de + A (c - delta)
-      for (int i = tid; i < M * kSub; i += kThreads) {
-        const int m = i / kSub, n = i % kSub;
-        const float* rr = sRh + m * DP;
-        const float* vr = sV + n * DP;
-        float de = sRin[m];
-        _Pragma("unroll 16") for (int dd = 0; dd < D; ++dd) de = fmaf(rr[dd], vr[dd], de);
-        _Pragma("unroll 4") for (int t = n; t < cnt; ++t) de = fmaf(sGm[m * kTP + t], sX[n * kTP + t] - sC[m * kTP + t], de);
-        const float A = sGm[m * kTP + n] * sLp[m * kTP + n];
-        sDe[m * kTP + n] = n < cnt ? sE[m * kTP + n] * de + A * (sC[m * kTP + n] - sDelta[n]) : 0.f;
+      // (the c part of the sum is a reverse running sum along the row: rin_m - sum_{t >= n} G_mt c_mt into sDe first)
+      for (int m = tid; m < M; m += kThreads) {
+        float run = sRin[m];
+#pragma unroll 8
+        for (int n = kSub - 1; n >= 0; --n) {
+          run -= sGm[m * kTP + n] * sC[m * kTP + n];
+          sDe[m * kTP + n] = run;
+        }
       }
+      __syncthreads();
+      tile_mm<4, 4>(M, kSub, D + kSub,
+                    [&](int m, int kk) { return kk < D ? sRh[m * DP + kk] : sGm[m * kTP + kk - D]; },
+                    [&](int kk, int n) { return kk < D ? sV[n * DP + kk] : (kk - D >= n ? sX[n * kTP + kk - D] : 0.f); },
+                    [&](int m, int n, float x) {
+                      const float de = x + sDe[m * kTP + n];
+                      const float A = sGm[m * kTP + n] * sLp[m * kTP + n];
+                      sDe[m * kTP + n] = n < cnt ? sE[m * kTP + n] * de + A * (sC[m * kTP + n] - sDelta[n]) : 0.f;
+                    });
       __syncthreads();
       // dq_m += scale sum_n dS_mn k_n (registers);  dk_n = scale sum_m dS_mn q_m;
       // Rout = Rin + G g,  rout = rin - sum_t G_mt c_mt
+      {
+        // this thread's 4 x 4 tile of dq stays in registers over the whole sequence (M * D / 16 <= 512 tiles)
+        const int nr = (M + 3) / 4, nc = D / 4;
+        if (tid < nr * nc) {
+          const int rt = tid / nc, ct = tid % nc;
+#pragma unroll 4
+          for (int n = 0; n < cnt; ++n) {
+            float av[4], bv[4];
 #pragma unroll
-      for (int r = 0; r < kMaxDq; ++r) {
-        const int i = tid + r * kThreads;
-        if (i < MD) {
-          const int m = i / D, dd = i % D;
-          float acc = 0.f, racc = 0.f;
-          _Pragma("unroll 4") for (int n = 0; n < cnt; ++n) {
-            acc = fmaf(sDe[m * kTP + n], sK[n * DP + dd], acc);
-            racc = fmaf(sGm[m * kTP + n], sG[n * DP + dd], racc);
+            for (int i = 0; i < 4; ++i) av[i] = sDe[min(rt + i * nr, M - 1) * kTP + n];
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) bv[jj] = sK[n * DP + ct + jj * nc];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) dqr[4 * i + jj] = fmaf(av[i], bv[jj], dqr[4 * i + jj]);
           }
-          dqr[r] = fmaf(a.scale, acc, dqr[r]);
-          sRh[m * DP + dd] += racc;                 // (this thread alone touches the element; its readers are done)
         }
       }
-      for (int i = tid; i < cnt * D; i += kThreads) {
-        const int n = i / D, dd = i % D;
-        float acc = 0.f;
-        _Pragma("unroll 8") for (int m = 0; m < M; ++m) acc = fmaf(sDe[m * kTP + n], sQ[m * DP + dd], acc);
-        dkp[(long long)(s0 + n) * a.dks[2] + dd] = from_f32<T>(acc * a.scale);
-      }
+      tile_mm<4, 4>(M, D, cnt, [&](int m, int t) { return sGm[m * kTP + t]; }, [&](int t, int dd) { return sG[t * DP + dd]; },
+                    [&](int m, int dd, float x) { sRh[m * DP + dd] += x; });   // (one thread per element; its readers are done)
+      tile_mm<2, 4>(cnt, D, M, [&](int n, int m) { return sDe[m * kTP + n]; }, [&](int m, int dd) { return sQ[m * DP + dd]; },
+                    [&](int n, int dd, float x) { dkp[(long long)(s0 + n) * a.dks[2] + dd] = from_f32<T>(x * a.scale); });
       for (int m = tid; m < M; m += kThreads) {
         float r = sRin[m];
         for (int t = 0; t < cnt; ++t) r -= sGm[m * kTP + t] * sC[m * kTP + t];
@@ -306,10 +329,16 @@ k_causal_bwd(CausalBwdArgs a) {
     }
   }
   float* dq = a.dq + (long long)bh * MD;
+  {
+    const int nr = (M + 3) / 4, nc = D / 4;
+    if (tid < nr * nc) {
+      const int rt = tid / nc, ct = tid % nc;
 #pragma unroll
-  for (int r = 0; r < kMaxDq; ++r) {
-    const int i = tid + r * kThreads;
-    if (i < MD) dq[i] = dqr[r];
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+          if (rt + i * nr < M) dq[(rt + i * nr) * D + ct + jj * nc] = dqr[4 * i + jj] * a.scale;
+    }
   }
 }
 
