@@ -144,9 +144,12 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
     const long long lrow = ((long long)b * a.H + h) * a.M_total + a.m0;
     const float* zb = a.z32 + lrow * D;
     const float* dzb = use_g ? a.dz32 + lrow * D : nullptr;
+    // CPR consecutive lanes share a latent row (eight values each): coalesced reads, and Delta_m = dZ_m . Z_m is
+    // summed over them by shuffles (whole warps run every iteration)
     for (int i = tid; i < 256 * CPR; i += 256) {
       const int r = i / CPR, c = i % CPR;
       uint4 pz = make_uint4(0, 0, 0, 0), pd = make_uint4(0, 0, 0, 0);
+      float dl = 0.f;
       if (r < M) {
         const float4 z0 = *reinterpret_cast<const float4*>(zb + r * D + c * 8);
         const float4 z1 = *reinterpret_cast<const float4*>(zb + r * D + c * 8 + 4);
@@ -157,21 +160,24 @@ k_tc_bwd(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtens
           const float4 d1 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8 + 4);
           pd = make_uint4(Op16<T16>::pack(d0.x, d0.y), Op16<T16>::pack(d0.z, d0.w), Op16<T16>::pack(d1.x, d1.y),
                           Op16<T16>::pack(d1.z, d1.w));
+          // Delta_m from dZ as the tensor core sees it (rounded to the operand type): sum_n P_mn (V_n . dZ_m) then
+          // cancels against it exactly instead of leaving a rounding residue of one sign along the row
+          const float zf[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+          const uint32_t dw[4] = {pd.x, pd.y, pd.z, pd.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 df = Op16<T16>::unpack(dw[j]);
+            dl = fmaf(df.x, zf[2 * j], dl);
+            dl = fmaf(df.y, zf[2 * j + 1], dl);
+          }
         }
       }
+#pragma unroll
+      for (int o = 1; o < CPR; o <<= 1) dl += __shfl_xor_sync(0xffffffffu, dl, o);
       *reinterpret_cast<uint4*>(sZ + swz_off<ROWB>(r, c)) = pz;
       *reinterpret_cast<uint4*>(sDZ + swz_off<ROWB>(r, c)) = pd;
-    }
-    {
-      const int m = tid;                           // 256 threads, 256 latent slots
-      float l2 = INFINITY, dl = 0.f;
-      if (m < M && use_g) {                        // without the gather term P = 0 (L = +inf)
-        // Delta_m from dZ as the tensor core sees it (rounded to the operand type): sum_n P_mn (V_n . dZ_m) then
-        // cancels against it exactly instead of leaving a rounding residue of one sign along the row
-        for (int i = 0; i < D; ++i) dl = fmaf(Op16<T16>::unpack(Op16<T16>::pack(dzb[m * D + i], 0.f)).x, zb[m * D + i], dl);
-        l2 = a.lse_m[lrow + m] * kLog2e;
-      }
-      sLD[m] = make_float2(l2, dl);
+      if (c == 0)                                  // without the gather term P = 0 (L = +inf)
+        sLD[r] = make_float2(r < M && use_g ? a.lse_m[lrow + r] * kLog2e : INFINITY, dl);
     }
   }
   fence_proxy_async();

@@ -173,11 +173,16 @@ k_tc_bwd_fast(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const long long lrow = ((long long)b * a.H + h) * a.M_total + a.m0;
     const float* zb = a.z32 + lrow * D;
     const float* dzb = a.dz32 + lrow * D;
+    // four consecutive lanes share a latent row (eight values each): coalesced reads, and Delta_m = dZ_m . Z_m
+    // is summed over the four by shuffles (whole warps run every iteration: 256 * CPR and blockDim are
+    // multiples of 32)
     for (int i = tid; i < 256 * CPR; i += blockDim.x) {
       const int r = i / CPR, c = i % CPR;
       uint4 pz = make_uint4(0, 0, 0, 0), pd = make_uint4(0, 0, 0, 0);
+      float l2 = INFINITY, dl = 0.f, el = 0.f;
       if (r < M) {
-        const float el = ex2(a.lse_m[lrow + r] * kLog2e - mu);
+        l2 = a.lse_m[lrow + r] * kLog2e;
+        el = ex2(l2 - mu);
         const float4 z0 = *reinterpret_cast<const float4*>(zb + r * D + c * 8);
         const float4 z1 = *reinterpret_cast<const float4*>(zb + r * D + c * 8 + 4);
         const float4 d0 = *reinterpret_cast<const float4*>(dzb + r * D + c * 8);
@@ -185,31 +190,34 @@ k_tc_bwd_fast(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         pz = make_uint4(pack_bf16(z0.x * el, z0.y * el), pack_bf16(z0.z * el, z0.w * el),
                         pack_bf16(z1.x * el, z1.y * el), pack_bf16(z1.z * el, z1.w * el));
         pd = make_uint4(pack_bf16(d0.x, d0.y), pack_bf16(d0.z, d0.w), pack_bf16(d1.x, d1.y), pack_bf16(d1.z, d1.w));
-      }
-      *reinterpret_cast<uint4*>(sZe + swz_off<ROWB>(r, c)) = pz;
-      *reinterpret_cast<uint4*>(sDZ + swz_off<ROWB>(r, c)) = pd;
-    }
-    if (tid < 256) {
-      const int m = tid;
-      float l2 = INFINITY, dl = 0.f, el = 0.f;
-      if (m < M) {
         // Delta_m from dZ as the tensor core sees it (rounded to bf16): sum_n P_mn (V_n . dZ_m) then cancels
         // against it exactly instead of leaving a rounding residue of one sign along the row
-        for (int i = 0; i < D; ++i) dl = fmaf(__bfloat162float(__float2bfloat16_rn(dzb[m * D + i])), zb[m * D + i], dl);
-        l2 = a.lse_m[lrow + m] * kLog2e;
-        el = ex2(l2 - mu);
-      }
-      sL2[m] = l2;
-      __nv_bfloat16 e[16];
+        const float zf[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+        const uint32_t dw[4] = {pd.x, pd.y, pd.z, pd.w};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) e[i] = __float2bfloat16_rn(0.f);
-      __nv_bfloat16 dh, dlw, eh, elw;
-      split_bf16_4(-dl, dh, dlw);
-      split_bf16_4(-el, eh, elw);
-      e[0] = dh; e[1] = dlw; e[2] = eh; e[3] = elw; e[4] = eh;
-      const uint4* src = reinterpret_cast<const uint4*>(e);
-      *reinterpret_cast<uint4*>(sXB + swz_off<32>(m, 0)) = src[0];
-      *reinterpret_cast<uint4*>(sXB + swz_off<32>(m, 1)) = src[1];
+        for (int j = 0; j < 4; ++j) {
+          const float2 df = Op16<__nv_bfloat16>::unpack(dw[j]);
+          dl = fmaf(df.x, zf[2 * j], dl);
+          dl = fmaf(df.y, zf[2 * j + 1], dl);
+        }
+      }
+      dl += __shfl_xor_sync(0xffffffffu, dl, 1);
+      dl += __shfl_xor_sync(0xffffffffu, dl, 2);
+      *reinterpret_cast<uint4*>(sZe + swz_off<ROWB>(r, c)) = pz;
+      *reinterpret_cast<uint4*>(sDZ + swz_off<ROWB>(r, c)) = pd;
+      if (c == 0) {
+        sL2[r] = l2;
+        __nv_bfloat16 e[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) e[j] = __float2bfloat16_rn(0.f);
+        __nv_bfloat16 dh, dlw, eh, elw;
+        split_bf16_4(-dl, dh, dlw);
+        split_bf16_4(-el, eh, elw);
+        e[0] = dh; e[1] = dlw; e[2] = eh; e[3] = elw; e[4] = eh;
+        const uint4* src = reinterpret_cast<const uint4*>(e);
+        *reinterpret_cast<uint4*>(sXB + swz_off<32>(r, 0)) = src[0];
+        *reinterpret_cast<uint4*>(sXB + swz_off<32>(r, 1)) = src[1];
+      }
     }
   }
 

@@ -114,6 +114,15 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
   const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   constexpr uint32_t kY = 64;                      // Y columns inside a buffer
 
+  // Q and the first K tiles are on their way while Z is converted
+  if (tid == 0) {
+    mbar_expect_tx(bar_q, (uint32_t)M * ROWB);
+    tma_load_4d(sQ, &tmQ, bar_q, 0, 0, h, a.q_batched ? b : 0);
+    for (int t = 0; t < 3 && t < T; ++t) {
+      mbar_expect_tx(&bar_full[t], L::kK);
+      tma_load_4d(sK + t * L::kK, &tmK, &bar_full[t], 0, n0 + t * 128, h, b);
+    }
+  }
   // Z of this (b, h) as bf16 in the swizzled operand layout (rows past M are never read)
   {
     const float* zb = a.z32 + ((long long)b * a.H + h) * a.z_bh_stride;
@@ -158,14 +167,6 @@ k_tc_scatter2(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ C
         }
         __syncwarp();
       };
-      if (elect_one()) {
-        mbar_expect_tx(bar_q, (uint32_t)M * ROWB);
-        tma_load_4d(sQ, &tmQ, bar_q, 0, 0, h, a.q_batched ? b : 0);
-        load_tile(0);
-        if (T > 1) load_tile(1);
-        if (T > 2) load_tile(2);
-      }
-      __syncwarp();
       mbar_wait(bar_q, 0, a.status, abort_flag);
       issue_s(0);
       if (T > 1) issue_s(1);
