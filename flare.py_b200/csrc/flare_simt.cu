@@ -425,10 +425,11 @@ struct PartsPtrs {
   __device__ __forceinline__ const float* at(int p) const { return ptrs[p]; }
 };
 
-// One warp per latent row.  The statistics (m_p, l_p) are read with one load per lane (parts spread over
-// the lanes, reduced by shuffles), the accumulators with lane = d and several parts' loads in flight: the
-// kernel's time is the latency of its dependent loads, not their volume.  The order of every sum is fixed
-// (shuffle tree over the lanes, then ascending parts), so equal inputs give equal bits on every rank.
+// One warp per latent row.  Parts are taken 32 at a time: lane p holds the statistics (m_p, l_p) of its part and
+// the weight e^{m_p - max}, which the accumulation over d (lane = d) fetches by shuffle while eight parts'
+// accumulator rows are in flight.  The kernel's time is the latency of its dependent loads, not their volume:
+// three rounds of loads instead of one per part.  The order of every sum is fixed (shuffle tree over the
+// lanes, then ascending parts), so equal inputs give equal bits on every rank.
 template <typename Parts>
 __global__ void __launch_bounds__(kThreads)
 k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
@@ -447,42 +448,48 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float lt = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};             // d = lane, lane + 32, ... (D <= 128)
   for (int p0 = 0; p0 < n_parts; p0 += 32) {
     const int p = p0 + lane;
-    float t = 0.f;
+    float w = 0.f, wl = 0.f;
     if (p < n_parts) {
       const float m = parts.at(p)[row * W + D];
-      const float w = (m == -INFINITY) ? 0.f : expf(m - mx);
-      t = w * parts.at(p)[row * W + D + 1];
+      w = (m == -INFINITY) ? 0.f : expf(m - mx);
+      wl = w * parts.at(p)[row * W + D + 1];
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    lt += t;
+    for (int o = 16; o > 0; o >>= 1) wl += __shfl_xor_sync(0xffffffffu, wl, o);
+    lt += wl;
+    const int cnt = min(32, n_parts - p0);
+    for (int j0 = 0; j0 < cnt; j0 += 8) {
+      float av[8][4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float* src = parts.at(p0 + min(j0 + j, cnt - 1)) + row * W;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) av[j][i] = (j0 + j < cnt && lane + 32 * i < D) ? src[lane + 32 * i] : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, w, (j0 + j) & 31);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = fmaf(wj, av[j][i], acc[i]);
+      }
+    }
   }
   const float inv = 1.f / lt;
-  for (int d = lane; d < D; d += 32) {
-    float a = 0.f;
-    for (int p0 = 0; p0 < n_parts; p0 += 8) {
-      float mv[8], av[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const bool in = p0 + j < n_parts;
-        mv[j] = in ? parts.at(p0 + j)[row * W + D] : -INFINITY;
-        av[j] = in ? parts.at(p0 + j)[row * W + d] : 0.f;
+  for (int i = 0; i < 4; ++i) {
+    const int d = lane + 32 * i;
+    if (d < D) {
+      if (rec_out) rec_out[row * W + d] = acc[i];
+      const float z = acc[i] * inv;
+      if (z32) z32[row * D + d] = z;
+      if (z_out) {
+        if (dtype == FLARE_F32) reinterpret_cast<float*>(z_out)[row * D + d] = z;
+        else if (dtype == FLARE_F16) reinterpret_cast<__half*>(z_out)[row * D + d] = __float2half_rn(z);
+        else reinterpret_cast<__nv_bfloat16*>(z_out)[row * D + d] = __float2bfloat16_rn(z);
       }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float w = (mv[j] == -INFINITY) ? 0.f : expf(mv[j] - mx);
-        a = fmaf(w, av[j], a);
-      }
-    }
-    if (rec_out) rec_out[row * W + d] = a;
-    const float z = a * inv;
-    if (z32) z32[row * D + d] = z;
-    if (z_out) {
-      if (dtype == FLARE_F32) reinterpret_cast<float*>(z_out)[row * D + d] = z;
-      else if (dtype == FLARE_F16) reinterpret_cast<__half*>(z_out)[row * D + d] = __float2half_rn(z);
-      else reinterpret_cast<__nv_bfloat16*>(z_out)[row * D + d] = __float2bfloat16_rn(z);
     }
   }
   if (lane == 0) {
