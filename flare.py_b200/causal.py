@@ -1,8 +1,10 @@
 """Causal FLARE: prefill over a whole sequence and recurrent decode on a per-(b, h) state.
 
-The reference links this path (README.md:60) without shipping code; the semantics are those of
-figs/flare_decoder.py:211-250.  ``y_t = softmax_M(S[:, t]) . z_t`` with
-``z_t = softmax_{n <= t}(S) v`` and ``S = scale * q k^T``.  The state is one record per latent,
+The reference links this path (README.md:60) without shipping code, a formula or a test vector (its
+figs/flare_decoder.py only animates a decoder diagram), so the definition is this library's own choice:
+``y_t = softmax_M(S[:, t]) . z_t`` with ``z_t = softmax_{n <= t}(S) v`` and ``S = scale * q k^T`` -- token t
+sees the latent summary of tokens 0..t inclusive, the natural reading of "causal" for the gather and the one
+under which decoding token by token reproduces the prefill.  The state is one record per latent,
 ``[B, H, M, D + 2] = (acc[D], m, l)`` in fp32, the same record the non-causal gather writes per token
 range; ``causal_state_init`` gives the empty one.  ``flare_causal_mixer`` is the differentiable form for
 training (a whole sequence from an empty prefix); prefill with a carried state and decode are forward only.

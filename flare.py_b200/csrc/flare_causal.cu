@@ -1,8 +1,10 @@
 // Causal FLARE: y_t = softmax_M(S[:, t]) . z_t with z_t = softmax_{n <= t}(S) v   (S = scale q k^T).
 //
-// The reference ships no code for this path, only its semantics (figs/flare_decoder.py:211-250: a
-// per-(b, h) state (m[M], l[M], acc[M, D]) updated with each (k_t, v_t)).  Here the state is the same
-// split-N record the non-causal gather produces, so prefill is three passes:
+// The reference links this path without code, formula or test vector (figs/flare_decoder.py animates a
+// decoder diagram, nothing more), so the definition above is this library's own choice: token t sees the
+// latent summary of tokens 0..t inclusive, which makes token-by-token decoding on a per-(b, h) state
+// (m[M], l[M], acc[M, D]) reproduce the prefill.  The state is the same split-N record the non-causal
+// gather produces, so prefill is three passes:
 //
 //   1. flare_gather_partial with 128-token ranges: one record per chunk           (existing kernels)
 //   2. k_causal_scan: exclusive log-sum-exp prefix of the records along the chunk axis, in place;

@@ -234,7 +234,9 @@ int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, co
                          flare_stream_t stream);
 
 /* Causal FLARE: y_t = softmax_M(S[:,t]) . z_t with z_t = softmax_{n<=t}(S) v.  The reference links
- * this path (README.md:60) but ships no code for it; the semantics follow figs/flare_decoder.py:211-250.
+ * this path (README.md:60) but ships no code, formula or test vector for it (figs/flare_decoder.py only
+ * animates a diagram): the definition -- token t sees tokens 0..t inclusive -- is this library's choice,
+ * checked for self-consistency only (dense == recurrent == chunked forms; prefill == token-by-token decode).
  * The state is one gather record per (b, h): float [B,H,M,D+2] = (acc[D], m, l) per latent, the same
  * record flare_gather_partial writes; start from acc = 0, m = -inf, l = 0.
  *   flare_causal_prefill: all N tokens at once.  workspace: flare_causal_workspace_bytes(p) bytes.

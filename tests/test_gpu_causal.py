@@ -192,3 +192,52 @@ def test_backward_refuses_what_it_cannot_hold(cuda_dev):
     y = fb.flare_causal_mixer(qd, kd, vd, 1.0)
     with pytest.raises(RuntimeError, match="causal_bwd"):
         y.backward(dy.to(cuda_dev))
+
+
+# ---------------------------------------------------------------------------------------------------------
+# the call-site variants of the reference's FLARE modules on the serving path
+# ---------------------------------------------------------------------------------------------------------
+def test_decode_with_shared_latents_and_normalised_q_k(cuda_dev):
+    """`shared_latents` (one latent set expand()-ed over the heads: stride 0) and `qk_norm` (q, k normalised
+    by the caller before the mixer; pdebench/models/flare.py:130-132) on prefill + decode: the broadcast view is
+    accepted as it is, and what comes out equals the oracle on the materialised, normalised tensors."""
+    import flare_b200 as fb
+    import torch.nn.functional as F
+    B, H, N, M, D = 2, 4, 150, 32, 32
+    g = torch.Generator().manual_seed(31)
+    q1 = torch.randn(1, M, D, generator=g)
+    k = torch.randn(B, H, N, D, generator=g)
+    v = torch.randn(B, H, N, D, generator=g)
+    qn = F.normalize(q1, dim=-1).expand(H, M, D)            # stride 0 over the heads
+    kn = F.normalize(k, dim=-1)
+    assert qn.stride(0) == 0
+    scale = 4.0                                             # unit vectors: a sharper softmax than scale 1
+    qd, kd, vd = qn.to(cuda_dev), kn.to(cuda_dev), v.to(cuda_dev)
+    qd = qd[:1].expand(H, M, D)                             # (.to() materialises; make the device view broadcast again)
+    n0 = 128
+    y0, st = fb.flare_causal_prefill(qd, kd[:, :, :n0], vd[:, :, :n0], scale)
+    ys = [y0] + [fb.flare_causal_decode(qd, kd[:, :, t:t + 1], vd[:, :, t:t + 1], st, scale) for t in range(n0, N)]
+    y = torch.cat(ys, dim=2)
+    y_ref, _ = O.causal_recurrent(qn.contiguous().double(), kn.double(), v.double(), scale)
+    assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-5
+
+
+def test_training_step_with_shared_latents(cuda_dev):
+    """flare_causal_mixer with the latents expand()-ed over the heads: autograd folds the per-head gradients
+    back onto the single latent set, equal to autograd through the dense definition."""
+    import flare_b200 as fb
+    B, H, N, M, D = 1, 3, 100, 16, 16
+    g = torch.Generator().manual_seed(32)
+    q1 = (torch.randn(1, M, D, generator=g) * 0.5)
+    k = torch.randn(B, H, N, D, generator=g) * 0.5
+    v = torch.randn(B, H, N, D, generator=g)
+    dy = torch.randn(B, H, N, D, generator=g)
+    qd = q1.to(cuda_dev).requires_grad_(True)
+    kd, vd = k.to(cuda_dev).requires_grad_(True), v.to(cuda_dev).requires_grad_(True)
+    fb.flare_causal_mixer(qd.expand(H, M, D), kd, vd, 1.0).backward(dy.to(cuda_dev))
+    qr = q1.double().requires_grad_(True)
+    kr, vr = k.double().requires_grad_(True), v.double().requires_grad_(True)
+    O.causal_dense(qr.expand(H, M, D), kr, vr, 1.0).backward(dy.double())
+    assert O.rel_l2(qd.grad.double().cpu(), qr.grad) <= 1e-4
+    assert O.rel_l2(kd.grad.double().cpu(), kr.grad) <= 1e-4
+    assert O.rel_l2(vd.grad.double().cpu(), vr.grad) <= 1e-4
