@@ -243,7 +243,9 @@ extern "C" {
 size_t flare_triple_workspace_bytes(int BH, int N, int Da, int Db, int Dc) {
   if (BH < 1 || N < 1) return 0;
   const int pb = (Db * Dc + kPairs - 1) / kPairs;
-  return (size_t)pick_splits(BH, N, pb) * BH * Da * Db * Dc * sizeof(float) + 256;
+  const size_t simt = (size_t)pick_splits(BH, N, pb) * BH * Da * Db * Dc * sizeof(float) + 256;
+  const size_t tc = triple_tc_outer_workspace(BH, N);                // dtype is not known here: room for either path
+  return simt > tc ? simt : tc;
 }
 
 int flare_triple_outer(int BH, int N, int Da, int Db, int Dc, int dtype, const void* a, const void* b, const void* c,
@@ -252,6 +254,13 @@ int flare_triple_outer(int BH, int N, int Da, int Db, int Dc, int dtype, const v
   if (!dim_ok(Da) || !dim_ok(Db) || !dim_ok(Dc)) return refuse(FLARE_EUNSUPPORTED, "triple_outer: dims %d,%d,%d must be multiples of 4 up to 64", Da, Db, Dc);
   if (!a || !b || !c || !out || !workspace) return refuse(FLARE_EINVAL, "triple_outer: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (triple_tc_supported(N, Da, Db, Dc, dtype)) {
+    const int rc = triple_tc_outer(BH, N, dtype, a, b, c, alpha, out, workspace, st);
+    if (rc != FLARE_OK) return refuse(rc, "triple_outer (tcgen05): launch setup failed");
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return refuse(FLARE_ECUDA, "triple_outer: %s", cudaGetErrorString(e));
+    return FLARE_OK;
+  }
   switch (dtype) {
     case FLARE_F32: return run_outer<float>(BH, N, Da, Db, Dc, a, b, c, alpha, out, workspace, st);
     case FLARE_F16: return run_outer<__half>(BH, N, Da, Db, Dc, a, b, c, alpha, out, workspace, st);
@@ -266,6 +275,13 @@ int flare_triple_contract(int BH, int N, int Dx, int Dy, int Dz, int dtype, cons
   if (!dim_ok(Dx) || !dim_ok(Dy) || !dim_ok(Dz)) return refuse(FLARE_EUNSUPPORTED, "triple_contract: dims %d,%d,%d must be multiples of 4 up to 64", Dx, Dy, Dz);
   if (!t || !a || !b || !out) return refuse(FLARE_EINVAL, "triple_contract: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (triple_tc_supported(N, Dx, Dy, Dz, dtype) && triple_tc_strides_ok(sx, sy, sz)) {
+    const int rc = triple_tc_contract(BH, N, dtype, t, sx, sy, sz, a, b, alpha, out, st);
+    if (rc != FLARE_OK) return refuse(rc, "triple_contract (tcgen05): launch setup failed");
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return refuse(FLARE_ECUDA, "triple_contract: %s", cudaGetErrorString(e));
+    return FLARE_OK;
+  }
   switch (dtype) {
     case FLARE_F32: return run_contract<float>(BH, N, Dx, Dy, Dz, t, sx, sy, sz, a, b, alpha, out, st);
     case FLARE_F16: return run_contract<__half>(BH, N, Dx, Dy, Dz, t, sx, sy, sz, a, b, alpha, out, st);

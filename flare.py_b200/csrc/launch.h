@@ -71,4 +71,13 @@ int* tc_status_ptr();
 int num_sms();
 int tc_set_dyn_smem(const void* kernel, int bytes);
 
+// Triple attention on the tensor cores (flare_triple_tc.cu): 16-bit inputs, every feature dimension 32.
+bool triple_tc_supported(int N, int D0, int D1, int D2, int dtype);
+bool triple_tc_strides_ok(long long sx, long long sy, long long sz);
+size_t triple_tc_outer_workspace(int BH, int N);
+int triple_tc_outer(int BH, int N, int dtype, const void* a, const void* b, const void* c, float alpha, float* out,
+                    float* ws, cudaStream_t st);
+int triple_tc_contract(int BH, int N, int dtype, const float* t, long long sx, long long sy, long long sz, const void* a,
+                       const void* b, float alpha, void* out, cudaStream_t st);
+
 }  // namespace flare
