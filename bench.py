@@ -609,6 +609,54 @@ def run_causal(args):
           flush=True)
 
 
+def run_triple(args):
+    """Secondary workload (not the headline line): triple attention forward and forward + backward at the
+    reference benchmark's shape (lra/models/triton/triple.py:936-1060: B=1, H=8, D=32, fp16), device-resident."""
+    import flare_b200 as fb
+    dev = torch.device("cuda:0")
+    B, H, D = 1, 8, 32
+    N = args.tokens or 500_000
+    g = torch.Generator().manual_seed(0)
+    mk = lambda s: (torch.randn(B, H, N, D, generator=g) * s).half().to(dev).requires_grad_(True)
+    q1, q2, k1, k2 = (mk(D ** -0.5) for _ in range(4))
+    v = mk(1.0)
+    do = torch.randn(B, H, N, D, generator=g).half().to(dev)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def fwd():
+        with torch.no_grad():
+            return fb.triple_attention(q1, q2, k1, k2, v)
+
+    def fwd_bwd():
+        for t in (q1, q2, k1, k2, v):
+            t.grad = None
+        fb.triple_attention(q1, q2, k1, k2, v)[1].backward(do)
+
+    for _ in range(max(args.warmup, 2)):
+        fwd_bwd()
+    ms_f, ms_fb = timed(fwd, args.steps), timed(fwd_bwd, args.steps)
+    # every launch is one product over the 1024-long pair axis: 2 * 1024 * D flops per token and head;
+    # forward = 2 launches (STATE, O), backward = 6 (dSTATE, dQ1, dQ2, dK1, dK2, dV)
+    pk = peaks()
+    per_launch = 2.0 * D * D * D * N * B * H
+    roof = dict(bound="tensor", achieved=8 * per_launch / (ms_fb * 1e-3) / 1e12, peak=pk["bf16_tflops"], unit="TFLOP/s",
+                frac=8 * per_launch / (ms_fb * 1e-3) / 1e12 / pk["bf16_tflops"], traffic=None, peaks_source=pk["source"],
+                kernel="k_triple_tc_outer / k_triple_tc_contract")
+    print(json.dumps(dict(metric="triple attention fwd+bwd Mtokens/s", value=B * N / ms_fb / 1e3, unit="Mtokens/s",
+                          n_gpus=1, steps=args.steps, warmup=max(args.warmup, 2), ms_per_step=ms_fb, fwd_ms=ms_f,
+                          higher_is_better=True, dtype="f16", data="synthetic", roofline=roof,
+                          config=dict(workload=f"triple: B={B} H={H} N={N} D={D} fp16"))), flush=True)
+
+
 def run_sdpa_gpu(args):
     """Secondary line (not the headline): the kernels the reference dispatches for this path on this GPU, i.e.
     its two F.scaled_dot_product_attention calls (README.md:49-50) and their autograd in bf16 through the
@@ -737,12 +785,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained leg")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "sdpa_gpu", "cp_encoder"],
-                    help="mixer: the headline line; causal: a secondary line for causal prefill/decode; sdpa_gpu: "
+    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "triple", "sdpa_gpu", "cp_encoder"],
+                    help="mixer: the headline line; causal: a secondary line for causal prefill/decode/training; triple: a "
+                         "secondary line for triple attention; sdpa_gpu: "
                          "a secondary line timing the reference's own two SDPA calls + autograd on this GPU")
     args = ap.parse_args()
     if args.workload == "causal":
         run_causal(args)
+    elif args.workload == "triple":
+        run_triple(args)
     elif args.workload == "sdpa_gpu":
         run_sdpa_gpu(args)
     elif args.workload == "cp_encoder":

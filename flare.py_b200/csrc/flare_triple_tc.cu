@@ -10,13 +10,14 @@
 //             128-token x 128-pair tile of P is the MN-major A operand (M = pairs, contraction = tokens),
 //             the token tile of b the MN-major B operand; eight accumulators of 32 columns in tensor memory
 //   contract  out[n,x] = alpha sum_{y,z} T[x,y,z] a[n,y] b[n,z]
-//             = (P T')[n, x]  with P[n,(y,z)] = a[n,y] b[n,z], T'[(y,z), x]:  the same tile of P read as a
-//             K-major A operand (M = tokens, contraction = pairs), T' resident in shared memory as 16-bit
+//             = (P T')[n, x]  with P[n,(y,z)] = a[n,y] b[n,z], T'[(y,z), x]:  here the rows of P are the
+//             tokens, so its tiles go straight into tensor memory (each thread packs the pairs of its own
+//             token row) and are the A operand from there; T' is resident in shared memory as 16-bit
 //             (scaled per (b,h) by a power of two so that fp16 cannot overflow)
 //
 // Eight producer warps build the tiles of P (one token row and half of the w features per thread: 4 packed
-// multiplies and one 16-byte swizzled store per eight pairs) into two buffers; one warp issues the products
-// (tcgen05.mma, fp32 accumulation) and recycles the buffers through mbarriers.  Every wait is bounded.
+// multiplies per eight pairs) into four buffers; one warp issues the products (tcgen05.mma, fp32
+// accumulation) and recycles the buffers through mbarriers.  Every wait is bounded.
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -79,6 +80,27 @@ __device__ __forceinline__ void build_pairs(uint8_t* dst, int n, int hk, int blk
       }
       *reinterpret_cast<uint4*>(half + swz_off<128>(n, 4 * (il & 1) + 2 * hk + cc)) = make_uint4(o[0], o[1], o[2], o[3]);
     }
+  }
+}
+
+// The same tile as the K-major A operand of a product whose rows are the tokens: thread (token row = its
+// tensor-memory lane, hk) writes its 16 pairs of every il as eight packed words at columns 16 il + 8 hk of
+// the 64-column tile -- no shared memory on the way, and the product reads A at twice the rate.
+template <typename T16>
+__device__ __forceinline__ void build_pairs_tmem(uint32_t tile, int hk, int blk, const uint32_t (&uw)[16],
+                                                 const uint32_t (&ww)[8]) {
+  using V2 = typename Pair16<T16>::V2;
+#pragma unroll
+  for (int il = 0; il < 4; ++il) {
+    const int i = 4 * blk + il;
+    const V2 ui = Pair16<T16>::splat(uw[i >> 1], i & 1);
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const V2 p = __hmul2(ui, *reinterpret_cast<const V2*>(&ww[j]));
+      o[j] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    tmem_st8(tile + 16 * il + 8 * hk, o);
   }
 }
 
@@ -243,8 +265,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
                      const T16* __restrict__ Bm, int N, int chunk, float alpha, T16* __restrict__ O, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sP = smem;                              // [kNP] tiles of P
-  uint8_t* sT = sP + kNP * kPBytes;                // T' [(y,z)][x], 16-bit, 64-byte swizzled rows
+  uint8_t* sT = smem;                              // T' [(y,z)][x], 16-bit, 64-byte swizzled rows
   TripleBars* bars = reinterpret_cast<TripleBars*>(sT + kTBytes);
   float* sRed = reinterpret_cast<float*>(bars + 1);                // [kThreadsT / 32] warp maxima
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -258,7 +279,8 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
     bars->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 0) tmem_alloc<64>(&bars->tmem_slot);
+  // tensor memory: kNP tiles of P (64 columns each: 128 pairs, 16-bit), then the two accumulators
+  if (warp == 0) tmem_alloc<512>(&bars->tmem_slot);
   // T of this (b, h): largest magnitude, then 16-bit copies scaled into [1, 2) at the top
   const float* tb = Tm + (long long)bh * (kTD * kTD * kTD);
   float mx = 0.f;
@@ -296,6 +318,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
   T16* o = O + (long long)bh * N * kTD;
   constexpr int F = Op16<T16>::kFmt;
   const float oscale = alpha * tinv;
+  constexpr uint32_t kAcc = 64 * kNP;
 
   if (warp < kProd / 32) {
     // ================= producers; they also write out the finished tile =================
@@ -306,7 +329,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
       mbar_wait(&bars->acc_full[par], (uint32_t)(t >> 1) & 1, status, abort_flag);
       tc_fence_after();
       uint32_t r[16];
-      tmem_ld16(lane_base + 32 * par + 16 * hk, r);
+      tmem_ld16(lane_base + kAcc + 32 * par + 16 * hk, r);
       tmem_wait_ld();
       tc_fence_before();
       arrive(&bars->acc_free[par]);
@@ -340,8 +363,9 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
       for (int blk = 0; blk < 8; ++blk) {
         const int g = 8 * t + blk, buf = g % kNP;
         if (g >= kNP) mbar_wait_hot(&bars->empty[buf], (uint32_t)(g / kNP - 1) & 1, status, abort_flag);
-        build_pairs<T16>(sP + buf * kPBytes, n, hk, blk, uw, ww);
-        fence_proxy_async();
+        build_pairs_tmem<T16>(lane_base + 64 * buf, hk, blk, uw, ww);
+        tmem_wait_st();
+        tc_fence_before();
         arrive(&bars->full[buf]);
       }
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
@@ -350,8 +374,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
     if (!*reinterpret_cast<volatile int*>(abort_flag)) write_tile(T - 1);
   } else {
     // ================= issuing warp =================
-    const uint32_t idesc = idesc_f16(128, kTD, F, F, 0, 1);          // A (tokens x pairs) K-major, B (pairs x x) MN-major
-    const uint64_t pdesc = smem_desc<128>(smem_u32(sP));
+    const uint32_t idesc = idesc_f16(128, kTD, F, F, 0, 1);          // A (tokens x pairs) in tensor memory, B (pairs x x) MN-major
     const uint64_t tdesc = smem_desc<64>(smem_u32(sT));
     for (int t = 0; t < T; ++t) {
       const int par = t & 1;
@@ -362,10 +385,9 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint64_t pa = pdesc + (uint64_t)(buf * (kPBytes >> 4) + (kk >> 2) * ((128 * 128) >> 4) + 2 * (kk & 3));
-            mma_ss(tmem + 32 * par, pa, tdesc + (uint64_t)(64 * (8 * blk + kk)), idesc, (blk > 0) || (kk > 0));
-          }
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ts(tmem + kAcc + 32 * par, tmem + 64 * buf + 8 * kk, tdesc + (uint64_t)(64 * (8 * blk + kk)), idesc,
+                   (blk > 0) || (kk > 0));
           mma_commit(&bars->empty[buf]);
           if (blk == 7) mma_commit(&bars->acc_full[par]);
         }
@@ -377,7 +399,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<64>(tmem);
+  if (warp == 0) tmem_dealloc<512>(tmem);
 }
 
 int splits_for(int BH, int N) {
@@ -426,7 +448,7 @@ static int contract_launch(int BH, int N, const float* t, long long sx, long lon
   const int S = splits_for(BH, N);
   const int chunk = ((N + S - 1) / S + 127) / 128 * 128;
   const int S2 = (N + chunk - 1) / chunk;
-  constexpr int smem = kNP * kPBytes + kTBytes + 1024 + 512;
+  constexpr int smem = kTBytes + 1024 + 512;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_triple_tc_contract<T16>), smem) != FLARE_OK) return FLARE_ECUDA;
   k_triple_tc_contract<T16><<<dim3((unsigned)S2, (unsigned)BH), kThreadsT, smem, st>>>(
       t, sx, sy, sz, reinterpret_cast<const T16*>(a), reinterpret_cast<const T16*>(b), N, chunk, alpha,
