@@ -241,3 +241,38 @@ def test_training_step_with_shared_latents(cuda_dev):
     assert O.rel_l2(qd.grad.double().cpu(), qr.grad) <= 1e-4
     assert O.rel_l2(kd.grad.double().cpu(), kr.grad) <= 1e-4
     assert O.rel_l2(vd.grad.double().cpu(), vr.grad) <= 1e-4
+
+
+def test_decode_step_replays_from_a_cuda_graph(cuda_dev):
+    """The serving loop: one decode step recorded in a CUDA graph over static k_t, v_t, y_t buffers and the
+    state record, replayed once per token (the state lives in one fp32 tensor updated in place, so the
+    recorded launch needs nothing new per step).  Equals the prefill over the same tokens."""
+    import flare_b200 as fb
+    B, H, N, M, D = 2, 4, 96, 64, 32
+    q, k, v = _inputs(B, H, N, M, D, torch.bfloat16, seed=41)
+    qd, kd, vd = q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)
+    n0 = 32
+    _, st = fb.flare_causal_prefill(qd, kd[:, :, :n0], vd[:, :, :n0], 1.0)
+    k_t = torch.empty(B, H, 1, D, dtype=torch.bfloat16, device=cuda_dev)
+    v_t = torch.empty_like(k_t)
+    k_t.copy_(kd[:, :, n0:n0 + 1]); v_t.copy_(vd[:, :, n0:n0 + 1])
+    side = torch.cuda.Stream(device=cuda_dev)
+    side.wait_stream(torch.cuda.current_stream(cuda_dev))
+    st_warm = st.clone()
+    with torch.cuda.stream(side):
+        fb.flare_causal_decode(qd, k_t, v_t, st_warm, 1.0)          # warm-up outside the recording
+    torch.cuda.current_stream(cuda_dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_t = fb.flare_causal_decode(qd, k_t, v_t, st, 1.0)
+    ys = []
+    for t in range(n0, N):
+        k_t.copy_(kd[:, :, t:t + 1]); v_t.copy_(vd[:, :, t:t + 1])
+        graph.replay()
+        ys.append(y_t.clone())
+    torch.cuda.synchronize()
+    y_all, st_all = fb.flare_causal_prefill(qd, kd, vd, 1.0)
+    assert O.rel_l2(torch.cat(ys, dim=2).float().cpu(), y_all[:, :, n0:].float().cpu()) <= 2e-2
+    z = lambda s: (s[..., :D] / s[..., D + 1:D + 2]).cpu()
+    assert O.rel_l2(z(st), z(st_all)) <= 2e-2          # (the prefill state comes from the bf16 tensor-core gather)
+    assert fb.device_status() == 0
