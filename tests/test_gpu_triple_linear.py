@@ -67,6 +67,37 @@ def test_triple_state_gradient(cuda_dev):
         assert O.rel_l2(t.grad.double().cpu(), r.grad) <= 1e-5
 
 
+@pytest.mark.parametrize("B,H,N,dtype", [
+    (3, 5, 1000, torch.bfloat16),             # ragged N: a last tile of 104 tokens, 15 (b, h)
+    (1, 2, 129, torch.float16),               # one full tile and one token
+    (2, 80, 300, torch.float16),              # more (b, h) than SMs: one token range each
+])
+def test_triple_tensor_core_shapes(cuda_dev, B, H, N, dtype):
+    """16-bit inputs with every feature dimension 32 run on the tensor-core kernels (the pair-axis operand
+    built on the fly): ragged token counts, a loss on both outputs so that dSTATE carries an upstream term,
+    inputs large enough that the rank-3 tensors leave fp16's comfortable range without the per-(b, h) scaling."""
+    import flare_b200 as fb
+    D = 32
+    q1, q2, k1, k2 = (_rand((B, H, N, D), dtype, 10 + i, 0.5) for i in range(4))
+    v = _rand((B, H, N, D), dtype, 14, 4.0)
+    do = _rand((B, H, N, D), dtype, 15, 8.0)
+    w = _rand((B, H, D, D, D), torch.float32, 16)
+    ref_in = [t.double().requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    st_ref = torch.einsum("bhni,bhnj,bhnk->bhijk", ref_in[2], ref_in[4], ref_in[3]) / N
+    o_ref = torch.einsum("bhni,bhijk,bhnk->bhnj", ref_in[0], st_ref, ref_in[1])
+    ((st_ref * w.double()).sum() + (o_ref * do.double()).sum()).backward()
+    ins = [t.to(cuda_dev).requires_grad_(True) for t in (q1, q2, k1, k2, v)]
+    state, o = fb.triple_attention(*ins)
+    ((state * w.to(cuda_dev)).sum() + (o.float() * do.to(cuda_dev).float()).sum()).backward()
+    tol = TOL[dtype]
+    assert fb.device_status() == 0
+    assert O.rel_l2(state.double().cpu(), st_ref.detach()) <= tol
+    assert O.rel_l2(o.double().cpu(), o_ref.detach()) <= tol
+    for name, t, r in zip(("dq1", "dq2", "dk1", "dk2", "dv"), ins, ref_in):
+        assert torch.isfinite(t.grad).all(), name
+        assert O.rel_l2(t.grad.double().cpu(), r.grad) <= tol, name
+
+
 def test_causal_linear_golden(cuda_dev):
     import flare_b200 as fb
     g = load_golden("causal_linear_ref")
