@@ -259,7 +259,9 @@ class GraphedStep:
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        # thread-local capture mode: another thread of the process (a communicator's watchdog polling its events)
+        # may make CUDA calls while this thread records
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
             step_fn()
             self.result = step_fn()
         self.steps_per_replay = 2
