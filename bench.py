@@ -204,6 +204,10 @@ def time_passes(fb, q, k, v, dy, iters=3):
     for it in range(iters + 1):
         for name, fn in calls:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            # the GPU is kept busy for ~0.25 ms while the host enqueues the events and the call, so that the
+            # interval between the events is device time only (a call's host side -- tensor maps, several
+            # launches -- takes tens of microseconds, more than the small kernels run)
+            torch.cuda._sleep(500_000)
             e0.record()
             _cabi.check(fn(), name)
             e1.record()
