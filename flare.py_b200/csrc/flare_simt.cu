@@ -426,7 +426,7 @@ struct PartsPtrs {
 };
 
 // One warp per latent row.  Parts are taken 32 at a time: lane p holds the statistics (m_p, l_p) of its part and
-// the weight e^{m_p - max}, which the accumulation over d (lane = d) fetches by shuffle while eight parts'
+// the weight e^{m_p - max}, which the accumulation over d (lane = d) fetches by shuffle while sixteen parts'
 // accumulator rows are in flight.  The kernel's time is the latency of its dependent loads, not their volume:
 // three rounds of loads instead of one per part.  The order of every sum is fixed (shuffle tree over the
 // lanes, then ascending parts), so equal inputs give equal bits on every rank.
@@ -461,16 +461,16 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
     for (int o = 16; o > 0; o >>= 1) wl += __shfl_xor_sync(0xffffffffu, wl, o);
     lt += wl;
     const int cnt = min(32, n_parts - p0);
-    for (int j0 = 0; j0 < cnt; j0 += 8) {
-      float av[8][4];
+    for (int j0 = 0; j0 < cnt; j0 += 16) {
+      float av[16][4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         const float* src = parts.at(p0 + min(j0 + j, cnt - 1)) + row * W;
 #pragma unroll
         for (int i = 0; i < 4; ++i) av[j][i] = (j0 + j < cnt && lane + 32 * i < D) ? src[lane + 32 * i] : 0.f;
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         const float wj = __shfl_sync(0xffffffffu, w, (j0 + j) & 31);
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[i] = fmaf(wj, av[j][i], acc[i]);
@@ -498,22 +498,29 @@ k_combine(Parts parts, int n_parts, long long rows, int D, int dtype,
   }
 }
 
-// out[i] = sum over parts, ascending; eight loads in flight per thread
+// out[i] = sum over parts.  Four neighbouring lanes share an element and take every fourth part each (eight
+// loads in flight per lane), then add up by two shuffles: a fixed order, and a third of the dependent
+// load rounds of one lane per element -- the kernel's time is their latency, not the volume.
 template <typename Parts>
 __global__ void __launch_bounds__(256)
 k_reduce_sum(Parts parts, int n_parts, long long n, float* __restrict__ out) {
   grid_dep_sync();
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  const long long gi = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = gi >> 2;
+  const int sub = (int)(gi & 3);
   float a = 0.f;
-  for (int p0 = 0; p0 < n_parts; p0 += 8) {
-    float v[8];
+  if (i < n) {
+    for (int p0 = sub; p0 < n_parts; p0 += 32) {
+      float v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = p0 + j < n_parts ? parts.at(p0 + j)[i] : 0.f;
+      for (int j = 0; j < 8; ++j) v[j] = p0 + 4 * j < n_parts ? parts.at(p0 + 4 * j)[i] : 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) a += v[j];
+      for (int j = 0; j < 8; ++j) a += v[j];
+    }
   }
-  out[i] = a;
+  a += __shfl_xor_sync(0xffffffffu, a, 1);
+  a += __shfl_xor_sync(0xffffffffu, a, 2);
+  if (sub == 0 && i < n) out[i] = a;
 }
 
 // ---------------------------------------------------------------------------------
@@ -598,7 +605,7 @@ int launch_combine(const float* rec, int n_parts, long long rows, int D, int dty
 }
 
 int launch_reduce_sum(const float* parts, int n_parts, long long n, float* out, cudaStream_t st) {
-  launch_dep(k_reduce_sum<PartsStrided>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, PartsStrided{parts, n}, n_parts, n, out);
+  launch_dep(k_reduce_sum<PartsStrided>, dim3((unsigned)((4 * n + 255) / 256)), dim3(256), 0, st, PartsStrided{parts, n}, n_parts, n, out);
   return FLARE_OK;
 }
 
@@ -613,7 +620,7 @@ int launch_combine_ptrs(const float* const* recs, int n_parts, long long rows, i
 }
 
 int launch_reduce_sum_ptrs(const float* const* parts, int n_parts, long long n, float* out, cudaStream_t st) {
-  launch_dep(k_reduce_sum<PartsPtrs>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, PartsPtrs{parts}, n_parts, n, out);
+  launch_dep(k_reduce_sum<PartsPtrs>, dim3((unsigned)((4 * n + 255) / 256)), dim3(256), 0, st, PartsPtrs{parts}, n_parts, n, out);
   return FLARE_OK;
 }
 
