@@ -359,14 +359,20 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
         const long long tok = (long long)n0 + (t + 1) * 128 + n;
         load_rows<T16>(a, b, tok, tok < n1, hk, un, wn);
       }
+      // two tiles of P per round trip of the tensor-memory stores
 #pragma unroll
-      for (int blk = 0; blk < 8; ++blk) {
-        const int g = 8 * t + blk, buf = g % kNP;
-        if (g >= kNP) mbar_wait_hot(&bars->empty[buf], (uint32_t)(g / kNP - 1) & 1, status, abort_flag);
+      for (int blk = 0; blk < 8; blk += 2) {
+        const int g = 8 * t + blk, buf = g % kNP, buf1 = (g + 1) % kNP;
+        if (g >= kNP) {
+          mbar_wait_hot(&bars->empty[buf], (uint32_t)(g / kNP - 1) & 1, status, abort_flag);
+          mbar_wait_hot(&bars->empty[buf1], (uint32_t)((g + 1) / kNP - 1) & 1, status, abort_flag);
+        }
         build_pairs_tmem<T16>(lane_base + 64 * buf, hk, blk, uw, ww);
+        build_pairs_tmem<T16>(lane_base + 64 * buf1, hk, blk + 1, uw, ww);
         tmem_wait_st();
         tc_fence_before();
         arrive(&bars->full[buf]);
+        arrive(&bars->full[buf1]);
       }
       if (*reinterpret_cast<volatile int*>(abort_flag)) break;
       if (t > 0) write_tile(t - 1);
