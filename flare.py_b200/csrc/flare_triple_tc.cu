@@ -16,8 +16,9 @@
 //             (scaled per (b,h) by a power of two so that fp16 cannot overflow)
 //
 // Eight producer warps build the tiles of P (one token row and half of the w features per thread: 4 packed
-// multiplies per eight pairs) into four buffers; one warp issues the products (tcgen05.mma, fp32
-// accumulation) and recycles the buffers through mbarriers.  Every wait is bounded.
+// multiplies per eight pairs) into four buffers; two warps issue the products (tcgen05.mma, fp32
+// accumulation; alternate tiles, each warp into accumulators of its own, so nothing depends on the order of
+// two threads' products) and recycle the buffers through mbarriers.  Every wait is bounded.
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -30,7 +31,7 @@ namespace {
 
 constexpr int kTD = 32;                            // every feature dimension
 constexpr int kProd = 256;                         // producer threads
-constexpr int kThreadsT = kProd + 32;              // + the issuing warp
+constexpr int kThreadsT = kProd + 64;              // + two issuing warps (alternate tiles of P, accumulators of their own)
 constexpr int kPBytes = 128 * 128 * 2;             // one tile of P: 128 tokens x 128 pairs, 16-bit
 constexpr int kNP = 4;                             // tiles of P in flight (building, waiting, being multiplied)
 constexpr int kBBytes = 128 * 64;                  // one token tile of b (outer)
@@ -152,7 +153,7 @@ k_triple_tc_outer(const T16* __restrict__ A, const T16* __restrict__ Bm, const T
   }
   if (tid == 0) {
     for (int i = 0; i < kNP; ++i) { mbar_init(&bars->full[i], kProd); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_free[i], kProd); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 2); mbar_init(&bars->acc_free[i], kProd); }
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -232,8 +233,9 @@ k_triple_tc_outer(const T16* __restrict__ A, const T16* __restrict__ Bm, const T
     const uint32_t idesc = idesc_f16(128, kTD, F, F, 1, 1);          // A (pairs x tokens) and B (tokens x j) MN-major
     const uint64_t pdesc = smem_desc_mn128(smem_u32(sP), 128 * 128, 1024);
     const uint64_t bdesc = smem_desc<64>(smem_u32(sB));
+    const int iw = warp - kProd / 32;              // this issuing warp takes the blocks iw, iw + 2, ... (accumulators of their own)
     for (int t = 0; t < T; ++t) {
-      for (int blk = 0; blk < 8; ++blk) {
+      for (int blk = iw; blk < 8; blk += 2) {
         const int g = 8 * t + blk, buf = g % kNP;
         mbar_wait_hot(&bars->full[buf], (uint32_t)(g / kNP) & 1, status, abort_flag);
         tc_fence_after();
@@ -243,7 +245,7 @@ k_triple_tc_outer(const T16* __restrict__ A, const T16* __restrict__ Bm, const T
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) mma_ss(tmem + 32 * blk, pa + 128 * kk, pb + 64 * kk, idesc, (t > 0) || (kk > 0));
           mma_commit(&bars->empty[buf]);
-          if (t == T - 1 && blk == 7) mma_commit(&bars->acc_full[0]);
+          if (t == T - 1 && blk >= 6) mma_commit(&bars->acc_full[0]);
         }
         __syncwarp();
         if (*reinterpret_cast<volatile int*>(abort_flag)) break;
@@ -275,7 +277,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
   if (T == 0) return;
   if (tid == 0) {
     for (int i = 0; i < kNP; ++i) { mbar_init(&bars->full[i], kProd); mbar_init(&bars->empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 1); mbar_init(&bars->acc_free[i], kProd); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&bars->acc_full[i], 2); mbar_init(&bars->acc_free[i], kProd); }
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -318,7 +320,7 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
   T16* o = O + (long long)bh * N * kTD;
   constexpr int F = Op16<T16>::kFmt;
   const float oscale = alpha * tinv;
-  constexpr uint32_t kAcc = 64 * kNP;
+  constexpr uint32_t kAcc = 64 * kNP;              // + 64 iw + 32 par: one accumulator per issuing warp and tile parity
 
   if (warp < kProd / 32) {
     // ================= producers; they also write out the finished tile =================
@@ -328,9 +330,12 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
       const int par = t & 1;
       mbar_wait(&bars->acc_full[par], (uint32_t)(t >> 1) & 1, status, abort_flag);
       tc_fence_after();
-      uint32_t r[16];
+      uint32_t r[16], r2[16];
       tmem_ld16(lane_base + kAcc + 32 * par + 16 * hk, r);
+      tmem_ld16(lane_base + kAcc + 64 + 32 * par + 16 * hk, r2);
       tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(r2[i]));
       tc_fence_before();
       arrive(&bars->acc_free[par]);
       const long long tok = (long long)n0 + t * 128 + n;
@@ -382,20 +387,21 @@ k_triple_tc_contract(const float* __restrict__ Tm, long long sx, long long sy, l
     // ================= issuing warp =================
     const uint32_t idesc = idesc_f16(128, kTD, F, F, 0, 1);          // A (tokens x pairs) in tensor memory, B (pairs x x) MN-major
     const uint64_t tdesc = smem_desc<64>(smem_u32(sT));
+    const int iw = warp - kProd / 32;              // this issuing warp takes the blocks iw, iw + 2, ... into its own accumulator
     for (int t = 0; t < T; ++t) {
       const int par = t & 1;
       if (t >= 2) mbar_wait(&bars->acc_free[par], (uint32_t)((t - 2) >> 1) & 1, status, abort_flag);
-      for (int blk = 0; blk < 8; ++blk) {
+      for (int blk = iw; blk < 8; blk += 2) {
         const int g = 8 * t + blk, buf = g % kNP;
         mbar_wait_hot(&bars->full[buf], (uint32_t)(g / kNP) & 1, status, abort_flag);
         tc_fence_after();
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            mma_ts(tmem + kAcc + 32 * par, tmem + 64 * buf + 8 * kk, tdesc + (uint64_t)(64 * (8 * blk + kk)), idesc,
-                   (blk > 0) || (kk > 0));
+            mma_ts(tmem + kAcc + 64 * iw + 32 * par, tmem + 64 * buf + 8 * kk, tdesc + (uint64_t)(64 * (8 * blk + kk)), idesc,
+                   (blk > iw) || (kk > 0));
           mma_commit(&bars->empty[buf]);
-          if (blk == 7) mma_commit(&bars->acc_full[par]);
+          if (blk >= 6) mma_commit(&bars->acc_full[par]);
         }
         __syncwarp();
         if (*reinterpret_cast<volatile int*>(abort_flag)) break;
