@@ -598,14 +598,14 @@ def run_causal(args):
     train_step()
     train_ms = timed(train_step, max(2, min(args.steps, 5)))
     # the prefill against its bounds: k, v read and y written once (2 bytes each), the three contractions of the
-    # chunked form (scores, state update, read-out: 2 M D flops per token each) on the tensor cores it does not
-    # use yet -- the walk kernel is fp32 FMA code, so the fractions say how far it is from the hardware
+    # chunked form (scores, state update, read-out: 2 M D flops per token each); the walk of every 128-token chunk
+    # runs on the tensor cores (five products per chunk), its softmax, running sum and mask on the fp32 pipes
     pk = peaks()
     tok_bytes = B * H * N * D * 2
     alg_bytes, alg_flops = 3 * tok_bytes, 3 * 2 * B * H * N * M * D
     roof = dict(bound="hbm", achieved=alg_bytes / (ms * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s",
                 frac=alg_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], traffic=None, peaks_source=pk["source"],
-                tensor_frac=alg_flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], kernel="k_causal_walk (fp32 SIMT)")
+                tensor_frac=alg_flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], kernel="k_causal_tc_walk (tcgen05)")
     print(json.dumps(dict(metric="causal FLARE prefill Mtokens/s", value=B * N / ms / 1e3, unit="Mtokens/s", n_gpus=1,
                           steps=args.steps, warmup=max(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
                           dtype="bf16", data="synthetic", decode_step_us=us, fwd_bwd_ms=train_ms, roofline=roof,

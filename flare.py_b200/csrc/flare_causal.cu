@@ -20,6 +20,7 @@
 #include <cstdio>
 #include <cuda_runtime.h>
 #include "common.cuh"
+#include "launch.h"
 
 namespace flare { void set_last_error(const char* msg); }
 
@@ -113,6 +114,7 @@ struct CausalArgs {
   const float* prefix;         // [n_chunks][B][H][M][D+2]: the record before each chunk
   float* state;                // decode: [B][H][M][D+2], updated in place (prefix == nullptr)
   int tokens_per_cta;          // kChunk in prefill, N (usually 1) in decode
+  const int* redo;             // prefill behind the tensor-core walk: [chunks][B*H], CTAs whose flag is 0 return
 };
 
 template <typename T, int D>
@@ -139,6 +141,7 @@ k_causal_walk(CausalArgs a) {
   const int d = tid % D, g = tid / D;
   const int nlat = M / G;                          // latents of this thread: g * nlat ... g * nlat + nlat - 1
   const int chunk = blockIdx.x, bh = blockIdx.y;
+  if (a.redo && a.redo[chunk * gridDim.y + bh] == 0) return;
   const int b = bh / a.H, h = bh % a.H;
   const int n0 = chunk * a.tokens_per_cta, n1 = min(a.N, n0 + a.tokens_per_cta);
   const int W = D + 2;
@@ -331,6 +334,7 @@ int fill_args(const FlareProblem* p, CausalArgs* a) {
   if (p->M % G != 0 || p->M / G > kMaxLat)
     return refuse(FLARE_EUNSUPPORTED, "causal: M=%d must be a multiple of %d and at most %d for D=%d", p->M, G, G * kMaxLat, D);
   a->B = p->B; a->H = p->H; a->N = p->N; a->M = p->M; a->D = D; a->scale = p->scale;
+  a->redo = nullptr;
   for (int i = 0; i < 3; ++i) { a->qs[i] = p->q_stride[i]; a->ks[i] = p->k_stride[i]; a->vs[i] = p->v_stride[i]; a->ys[i] = p->y_stride[i]; }
   return FLARE_OK;
 }
@@ -363,7 +367,7 @@ extern "C" {
 size_t flare_causal_workspace_bytes(const FlareProblem* p) {
   if (!p || p->N < 1) return 0;
   const size_t chunks = ((size_t)p->N + kChunk - 1) / kChunk;
-  return chunks * p->B * p->H * p->M * (p->D + 2) * sizeof(float) + 256;
+  return chunks * p->B * p->H * p->M * (p->D + 2) * sizeof(float) + chunks * p->B * p->H * sizeof(int) + 256;
 }
 
 int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
@@ -386,6 +390,16 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;
   a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;
+  if (flare::causal_tc_walk_supported(p, q, k, v, y)) {
+    // the tensor-core walk flags the chunks whose scores span too many octaves for its fixed reference
+    // maximum; the fp32 walk, launched behind it, redoes exactly those (every other CTA returns at once)
+    int* redo = reinterpret_cast<int*>(workspace + (size_t)chunks * rows * (p->D + 2));
+    rc = flare::causal_tc_walk(p, q, k, v, y, workspace, redo, chunks, st);
+    if (rc != FLARE_OK) return refuse(rc, "causal_prefill: tensor-core walk could not be launched");
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal_prefill: %s", cudaGetErrorString(e));
+    a.redo = redo;
+  }
   return run_walk(p, a, chunks, st);
 }
 

@@ -1,0 +1,355 @@
+// Causal FLARE prefill, pass 3 on the tensor cores (bf16, M <= 128, D in {32, 64}).
+//
+// One CTA per (b, h, 128-token chunk) starts from the chunk's prefix record (m0, l0, acc0) and writes the
+// chunk's y.  In the chunked form every contraction is a product (S = scale q k^T, mu = max(m0, rowmax S),
+// a = e^{m0 - mu}, E = e^{S - mu}, l_mt = a l0 + cumsum_t E, A = softmax_M(S), G = A / l):
+//
+//   y_t = sum_m G_mt (a_m acc0_m)  +  sum_{n <= t} W_tn v_n,        W_tn = sum_m G_mt E_mn
+//
+//   1. S [latent lanes x token columns] and S^T [token lanes x latent columns]: two tcgen05 products, so that
+//      the softmax over the latents (per token) and the running sum over the tokens (per latent) are both walks
+//      along a thread's own tensor-memory row
+//   2. token threads: column maximum and sum of S^T -> shared memory (128 + 128 floats)
+//   3. latent threads: mu, a, E, l (running sum), G; E and G rows as bf16 into shared memory, laid out as the
+//      MN-major operands of the next product (contraction over the latents); a * acc0 as bf16 beside them
+//   4. W = G^T E (token lanes x token columns) and Y = G^T (a acc0): products from shared memory
+//   5. token threads: W masked to n <= t, packed to bf16 in place in tensor memory
+//   6. Y += W V: A operand from tensor memory, V tile as loaded by TMA
+//   7. token threads: Y -> y
+//
+// 128 row threads (a thread is latent m in steps 3 and token t in steps 2, 5, 7) and one issuing warp; every
+// wait is bounded.  bf16 operands also for fp16-sized dynamic range: E and G are relative to the chunk's final
+// maximum and can be very small and very large before it is reached.
+#include "common.cuh"
+#include "launch.h"
+#include "tc_common.cuh"
+#include "tma_host.h"
+
+namespace flare {
+
+using namespace tc;
+
+namespace {
+
+constexpr int kRows = 128;                         // row threads = latents = tokens of a chunk
+constexpr int kThreadsW = kRows + 32;
+
+struct CausalTcArgs {
+  int B, H, N, M;
+  float scale_log2;
+  int q_batched;
+  const float* prefix;                             // [chunks][B][H][M][D+2]
+  __nv_bfloat16* y;
+  long long ys[3];
+  int* redo;                                       // [chunks][B*H]: 1 = this chunk's scores span too many octaves
+  int* status;
+};
+
+__device__ __forceinline__ void arrive_w(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void row_sync() {       // the 128 row threads
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreadsW, 1)
+k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, CausalTcArgs a) {
+  constexpr int ROWB = 2 * D, CPR = ROWB / 16, W = D + 2;
+  constexpr int kTile = 128 * ROWB;                // Q, K, V, a*acc0
+  constexpr int kHalf = 128 * 128;                 // 64-token half of the E / G tiles
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTile;
+  uint8_t* sV = sK + kTile;
+  uint8_t* sA0 = sV + kTile;                       // a_m acc0_m as bf16: [latent][D]
+  uint8_t* sG = sA0 + kTile;                       // [2 halves][latent rows][64 tokens]
+  uint8_t* sE = sG + 2 * kHalf;
+  float* sCmax = reinterpret_cast<float*>(sE + 2 * kHalf);   // [128] column maximum (log2 units)
+  float* sCinv = sCmax + 128;                      // [128] 1 / column sum (0 past the end of the sequence)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sCinv + 128);
+  uint64_t* bar_load = bars;                       // Q, K, V landed
+  uint64_t* bar_s = bars + 1;                      // S, S^T complete
+  uint64_t* bar_ge = bars + 2;                     // E, G, a*acc0 written (128 arrivals)
+  uint64_t* bar_w = bars + 3;                      // W and the first part of Y complete
+  uint64_t* bar_wp = bars + 4;                     // masked W packed (128 arrivals)
+  uint64_t* bar_y = bars + 5;                      // Y complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  int* abort_flag = reinterpret_cast<int*>(bars + 7);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int n0 = chunk * 128;
+  const int cnt = min(128, a.N - n0);
+  const int M = a.M;
+
+  if (tid == 0) {
+    mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_ge, kRows); mbar_init(bar_w, 1);
+    mbar_init(bar_wp, kRows); mbar_init(bar_y, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;                             // range flag of this chunk
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 0) tmem_alloc<512>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t cS = 0, cST = 128, cW = 256, cY = 384;
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 3 * kTile);
+    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);      // rows past M arrive as zeros
+    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);                       // rows past N arrive as zeros
+    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
+  }
+
+  if (warp == kRows / 32) {
+    // ================= issuing warp =================
+    const uint32_t id_s = idesc_f16(128, 128, 1, 1, 0, 0);          // S, S^T: A, B K-major
+    const uint32_t id_w = idesc_f16(128, 64, 1, 1, 1, 1);           // W halves: A = G, B = E, both MN-major
+    const uint32_t id_y0 = idesc_f16(128, D, 1, 1, 1, 1);           // Y = G^T (a acc0): A, B MN-major
+    const uint32_t id_y1 = idesc_f16(128, D, 1, 1, 0, 1);           // Y += W V: A in tensor memory, B MN-major
+    const uint64_t dQ = smem_desc<ROWB>(smem_u32(sQ)), dK = smem_desc<ROWB>(smem_u32(sK)), dV = smem_desc<ROWB>(smem_u32(sV)),
+                   dA0 = smem_desc<ROWB>(smem_u32(sA0));
+    const uint64_t dG = smem_desc_mn128(smem_u32(sG), kHalf, 1024);
+    const uint64_t dE0 = smem_desc<128>(smem_u32(sE)), dE1 = smem_desc<128>(smem_u32(sE + kHalf));
+    mbar_wait(bar_load, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cS, dQ + 2 * kk, dK + 2 * kk, id_s, kk > 0);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cST, dK + 2 * kk, dQ + 2 * kk, id_s, kk > 0);
+      mma_commit(bar_s);
+    }
+    __syncwarp();
+    mbar_wait(bar_ge, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {             // contraction over the latents, 16 per product
+        mma_ss(tmem + cW, dG + 128 * kk, dE0 + 128 * kk, id_w, kk > 0);
+        mma_ss(tmem + cW + 64, dG + 128 * kk, dE1 + 128 * kk, id_w, kk > 0);
+        mma_ss(tmem + cY, dG + 128 * kk, dA0 + (uint64_t)(kk * ROWB), id_y0, kk > 0);
+      }
+      mma_commit(bar_w);
+    }
+    __syncwarp();
+    mbar_wait(bar_wp, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk)               // contraction over the chunk's tokens
+        mma_ts(tmem + cY, tmem + cW + 8 * kk, dV + (uint64_t)(kk * ROWB), id_y1, true);
+      mma_commit(bar_y);
+    }
+    __syncwarp();
+  } else {
+    // ================= row threads: token t in steps 2, 5, 7, latent m in step 3 =================
+    const int r = tid;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const float sl = a.scale_log2;
+    // the prefix record of latent r (needed in step 3; fetched now)
+    const float* rec = a.prefix + ((((long long)chunk * a.B + b) * a.H + h) * M + min(r, M - 1)) * W;
+    const float m0 = rec[D], l0 = rec[D + 1];
+
+    // ---- step 2: softmax statistics over the latents of token r ----
+    mbar_wait(bar_s, 0, a.status, abort_flag);
+    tc_fence_after();
+    {
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cST + 32 * c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (32 * c + j < M) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
+      }
+      float su = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cST + 32 * c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (32 * c + j < M) su += ex2(fmaf(__uint_as_float(v[j]), sl, -mx));
+      }
+      const bool in = r < cnt;
+      sCmax[r] = in ? mx : 0.f;
+      sCinv[r] = in ? 1.f / su : 0.f;
+    }
+    row_sync();
+
+    // ---- step 3: latent r: mu, a, E, running l, G; rows of E, G and a * acc0 into shared memory ----
+    {
+      const bool live = r < M;
+      float mu = m0 * kLog2e;                      // the record keeps m in natural-log units
+      float first = mu;                            // the running maximum after the chunk's first token
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cS + 32 * c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (32 * c + j < cnt) mu = fmaxf(mu, __uint_as_float(v[j]) * sl);
+        if (c == 0) first = fmaxf(first, __uint_as_float(v[0]) * sl);
+      }
+      // E and l are relative to the chunk's final maximum: l_mt >= 2^(first - mu).  Past 64 octaves the chunk is
+      // handed to the walk that carries a running maximum (flagged; its y overwrites this kernel's).
+      if (live && mu - first > 64.f) abort_flag[1] = 1;
+      const float aa = (m0 == -INFINITY) ? 0.f : ex2(m0 * kLog2e - mu);
+      float l = aa * l0;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cS + 32 * c, v);
+        tmem_wait_ld();
+        uint32_t pe[16], pg[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float e2[2], g2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int t = 32 * c + j + u;
+            const float s2 = __uint_as_float(v[j + u]) * sl;
+            const bool in = live && t < cnt;
+            const float e = in ? ex2(s2 - mu) : 0.f;
+            l += e;
+            const float A = in ? ex2(s2 - sCmax[t]) * sCinv[t] : 0.f;
+            e2[u] = e;
+            g2[u] = l > 0.f ? __fdividef(A, l) : 0.f;
+          }
+          pe[j >> 1] = pack_bf16(e2[0], e2[1]);
+          pg[j >> 1] = pack_bf16(g2[0], g2[1]);
+        }
+        // 32 tokens = four 16-byte chunks of the 64-token half c / 2
+        uint8_t* eh = sE + (c >> 1) * kHalf;
+        uint8_t* gh = sG + (c >> 1) * kHalf;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t off = swz_off<128>(r, 4 * (c & 1) + q4);
+          *reinterpret_cast<uint4*>(eh + off) = make_uint4(pe[4 * q4], pe[4 * q4 + 1], pe[4 * q4 + 2], pe[4 * q4 + 3]);
+          *reinterpret_cast<uint4*>(gh + off) = make_uint4(pg[4 * q4], pg[4 * q4 + 1], pg[4 * q4 + 2], pg[4 * q4 + 3]);
+        }
+      }
+      // a * acc0 of this latent
+#pragma unroll
+      for (int c = 0; c < CPR; ++c) {
+        uint4 o = make_uint4(0, 0, 0, 0);
+        if (live) {
+          const float2* x = reinterpret_cast<const float2*>(rec + 8 * c);   // records are D + 2 floats: 8-byte aligned
+          const float2 x0 = x[0], x1 = x[1], x2 = x[2], x3 = x[3];
+          o = make_uint4(pack_bf16(x0.x * aa, x0.y * aa), pack_bf16(x1.x * aa, x1.y * aa), pack_bf16(x2.x * aa, x2.y * aa),
+                         pack_bf16(x3.x * aa, x3.y * aa));
+        }
+        *reinterpret_cast<uint4*>(sA0 + swz_off<ROWB>(r, c)) = o;
+      }
+      fence_proxy_async();
+      arrive_w(bar_ge);
+    }
+
+    // ---- step 5: token r: W masked to n <= r (and to the tokens that exist), packed in place ----
+    mbar_wait(bar_w, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (r == 0) a.redo[chunk * gridDim.y + bh] = abort_flag[1];
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32], pw[16];
+      tmem_ld32(lane_base + cW + 32 * c, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const int n = 32 * c + j;
+        const float w0 = (n <= r && n < cnt) ? __uint_as_float(v[j]) : 0.f;
+        const float w1 = (n + 1 <= r && n + 1 < cnt) ? __uint_as_float(v[j + 1]) : 0.f;
+        pw[j >> 1] = pack_bf16(w0, w1);
+      }
+      tmem_st16(lane_base + cW + 16 * c, pw);      // columns already read: the packed row trails the reads
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    arrive_w(bar_wp);
+
+    // ---- step 7: Y of token r -> y ----
+    mbar_wait(bar_y, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (!*reinterpret_cast<volatile int*>(abort_flag)) {
+      __nv_bfloat16* yp = a.y + b * a.ys[0] + h * a.ys[1] + (long long)(n0 + r) * a.ys[2];
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cY + 32 * c, v);
+        tmem_wait_ld();
+        if (r < cnt) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+            o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+            o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+            o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+            reinterpret_cast<uint4*>(yp + 32 * c)[q4] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc<512>(tmem);
+}
+
+template <int D>
+int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
+                   int* redo, int chunks, cudaStream_t st) {
+  CUtensorMap tmQ, tmK, tmV;
+  const uint64_t e = 2;
+  const bool qb = p->q_stride[0] != 0;
+  if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)p->M, (uint64_t)p->H, (uint64_t)(qb ? p->B : 1), p->q_stride[2] * e,
+                     p->q_stride[1] * e, (qb ? p->q_stride[0] : p->q_stride[1] * p->H) * e, 128) ||
+      !make_tile_map(&tmK, k, 1, D, (uint64_t)p->N, (uint64_t)p->H, (uint64_t)p->B, p->k_stride[2] * e, p->k_stride[1] * e,
+                     (p->B > 1 ? p->k_stride[0] : p->k_stride[1] * p->H) * e, 128) ||
+      !make_tile_map(&tmV, v, 1, D, (uint64_t)p->N, (uint64_t)p->H, (uint64_t)p->B, p->v_stride[2] * e, p->v_stride[1] * e,
+                     (p->B > 1 ? p->v_stride[0] : p->v_stride[1] * p->H) * e, 128))
+    return FLARE_EUNSUPPORTED;
+  CausalTcArgs a;
+  a.B = p->B; a.H = p->H; a.N = p->N; a.M = p->M;
+  a.scale_log2 = p->scale * kLog2e;
+  a.q_batched = qb ? 1 : 0;
+  a.prefix = prefix;
+  a.y = reinterpret_cast<__nv_bfloat16*>(y);
+  for (int i = 0; i < 3; ++i) a.ys[i] = p->y_stride[i];
+  a.redo = redo;
+  a.status = tc_status_ptr();
+  constexpr int smem = 4 * 128 * 2 * D + 4 * 128 * 128 + 1024 + 256 + 1024;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_walk<D>), smem) != FLARE_OK) return FLARE_ECUDA;
+  k_causal_tc_walk<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(tmQ, tmK, tmV, a);
+  return FLARE_OK;
+}
+
+}  // namespace
+
+// bf16, M <= 128, D in {32, 64}, rows the TMA can address (unit stride on D, 16-byte aligned strides)
+bool causal_tc_walk_supported(const FlareProblem* p, const void* q, const void* k, const void* v, const void* y) {
+  if (p->dtype != FLARE_BF16 || p->M < 1 || p->M > 128 || (p->D != 32 && p->D != 64)) return false;
+  if ((long long)p->B * p->H > 65535) return false;
+  auto ok = [&](const void* ptr, const int64_t* s) {
+    if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+    for (int i = 0; i < 3; ++i) if ((s[i] * 2) % 16) return false;
+    return true;
+  };
+  return ok(q, p->q_stride) && ok(k, p->k_stride) && ok(v, p->v_stride) && ok(y, p->y_stride);
+}
+
+int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
+                   int* redo, int chunks, cudaStream_t st) {
+  return p->D == 32 ? launch_walk_tc<32>(p, q, k, v, y, prefix, redo, chunks, st)
+                    : launch_walk_tc<64>(p, q, k, v, y, prefix, redo, chunks, st);
+}
+
+}  // namespace flare

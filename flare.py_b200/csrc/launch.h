@@ -71,6 +71,12 @@ int* tc_status_ptr();
 int num_sms();
 int tc_set_dyn_smem(const void* kernel, int bytes);
 
+// Causal prefill, pass 3 on the tensor cores (flare_causal_tc.cu): bf16, M <= 128, D in {32, 64}.
+bool causal_tc_walk_supported(const FlareProblem* p, const void* q, const void* k, const void* v, const void* y);
+// redo: int [chunks][B*H], written by every CTA: 1 where the chunk must be redone by the fp32 walk.
+int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
+                   int* redo, int chunks, cudaStream_t st);
+
 // Triple attention on the tensor cores (flare_triple_tc.cu): 16-bit inputs, every feature dimension 32.
 bool triple_tc_supported(int N, int D0, int D1, int D2, int dtype);
 bool triple_tc_strides_ok(long long sx, long long sy, long long sz);

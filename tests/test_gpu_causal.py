@@ -120,6 +120,49 @@ def test_serving_shape_split_prefill(cuda_dev):
     assert ((z_a - z_b).norm() / z_a.norm()).item() <= 2e-2
 
 
+@pytest.mark.parametrize("B,H,N,M,D,shared", [
+    (1, 2, 128, 128, 32, False),     # exactly one chunk
+    (2, 2, 333, 128, 64, True),      # ragged last chunk, latents shared by the batch
+    (1, 3, 700, 64, 64, False),      # fewer latents than tensor-memory lanes
+    (2, 1, 130, 96, 32, True),
+    (1, 1, 5, 32, 32, False),        # a handful of tokens
+])
+def test_prefill_tensor_core_walk_shapes(cuda_dev, B, H, N, M, D, shared):
+    """bf16 with M <= 128 and D in {32, 64} takes the tensor-core walk; state carried from a prior prefill too."""
+    import flare_b200 as fb
+    q, k, v = _inputs(B, H, N, M, D, torch.bfloat16, seed=11)          # q: [H, M, D]
+    if not shared:                                                      # one latent set per batch element
+        q = (torch.randn(B, H, M, D, generator=torch.Generator().manual_seed(12)) * D ** -0.25).bfloat16()
+    y_ref, (m_ref, l_ref, a_ref) = O.causal_recurrent(q.double(), k.double(), v.double(), 0.9)
+    qd, kd, vd = q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)
+    y, st = fb.flare_causal_prefill(qd, kd, vd, 0.9)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-2
+    if N > 64:                                           # split anywhere: the second call starts from a record
+        n0 = N // 3
+        y0, st0 = fb.flare_causal_prefill(qd, kd[:, :, :n0].contiguous(), vd[:, :, :n0].contiguous(), 0.9)
+        y1, _ = fb.flare_causal_prefill(qd, kd[:, :, n0:].contiguous(), vd[:, :, n0:].contiguous(), 0.9, state=st0)
+        assert O.rel_l2(torch.cat([y0, y1], 2).double().cpu(), y_ref) <= 2e-2
+
+
+def test_prefill_tensor_core_walk_hands_wide_chunks_to_the_fp32_walk(cuda_dev):
+    """Scores that climb by hundreds of octaves inside one chunk: the tensor-core walk keeps one reference
+    maximum per chunk, flags such chunks, and the fp32 walk with a running maximum redoes them."""
+    import flare_b200 as fb
+    B, H, N, M, D = 1, 2, 384, 64, 32
+    q, k, v = _inputs(B, H, N, M, D, torch.bfloat16, seed=13)
+    ramp = torch.ones(N)
+    ramp[128:256] = torch.linspace(1.0, 60.0, 128)       # the middle chunk only
+    k = (k.float() * ramp[None, None, :, None]).bfloat16()
+    y_ref, _ = O.causal_recurrent(q.double(), k.double(), v.double(), 1.0)
+    y, _ = fb.flare_causal_prefill(q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev), 1.0)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    assert torch.isfinite(y.float()).all()
+    assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-2
+
+
 # ---------------------------------------------------------------------------------------------------------
 # backward (flare_causal_mixer): against autograd through the dense definition and the chunked restatement
 # ---------------------------------------------------------------------------------------------------------
