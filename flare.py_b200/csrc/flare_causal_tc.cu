@@ -18,8 +18,10 @@
 //   7. token threads: Y -> y
 //
 // 128 row threads (a thread is latent m in steps 3 and token t in steps 2, 5, 7) and one issuing warp; every
-// wait is bounded.  bf16 operands also for fp16-sized dynamic range: E and G are relative to the chunk's final
-// maximum and can be very small and very large before it is reached.
+// wait is bounded.  bf16 only: E and G are relative to the chunk's final maximum and need the exponent range
+// of fp32 before that maximum is reached.  A chunk whose scores climb by more than 64 octaves is flagged and
+// redone by the fp32 walk, which carries a running maximum.  Two CTAs per SM (256 tensor-memory columns and
+// under 100 KB of shared memory each) so that one chunk's products and loads overlap another's arithmetic.
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -53,7 +55,7 @@ __device__ __forceinline__ void row_sync() {       // the 128 row threads
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreadsW, 1)
+__global__ void __launch_bounds__(kThreadsW, 2)
 k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, CausalTcArgs a) {
   constexpr int ROWB = 2 * D, CPR = ROWB / 16, W = D + 2;
@@ -61,13 +63,15 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   constexpr int kHalf = 128 * 128;                 // 64-token half of the E / G tiles
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // Two CTAs per SM: Q and K are dead once S and S^T are complete, and G takes their place
+  uint8_t* sG = smem;                              // [2 halves][latent rows][64 tokens]
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTile;
-  uint8_t* sV = sK + kTile;
-  uint8_t* sA0 = sV + kTile;                       // a_m acc0_m as bf16: [latent][D]
-  uint8_t* sG = sA0 + kTile;                       // [2 halves][latent rows][64 tokens]
   uint8_t* sE = sG + 2 * kHalf;
-  float* sCmax = reinterpret_cast<float*>(sE + 2 * kHalf);   // [128] column maximum (log2 units)
+  uint8_t* sV = sE + 2 * kHalf;
+  uint8_t* sA0 = sV + kTile;                       // a_m acc0_m as bf16: [latent][D]
+  static_assert(2 * kTile <= 2 * kHalf, "Q and K must fit in the G tile");
+  float* sCmax = reinterpret_cast<float*>(sA0 + kTile);      // [128] column maximum (log2 units)
   float* sCinv = sCmax + 128;                      // [128] 1 / column sum (0 past the end of the sequence)
   uint64_t* bars = reinterpret_cast<uint64_t*>(sCinv + 128);
   uint64_t* bar_load = bars;                       // Q, K, V landed
@@ -94,12 +98,13 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
   }
-  if (warp == 0) tmem_alloc<512>(tmem_slot);
+  if (warp == 0) tmem_alloc<256>(tmem_slot);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t cS = 0, cST = 128, cW = 256, cY = 384;
+  // W takes the columns of S once every latent thread has read its row, Y those of S^T
+  constexpr uint32_t cS = 0, cST = 128, cW = 0, cY = 128;
   if (tid == 0) {
     mbar_expect_tx(bar_load, 3 * kTile);
     tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);      // rows past M arrive as zeros
@@ -250,6 +255,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         *reinterpret_cast<uint4*>(sA0 + swz_off<ROWB>(r, c)) = o;
       }
       fence_proxy_async();
+      tc_fence_before();
       arrive_w(bar_ge);
     }
 
@@ -301,7 +307,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<512>(tmem);
+  if (warp == 0) tmem_dealloc<256>(tmem);
 }
 
 template <int D>
@@ -326,7 +332,7 @@ int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const vo
   for (int i = 0; i < 3; ++i) a.ys[i] = p->y_stride[i];
   a.redo = redo;
   a.status = tc_status_ptr();
-  constexpr int smem = 4 * 128 * 2 * D + 4 * 128 * 128 + 1024 + 256 + 1024;
+  constexpr int smem = 2 * 128 * 2 * D + 4 * 128 * 128 + 1024 + 256 + 1024;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_walk<D>), smem) != FLARE_OK) return FLARE_ECUDA;
   k_causal_tc_walk<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(tmQ, tmK, tmV, a);
   return FLARE_OK;
