@@ -160,8 +160,14 @@ k_causal_walk(CausalArgs a) {
   for (int j = 0; j < kMaxLat; ++j) acc[j] = (j < nlat) ? rec[(g * nlat + j) * W + d] : 0.f;
   __syncthreads();
 
-  for (int s0 = n0; s0 < n1; s0 += kSub) {
-    const int cnt = min(kSub, n1 - s0);
+  // E, l and acc of a sub-chunk are relative to the running maximum at its end, so l_mt >= e^{first - mu} with
+  // `first` the running maximum after its first token.  Where the scores of some latent climb by more than
+  // kSpread inside one sub-chunk that bound nears the underflow of fp32: from there on the chunk is walked token
+  // by token (a one-token step has l >= l0 or e = 1).
+  constexpr float kSpread = 60.f;
+  int sub = kSub;
+  for (int s0 = n0; s0 < n1;) {
+    const int cnt = min(sub, n1 - s0);
     for (int i = tid; i < cnt * D; i += kThreads) {
       const int t = i / D, dd = i % D;
       sK[t * DP + dd] = to_f32(kp[(long long)(s0 + t) * a.ks[2] + dd]);
@@ -213,6 +219,17 @@ k_causal_walk(CausalArgs a) {
       }
     }
     __syncthreads();
+    {
+      int wide = 0;
+      for (int m = tid; m < M; m += kThreads) {
+        const float mu0 = sMu[m];
+        float mu = mu0;
+        for (int t = 0; t < cnt; ++t) mu = fmaxf(mu, sS[t * MP + m]);
+        sA[m] = mu;
+        wide |= (mu - fmaxf(mu0, sS[m]) > kSpread);
+      }
+      if (cnt > 1 && __syncthreads_or(wide)) { sub = 1; continue; }    // again from s0, one token at a time
+    }
     // per token: max and sum over the latents (the scatter softmax); eight threads per token, latents
     // part, part + 8, ... each, combined by shuffles
     {
@@ -230,9 +247,7 @@ k_causal_walk(CausalArgs a) {
     __syncthreads();
     // per latent: new running max over the sub-chunk, E = e^{S - mu}, running l, weights
     for (int m = tid; m < M; m += kThreads) {
-      const float mu0 = sMu[m];
-      float mu = mu0;
-      for (int t = 0; t < cnt; ++t) mu = fmaxf(mu, sS[t * MP + m]);
+      const float mu0 = sMu[m], mu = sA[m];
       const float al = (mu0 == -INFINITY) ? 0.f : __expf(mu0 - mu);
       float l = al * sL[m];
       for (int t = 0; t < cnt; ++t) {
@@ -287,6 +302,7 @@ k_causal_walk(CausalArgs a) {
       }
     }
     __syncthreads();
+    s0 += cnt;
   }
   if (!a.prefix) {                                 // decode: the record moves on
     float* st = a.state + ((long long)b * a.H + h) * M * W;
@@ -379,10 +395,16 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int chunks = (p->N + kChunk - 1) / kChunk;
   // pass 1: one record per 128-token chunk
-  FlareProblem pp = *p;
-  pp.n_splits = chunks;
-  rc = flare_gather_partial(&pp, q, k, v, nullptr, workspace, st);
-  if (rc != FLARE_OK) return rc;
+  const bool on_tc = flare::causal_tc_walk_supported(p, q, k, v, y);
+  if (on_tc) {
+    rc = flare::causal_tc_record(p, q, k, v, workspace, chunks, st);
+    if (rc != FLARE_OK) return refuse(rc, "causal_prefill: tensor-core record pass could not be launched");
+  } else {
+    FlareProblem pp = *p;
+    pp.n_splits = chunks;
+    rc = flare_gather_partial(&pp, q, k, v, nullptr, workspace, st);
+    if (rc != FLARE_OK) return rc;
+  }
   // pass 2: exclusive prefix along the chunk axis
   const long long rows = (long long)p->B * p->H * p->M;
   const int rpb = kThreads / 32;
@@ -390,7 +412,7 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;
   a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;
-  if (flare::causal_tc_walk_supported(p, q, k, v, y)) {
+  if (on_tc) {
     // the tensor-core walk flags the chunks whose scores span too many octaves for its fixed reference
     // maximum; the fp32 walk, launched behind it, redoes exactly those (every other CTA returns at once)
     int* redo = reinterpret_cast<int*>(workspace + (size_t)chunks * rows * (p->D + 2));

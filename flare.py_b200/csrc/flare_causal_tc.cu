@@ -310,10 +310,148 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 0) tmem_dealloc<256>(tmem);
 }
 
+// Pass 1 for the same shapes: the record (acc, m, l) of every 128-token chunk on its own.  S = scale q k^T,
+// m = rowmax, E = e^{S - m} packed to bf16 in place in tensor memory, acc = E V.  128 tensor-memory columns and
+// three operand tiles per CTA: four CTAs per SM.  The record leaves through shared memory in one contiguous block.
 template <int D>
-int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
-                   int* redo, int chunks, cudaStream_t st) {
+__global__ void __launch_bounds__(kThreadsW, 4)
+k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, CausalTcArgs a, float* __restrict__ rec_out) {
+  constexpr int ROWB = 2 * D, W = D + 2;
+  constexpr int kTile = 128 * ROWB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTile;
+  uint8_t* sV = sK + kTile;
+  float* sOut = reinterpret_cast<float*>(smem);    // [M][D + 2], over the operand tiles once the products are done
+  static_assert(128 * W * 4 <= 3 * kTile, "the record must fit over the operand tiles");
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kTile);
+  uint64_t* bar_load = bars;
+  uint64_t* bar_s = bars + 1;
+  uint64_t* bar_p = bars + 2;                      // E packed (128 arrivals)
+  uint64_t* bar_acc = bars + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  int* abort_flag = reinterpret_cast<int*>(bars + 5);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / a.H, h = bh % a.H;
+  const int n0 = chunk * 128;
+  const int cnt = min(128, a.N - n0);
+  const int M = a.M;
+
+  if (tid == 0) {
+    mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_p, kRows); mbar_init(bar_acc, 1);
+    abort_flag[0] = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+  }
+  if (warp == 0) tmem_alloc<128>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t cS = 0, cAcc = 64;            // E packed occupies columns [0, 64) when acc is written
+  if (tid == 0) {
+    mbar_expect_tx(bar_load, 3 * kTile);
+    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);
+    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);
+    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
+  }
+
+  const int r = tid;
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+  float mx = -INFINITY, l = 0.f;
+  if (warp == kRows / 32) {
+    const uint32_t id_s = idesc_f16(128, 128, 1, 1, 0, 0);
+    const uint32_t id_pv = idesc_f16(128, D, 1, 1, 0, 1);
+    const uint64_t dQ = smem_desc<ROWB>(smem_u32(sQ)), dK = smem_desc<ROWB>(smem_u32(sK)), dV = smem_desc<ROWB>(smem_u32(sV));
+    mbar_wait(bar_load, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) mma_ss(tmem + cS, dQ + 2 * kk, dK + 2 * kk, id_s, kk > 0);
+      mma_commit(bar_s);
+    }
+    __syncwarp();
+    mbar_wait(bar_p, 0, a.status, abort_flag);
+    tc_fence_after();
+    if (elect_one()) {
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) mma_ts(tmem + cAcc, tmem + cS + 8 * kk, dV + (uint64_t)(kk * ROWB), id_pv, kk > 0);
+      mma_commit(bar_acc);
+    }
+    __syncwarp();
+    mbar_wait(bar_acc, 0, a.status, abort_flag);
+  } else {
+    const float sl = a.scale_log2;
+    mbar_wait(bar_s, 0, a.status, abort_flag);
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      tmem_ld32(lane_base + cS + 32 * c, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if (32 * c + j < cnt) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
+    }
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32], pe[16];
+      tmem_ld32(lane_base + cS + 32 * c, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float e0 = (32 * c + j < cnt) ? ex2(fmaf(__uint_as_float(v[j]), sl, -mx)) : 0.f;
+        const float e1 = (32 * c + j + 1 < cnt) ? ex2(fmaf(__uint_as_float(v[j + 1]), sl, -mx)) : 0.f;
+        l += e0 + e1;
+        pe[j >> 1] = pack_bf16(e0, e1);
+      }
+      tmem_st16(lane_base + cS + 16 * c, pe);      // columns already read
+    }
+    tmem_wait_st();
+    tc_fence_before();
+    arrive_w(bar_p);
+    mbar_wait(bar_acc, 0, a.status, abort_flag);
+    tc_fence_after();
+  }
+  __syncthreads();                                 // the products are complete: the operand tiles are free
+  if (warp < kRows / 32) {                         // whole warps: rows past M are staged and not copied out
+    {
+      float* orow = sOut + r * W;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(lane_base + cAcc + 32 * c, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          *reinterpret_cast<float2*>(orow + 32 * c + j) = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+      }
+      *reinterpret_cast<float2*>(orow + D) = make_float2(mx * kLn2, l);
+    }
+  }
+  __syncthreads();
+  // the record of this (chunk, b, h): M * (D + 2) contiguous floats
+  if (!*reinterpret_cast<volatile int*>(abort_flag)) {
+    float2* dst = reinterpret_cast<float2*>(rec_out + (((long long)chunk * a.B + b) * a.H + h) * M * W);
+    const float2* src = reinterpret_cast<const float2*>(sOut);
+    for (int i = tid; i < M * W / 2; i += kThreadsW) dst[i] = src[i];
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc<128>(tmem);
+}
+
+struct TcLaunch {
   CUtensorMap tmQ, tmK, tmV;
+  CausalTcArgs a;
+};
+
+template <int D>
+int fill_launch(const FlareProblem* p, const void* q, const void* k, const void* v, TcLaunch* L) {
+  CUtensorMap &tmQ = L->tmQ, &tmK = L->tmK, &tmV = L->tmV;
   const uint64_t e = 2;
   const bool qb = p->q_stride[0] != 0;
   if (!make_tile_map(&tmQ, q, 1, D, (uint64_t)p->M, (uint64_t)p->H, (uint64_t)(qb ? p->B : 1), p->q_stride[2] * e,
@@ -323,18 +461,42 @@ int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const vo
       !make_tile_map(&tmV, v, 1, D, (uint64_t)p->N, (uint64_t)p->H, (uint64_t)p->B, p->v_stride[2] * e, p->v_stride[1] * e,
                      (p->B > 1 ? p->v_stride[0] : p->v_stride[1] * p->H) * e, 128))
     return FLARE_EUNSUPPORTED;
-  CausalTcArgs a;
+  CausalTcArgs& a = L->a;
   a.B = p->B; a.H = p->H; a.N = p->N; a.M = p->M;
   a.scale_log2 = p->scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
+  a.prefix = nullptr; a.y = nullptr; a.redo = nullptr;
+  for (int i = 0; i < 3; ++i) a.ys[i] = p->y_stride[i];
+  a.status = tc_status_ptr();
+  return FLARE_OK;
+}
+
+template <int D>
+int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
+                   int* redo, int chunks, cudaStream_t st) {
+  TcLaunch L;
+  const int rc = fill_launch<D>(p, q, k, v, &L);
+  if (rc != FLARE_OK) return rc;
+  CausalTcArgs& a = L.a;
+  const CUtensorMap &tmQ = L.tmQ, &tmK = L.tmK, &tmV = L.tmV;
   a.prefix = prefix;
   a.y = reinterpret_cast<__nv_bfloat16*>(y);
-  for (int i = 0; i < 3; ++i) a.ys[i] = p->y_stride[i];
   a.redo = redo;
-  a.status = tc_status_ptr();
   constexpr int smem = 2 * 128 * 2 * D + 4 * 128 * 128 + 1024 + 256 + 1024;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_walk<D>), smem) != FLARE_OK) return FLARE_ECUDA;
   k_causal_tc_walk<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(tmQ, tmK, tmV, a);
+  return FLARE_OK;
+}
+
+template <int D>
+int launch_record_tc(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
+                     cudaStream_t st) {
+  TcLaunch L;
+  const int rc = fill_launch<D>(p, q, k, v, &L);
+  if (rc != FLARE_OK) return rc;
+  constexpr int smem = 3 * 128 * 2 * D + 256 + 1024;
+  if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_record<D>), smem) != FLARE_OK) return FLARE_ECUDA;
+  k_causal_tc_record<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(L.tmQ, L.tmK, L.tmV, L.a, rec);
   return FLARE_OK;
 }
 
@@ -358,4 +520,11 @@ int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const vo
                     : launch_walk_tc<64>(p, q, k, v, y, prefix, redo, chunks, st);
 }
 
+}  // namespace flare
+
+namespace flare {
+int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
+                     cudaStream_t st) {
+  return p->D == 32 ? launch_record_tc<32>(p, q, k, v, rec, chunks, st) : launch_record_tc<64>(p, q, k, v, rec, chunks, st);
+}
 }  // namespace flare
