@@ -49,6 +49,7 @@ int refuse(int code, const char* fmt, ...) {
 __global__ void __launch_bounds__(kThreads)
 k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, const float* __restrict__ state_in,
               float* __restrict__ state_out) {
+  grid_dep_sync();
   const long long row = (long long)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   if (row >= rows) return;
@@ -61,38 +62,48 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) acc[i] = state_in[row * W + lane + 32 * i];
   }
-  // the record of chunk c + 1 is fetched while chunk c is combined: the chain is latency bound
-  float mn_ = 0.f, ln_ = 0.f, an_[4] = {0.f, 0.f, 0.f, 0.f};
-  {
-    const float* r = rec + row * W;
-    mn_ = r[D]; ln_ = r[D + 1];
+  // kAhead records are in flight per warp while one is combined: a warp's chain is latency bound and a record is
+  // only (D + 2) floats, so the memory system needs several per warp to stay busy
+  constexpr int kAhead = 4;
+  float mb[kAhead], lb[kAhead], ab[kAhead][4];
+  auto fetch = [&](int c, float& mo, float& lo, float (&ao)[4]) {
+    const float* r = rec + c * cs + row * W;
+    mo = r[D]; lo = r[D + 1];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) an_[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+    for (int i = 0; i < 4; ++i) ao[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+  };
+#pragma unroll
+  for (int i = 0; i < kAhead; ++i) {
+    mb[i] = -INFINITY; lb[i] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ab[i][j] = 0.f;
+    if (i < n_chunks) fetch(i, mb[i], lb[i], ab[i]);
   }
-  for (int c = 0; c < n_chunks; ++c) {
-    float* r = rec + c * cs + row * W;
-    const float mc = mn_, lc = ln_;
-    float ac[4];
+  for (int c0 = 0; c0 < n_chunks; c0 += kAhead) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ac[i] = an_[i];
-    if (c + 1 < n_chunks) {
-      const float* rn = r + cs;
-      mn_ = rn[D]; ln_ = rn[D + 1];
+    for (int u = 0; u < kAhead; ++u) {
+      const int c = c0 + u;
+      if (c < n_chunks) {
+        float* r = rec + c * cs + row * W;
+        const float mc = mb[u], lc = lb[u];
+        float ac[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) an_[i] = (lane + 32 * i < D) ? rn[lane + 32 * i] : 0.f;
+        for (int i = 0; i < 4; ++i) ac[i] = ab[u][i];
+        if (c + kAhead < n_chunks) fetch(c + kAhead, mb[u], lb[u], ab[u]);
+        __syncwarp();
+        // the record of everything before chunk c
+#pragma unroll
+        for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[i];
+        if (lane == 0) { r[D] = m; r[D + 1] = l; }
+        const float mn = fmaxf(m, mc);
+        const float wa = (m == -INFINITY) ? 0.f : __expf(m - mn);
+        const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
+        l = wa * l + wc * lc;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[i] = wa * acc[i] + wc * ac[i];
+        m = mn;
+      }
     }
-    __syncwarp();
-    // the record of everything before chunk c
-#pragma unroll
-    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[i];
-    if (lane == 0) { r[D] = m; r[D + 1] = l; }
-    const float mn = fmaxf(m, mc);
-    const float wa = (m == -INFINITY) ? 0.f : __expf(m - mn);
-    const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
-    l = wa * l + wc * lc;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i] = wa * acc[i] + wc * ac[i];
-    m = mn;
   }
   if (state_out) {
 #pragma unroll
@@ -120,6 +131,7 @@ struct CausalArgs {
 template <typename T, int D>
 __global__ void __launch_bounds__(kThreads)
 k_causal_walk(CausalArgs a) {
+  grid_dep_sync();
   constexpr int G = kThreads / D;                  // latent groups
   extern __shared__ __align__(16) float sm[];
   const int M = a.M;
@@ -322,7 +334,7 @@ int launch_walk(const CausalArgs& a, int n_cta_x, cudaStream_t st) {
   if (smem > 227 * 1024) return refuse(FLARE_EUNSUPPORTED, "causal: M=%d D=%d needs %zu bytes of shared memory", a.M, D, smem);
   cudaError_t e = cudaFuncSetAttribute(k_causal_walk<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
-  k_causal_walk<T, D><<<dim3((unsigned)n_cta_x, (unsigned)(a.B * a.H)), kThreads, smem, st>>>(a);
+  launch_dep(k_causal_walk<T, D>, dim3((unsigned)n_cta_x, (unsigned)(a.B * a.H)), dim3(kThreads), smem, st, a);
   e = cudaPeekAtLastError();
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
   return FLARE_OK;
@@ -408,7 +420,8 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   // pass 2: exclusive prefix along the chunk axis
   const long long rows = (long long)p->B * p->H * p->M;
   const int rpb = kThreads / 32;
-  k_causal_scan<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(workspace, chunks, rows, p->D, state_in, state_out);
+  launch_dep(k_causal_scan, dim3((unsigned)((rows + rpb - 1) / rpb)), dim3(kThreads), 0, st, workspace, chunks, rows, p->D,
+             state_in, state_out);
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;
   a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;

@@ -54,10 +54,54 @@ __device__ __forceinline__ void row_sync() {       // the 128 row threads
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
+// The wait for outstanding tensor-memory loads, written as a dependency of the registers they fill, so that no use
+// of them can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_wait_ld_on(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :: "memory");
+}
+// One pass over a thread's 128-column row in four blocks of 32: block c + 1 is in flight while f works on block c.
+template <typename F>
+__device__ __forceinline__ void row_pass(uint32_t taddr, F&& f) {
+  uint32_t v[2][32];
+  tmem_ld32(taddr, v[0]);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tmem_wait_ld_on(v[c & 1]);
+    if (c + 1 < 4) tmem_ld32(taddr + 32 * (c + 1), v[(c + 1) & 1]);
+    f(c, v[c & 1]);
+  }
+}
+
+// Half a row (64 columns) in two blocks of 32.
+template <typename F>
+__device__ __forceinline__ void row_half_pass(uint32_t taddr, F&& f) {
+  uint32_t v[2][32];
+  tmem_ld32(taddr, v[0]);
+  tmem_wait_ld_on(v[0]);
+  tmem_ld32(taddr + 32, v[1]);
+  f(0, v[0]);
+  tmem_wait_ld_on(v[1]);
+  f(1, v[1]);
+}
+__device__ __forceinline__ void rows_sync() {      // the 256 row threads
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+// 256 row threads: thread (r, hb) owns row r (tensor-memory lane r) and the column half hb of every pass, so that a
+// pass is two blocks of 32 columns per thread and eight warps share the latency of one chunk.
+constexpr int kRowT = 256;
+constexpr int kThreadsW2 = kRowT + 32;
+
 template <int D>
-__global__ void __launch_bounds__(kThreadsW, 2)
+__global__ void __launch_bounds__(kThreadsW2, 2)
 k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, CausalTcArgs a) {
+  grid_dep_sync();
   constexpr int ROWB = 2 * D, CPR = ROWB / 16, W = D + 2;
   constexpr int kTile = 128 * ROWB;                // Q, K, V, a*acc0
   constexpr int kHalf = 128 * 128;                 // 64-token half of the E / G tiles
@@ -73,12 +117,14 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   static_assert(2 * kTile <= 2 * kHalf, "Q and K must fit in the G tile");
   float* sCmax = reinterpret_cast<float*>(sA0 + kTile);      // [128] column maximum (log2 units)
   float* sCinv = sCmax + 128;                      // [128] 1 / column sum (0 past the end of the sequence)
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sCinv + 128);
+  float2* sPart = reinterpret_cast<float2*>(sCinv + 128);    // [2][128] (maximum, sum) of a token over half the latents
+  float* sMuP = reinterpret_cast<float*>(sPart + 256);       // [2][128] maximum of a latent over half the tokens
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sMuP + 256);
   uint64_t* bar_load = bars;                       // Q, K, V landed
   uint64_t* bar_s = bars + 1;                      // S, S^T complete
-  uint64_t* bar_ge = bars + 2;                     // E, G, a*acc0 written (128 arrivals)
+  uint64_t* bar_ge = bars + 2;                     // E, G, a*acc0 written (256 arrivals)
   uint64_t* bar_w = bars + 3;                      // W and the first part of Y complete
-  uint64_t* bar_wp = bars + 4;                     // masked W packed (128 arrivals)
+  uint64_t* bar_wp = bars + 4;                     // masked W packed (256 arrivals)
   uint64_t* bar_y = bars + 5;                      // Y complete
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
   int* abort_flag = reinterpret_cast<int*>(bars + 7);
@@ -91,8 +137,8 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int M = a.M;
 
   if (tid == 0) {
-    mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_ge, kRows); mbar_init(bar_w, 1);
-    mbar_init(bar_wp, kRows); mbar_init(bar_y, 1);
+    mbar_init(bar_load, 1); mbar_init(bar_s, 1); mbar_init(bar_ge, kRowT); mbar_init(bar_w, 1);
+    mbar_init(bar_wp, kRowT); mbar_init(bar_y, 1);
     abort_flag[0] = 0;
     abort_flag[1] = 0;                             // range flag of this chunk
     fence_barrier_init();
@@ -103,8 +149,8 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  // W takes the columns of S once every latent thread has read its row, Y those of S^T
-  constexpr uint32_t cS = 0, cST = 128, cW = 0, cY = 128;
+  // W takes the columns of S once every latent thread has read its row, Y those of S^T; the packed W sits behind Y
+  constexpr uint32_t cS = 0, cST = 128, cW = 0, cY = 128, cWp = 192;
   if (tid == 0) {
     mbar_expect_tx(bar_load, 3 * kTile);
     tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);      // rows past M arrive as zeros
@@ -112,7 +158,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
   }
 
-  if (warp == kRows / 32) {
+  if (warp == kRowT / 32) {
     // ================= issuing warp =================
     const uint32_t id_s = idesc_f16(128, 128, 1, 1, 0, 0);          // S, S^T: A, B K-major
     const uint32_t id_w = idesc_f16(128, 64, 1, 1, 1, 1);           // W halves: A = G, B = E, both MN-major
@@ -149,102 +195,105 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (elect_one()) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk)               // contraction over the chunk's tokens
-        mma_ts(tmem + cY, tmem + cW + 8 * kk, dV + (uint64_t)(kk * ROWB), id_y1, true);
+        mma_ts(tmem + cY, tmem + cWp + 8 * kk, dV + (uint64_t)(kk * ROWB), id_y1, true);
       mma_commit(bar_y);
     }
     __syncwarp();
   } else {
-    // ================= row threads: token t in steps 2, 5, 7, latent m in step 3 =================
-    const int r = tid;
+    // ================= row threads: token r in steps 2, 5, 7, latent r in step 3; column half hb =================
+    const int r = 32 * (warp & 3) + lane, hb = warp >> 2;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl = a.scale_log2;
     // the prefix record of latent r (needed in step 3; fetched now)
     const float* rec = a.prefix + ((((long long)chunk * a.B + b) * a.H + h) * M + min(r, M - 1)) * W;
     const float m0 = rec[D], l0 = rec[D + 1];
+    const bool live = r < M;
 
-    // ---- step 2: softmax statistics over the latents of token r ----
     mbar_wait(bar_s, 0, a.status, abort_flag);
     tc_fence_after();
+    // ---- step 2: token r over the latents 64 hb ... 64 hb + 63: maximum and sum relative to it ----
     {
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cST + 32 * c, v);
-        tmem_wait_ld();
+      float mx = -INFINITY, su = 0.f;
+      row_half_pass(lane_base + cST + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (32 * c + j < M) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
-      }
-      float su = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cST + 32 * c, v);
-        tmem_wait_ld();
+        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < M) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
+      });
+      row_half_pass(lane_base + cST + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (32 * c + j < M) su += ex2(fmaf(__uint_as_float(v[j]), sl, -mx));
-      }
-      const bool in = r < cnt;
-      sCmax[r] = in ? mx : 0.f;
-      sCinv[r] = in ? 1.f / su : 0.f;
+        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < M) su += ex2(fmaf(__uint_as_float(v[j]), sl, -mx));
+      });
+      sPart[hb * 128 + r] = make_float2(mx, su);
     }
-    row_sync();
-
-    // ---- step 3: latent r: mu, a, E, running l, G; rows of E, G and a * acc0 into shared memory ----
+    // ---- step 3, first pass: latent r over the tokens 64 hb ... 64 hb + 63: maximum ----
+    float first = m0 * kLog2e;                     // hb == 0: the running maximum after the chunk's first token
     {
-      const bool live = r < M;
-      float mu = m0 * kLog2e;                      // the record keeps m in natural-log units
-      float first = mu;                            // the running maximum after the chunk's first token
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cS + 32 * c, v);
-        tmem_wait_ld();
+      float mp = -INFINITY;
+      row_half_pass(lane_base + cS + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (32 * c + j < cnt) mu = fmaxf(mu, __uint_as_float(v[j]) * sl);
+        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < cnt) mp = fmaxf(mp, __uint_as_float(v[j]) * sl);
         if (c == 0) first = fmaxf(first, __uint_as_float(v[0]) * sl);
-      }
+      });
+      sMuP[hb * 128 + r] = mp;
+    }
+    rows_sync();
+    if (hb == 0) {                                 // the two halves of token r's statistics
+      const float2 p0 = sPart[r], p1 = sPart[128 + r];
+      const float cm = fmaxf(p0.x, p1.x);
+      const float cs = p0.y * ex2(p0.x - cm) + (p1.x == -INFINITY ? 0.f : p1.y * ex2(p1.x - cm));
+      const bool in = r < cnt;
+      sCmax[r] = in ? cm : 0.f;
+      sCinv[r] = in ? 1.f / cs : 0.f;
+    }
+    const float mu = fmaxf(m0 * kLog2e, fmaxf(sMuP[r], sMuP[128 + r]));   // the record keeps m in natural-log units
+    rows_sync();
+
+    // ---- step 3: latent r: a, E, running l, G over its half of the tokens; a * acc0 over its half of D ----
+    {
       // E and l are relative to the chunk's final maximum: l_mt >= 2^(first - mu).  Past 64 octaves the chunk is
       // handed to the walk that carries a running maximum (flagged; its y overwrites this kernel's).
-      if (live && mu - first > 64.f) abort_flag[1] = 1;
+      if (hb == 0 && live && mu - first > 64.f) abort_flag[1] = 1;
       const float aa = (m0 == -INFINITY) ? 0.f : ex2(m0 * kLog2e - mu);
       float l = aa * l0;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cS + 32 * c, v);
-        tmem_wait_ld();
+      if (hb == 1) {                               // the sum over the first half, in the order its owner adds it
+        row_half_pass(lane_base + cS, [&](int c, const uint32_t (&v)[32]) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            l += (live && 32 * c + j < cnt) ? ex2(fmaf(__uint_as_float(v[j]), sl, -mu)) : 0.f;
+        });
+      }
+      uint8_t* eh = sE + hb * kHalf;
+      uint8_t* gh = sG + hb * kHalf;
+      row_half_pass(lane_base + cS + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
         uint32_t pe[16], pg[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
           float e2[2], g2[2];
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
-            const int t = 32 * c + j + u;
-            const float s2 = __uint_as_float(v[j + u]) * sl;
+            const int t = 64 * hb + 32 * c + j + u;
+            const float x = __uint_as_float(v[j + u]);
             const bool in = live && t < cnt;
-            const float e = in ? ex2(s2 - mu) : 0.f;
+            const float e = in ? ex2(fmaf(x, sl, -mu)) : 0.f;
             l += e;
-            const float A = in ? ex2(s2 - sCmax[t]) * sCinv[t] : 0.f;
+            const float A = in ? ex2(fmaf(x, sl, -sCmax[t])) * sCinv[t] : 0.f;
             e2[u] = e;
             g2[u] = l > 0.f ? __fdividef(A, l) : 0.f;
           }
           pe[j >> 1] = pack_bf16(e2[0], e2[1]);
           pg[j >> 1] = pack_bf16(g2[0], g2[1]);
         }
-        // 32 tokens = four 16-byte chunks of the 64-token half c / 2
-        uint8_t* eh = sE + (c >> 1) * kHalf;
-        uint8_t* gh = sG + (c >> 1) * kHalf;
+        // 32 tokens = four 16-byte chunks of this thread's 64-token half
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t off = swz_off<128>(r, 4 * (c & 1) + q4);
+          const uint32_t off = swz_off<128>(r, 4 * c + q4);
           *reinterpret_cast<uint4*>(eh + off) = make_uint4(pe[4 * q4], pe[4 * q4 + 1], pe[4 * q4 + 2], pe[4 * q4 + 3]);
           *reinterpret_cast<uint4*>(gh + off) = make_uint4(pg[4 * q4], pg[4 * q4 + 1], pg[4 * q4 + 2], pg[4 * q4 + 3]);
         }
-      }
-      // a * acc0 of this latent
+      });
+      // a * acc0 of this latent, half of its D values
 #pragma unroll
-      for (int c = 0; c < CPR; ++c) {
+      for (int cc = 0; cc < CPR / 2; ++cc) {
+        const int c = hb * (CPR / 2) + cc;
         uint4 o = make_uint4(0, 0, 0, 0);
         if (live) {
           const float2* x = reinterpret_cast<const float2*>(rec + 8 * c);   // records are D + 2 floats: 8-byte aligned
@@ -259,48 +308,51 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       arrive_w(bar_ge);
     }
 
-    // ---- step 5: token r: W masked to n <= r (and to the tokens that exist), packed in place ----
+    // ---- step 5: token r: its half of W masked to n <= r (and to the tokens that exist), packed behind Y ----
     mbar_wait(bar_w, 0, a.status, abort_flag);
     tc_fence_after();
-    if (r == 0) a.redo[chunk * gridDim.y + bh] = abort_flag[1];
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32], pw[16];
-      tmem_ld32(lane_base + cW + 32 * c, v);
-      tmem_wait_ld();
+    if (r == 0 && hb == 0) a.redo[chunk * gridDim.y + bh] = abort_flag[1];
+    if (hb == 1 && (warp & 3) < 2) {               // tokens 0 ... 63 see none of the columns 64 ... 127
+      uint32_t z[16];
 #pragma unroll
-      for (int j = 0; j < 32; j += 2) {
-        const int n = 32 * c + j;
-        const float w0 = (n <= r && n < cnt) ? __uint_as_float(v[j]) : 0.f;
-        const float w1 = (n + 1 <= r && n + 1 < cnt) ? __uint_as_float(v[j + 1]) : 0.f;
-        pw[j >> 1] = pack_bf16(w0, w1);
-      }
-      tmem_st16(lane_base + cW + 16 * c, pw);      // columns already read: the packed row trails the reads
+      for (int j = 0; j < 16; ++j) z[j] = 0u;
+      tmem_st16(lane_base + cWp + 32, z);
+      tmem_st16(lane_base + cWp + 48, z);
+    } else {
+      row_half_pass(lane_base + cW + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
+        uint32_t pw[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const int n = 64 * hb + 32 * c + j;
+          const float w0 = (n <= r && n < cnt) ? __uint_as_float(v[j]) : 0.f;
+          const float w1 = (n + 1 <= r && n + 1 < cnt) ? __uint_as_float(v[j + 1]) : 0.f;
+          pw[j >> 1] = pack_bf16(w0, w1);
+        }
+        tmem_st16(lane_base + cWp + 32 * hb + 16 * c, pw);
+      });
     }
     tmem_wait_st();
     tc_fence_before();
     arrive_w(bar_wp);
 
-    // ---- step 7: Y of token r -> y ----
+    // ---- step 7: Y of token r, half of its D values -> y ----
     mbar_wait(bar_y, 0, a.status, abort_flag);
     tc_fence_after();
     if (!*reinterpret_cast<volatile int*>(abort_flag)) {
-      __nv_bfloat16* yp = a.y + b * a.ys[0] + h * a.ys[1] + (long long)(n0 + r) * a.ys[2];
+      __nv_bfloat16* yp = a.y + b * a.ys[0] + h * a.ys[1] + (long long)(n0 + r) * a.ys[2] + hb * (D / 2);
+      uint32_t v[32];
+      if constexpr (D == 64) tmem_ld32(lane_base + cY + 32 * hb, v);
+      else tmem_ld16(lane_base + cY + 16 * hb, v);
+      tmem_wait_ld();
+      if (r < cnt) {
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cY + 32 * c, v);
-        tmem_wait_ld();
-        if (r < cnt) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
-            o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-            o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-            o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
-            reinterpret_cast<uint4*>(yp + 32 * c)[q4] = o;
-          }
+        for (int q4 = 0; q4 < D / 16; ++q4) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+          o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+          o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+          o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+          reinterpret_cast<uint4*>(yp)[q4] = o;
         }
       }
     }
@@ -317,6 +369,7 @@ template <int D>
 __global__ void __launch_bounds__(kThreadsW, 4)
 k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, CausalTcArgs a, float* __restrict__ rec_out) {
+  grid_dep_sync();
   constexpr int ROWB = 2 * D, W = D + 2;
   constexpr int kTile = 128 * ROWB;
   extern __shared__ uint8_t smem_raw[];
@@ -388,19 +441,12 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const float sl = a.scale_log2;
     mbar_wait(bar_s, 0, a.status, abort_flag);
     tc_fence_after();
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32];
-      tmem_ld32(lane_base + cS + 32 * c, v);
-      tmem_wait_ld();
+    row_pass(lane_base + cS, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) if (32 * c + j < cnt) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
-    }
-#pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32], pe[16];
-      tmem_ld32(lane_base + cS + 32 * c, v);
-      tmem_wait_ld();
+    });
+    row_pass(lane_base + cS, [&](int c, const uint32_t (&v)[32]) {
+      uint32_t pe[16];
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
         const float e0 = (32 * c + j < cnt) ? ex2(fmaf(__uint_as_float(v[j]), sl, -mx)) : 0.f;
@@ -409,7 +455,7 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         pe[j >> 1] = pack_bf16(e0, e1);
       }
       tmem_st16(lane_base + cS + 16 * c, pe);      // columns already read
-    }
+    });
     tmem_wait_st();
     tc_fence_before();
     arrive_w(bar_p);
@@ -482,9 +528,9 @@ int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const vo
   a.prefix = prefix;
   a.y = reinterpret_cast<__nv_bfloat16*>(y);
   a.redo = redo;
-  constexpr int smem = 2 * 128 * 2 * D + 4 * 128 * 128 + 1024 + 256 + 1024;
+  constexpr int smem = 2 * 128 * 2 * D + 4 * 128 * 128 + 4096 + 256 + 1024;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_walk<D>), smem) != FLARE_OK) return FLARE_ECUDA;
-  k_causal_tc_walk<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(tmQ, tmK, tmV, a);
+  launch_dep(k_causal_tc_walk<D>, dim3((unsigned)chunks, (unsigned)(p->B * p->H)), dim3(kThreadsW2), smem, st, tmQ, tmK, tmV, a);
   return FLARE_OK;
 }
 
@@ -496,7 +542,8 @@ int launch_record_tc(const FlareProblem* p, const void* q, const void* k, const 
   if (rc != FLARE_OK) return rc;
   constexpr int smem = 3 * 128 * 2 * D + 256 + 1024;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_record<D>), smem) != FLARE_OK) return FLARE_ECUDA;
-  k_causal_tc_record<D><<<dim3((unsigned)chunks, (unsigned)(p->B * p->H)), kThreadsW, smem, st>>>(L.tmQ, L.tmK, L.tmV, L.a, rec);
+  launch_dep(k_causal_tc_record<D>, dim3((unsigned)chunks, (unsigned)(p->B * p->H)), dim3(kThreadsW), smem, st, L.tmQ, L.tmK,
+             L.tmV, L.a, rec);
   return FLARE_OK;
 }
 
