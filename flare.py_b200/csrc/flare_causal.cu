@@ -46,70 +46,105 @@ int refuse(int code, const char* fmt, ...) {
 // ---------------------------------------------------------------------------------------------
 // pass 2: exclusive prefix of records along the chunk axis.  rec[c][row][D+2]; one warp per row.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads)
+constexpr int kScanThreads = 128;
+constexpr int kScanRows = 2;      // rows per warp, walked side by side
+
+template <int NPL>                // columns per lane: D <= 32 * NPL
+__global__ void __launch_bounds__(kScanThreads, NPL == 4 ? 5 : 8)
 k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, const float* __restrict__ state_in,
               float* __restrict__ state_out) {
   grid_dep_sync();
-  const long long row = (long long)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
-  if (row >= rows) return;
+  const long long row0 = ((long long)blockIdx.x * (kScanThreads / 32) + threadIdx.x / 32) * kScanRows;
+  if (row0 >= rows) return;
   const int W = D + 2;
   const long long cs = rows * W;
-  float m = -INFINITY, l = 0.f;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};             // D <= 128: four columns per lane
-  if (state_in) {
-    m = state_in[row * W + D]; l = state_in[row * W + D + 1];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) acc[i] = state_in[row * W + lane + 32 * i];
-  }
-  // kAhead records are in flight per warp while one is combined: a warp's chain is latency bound and a record is
-  // only (D + 2) floats, so the memory system needs several per warp to stay busy
+  // A warp's chain is latency bound and a record is only (D + 2) floats: two rows per warp and kAhead records of each
+  // in flight keep the memory system busy, and half as many warps fit the GPU in one wave.
   constexpr int kAhead = 4;
-  float mb[kAhead], lb[kAhead], ab[kAhead][4];
-  auto fetch = [&](int c, float& mo, float& lo, float (&ao)[4]) {
-    const float* r = rec + c * cs + row * W;
+  long long row[kScanRows];
+  bool on[kScanRows];
+  float m[kScanRows], l[kScanRows], acc[kScanRows][NPL];
+  float mb[kScanRows][kAhead], lb[kScanRows][kAhead], ab[kScanRows][kAhead][NPL];
+  auto fetch = [&](long long rw, int c, float& mo, float& lo, float (&ao)[NPL]) {
+    const float* r = rec + c * cs + rw * W;
     mo = r[D]; lo = r[D + 1];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) ao[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+    for (int i = 0; i < NPL; ++i) ao[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
   };
 #pragma unroll
-  for (int i = 0; i < kAhead; ++i) {
-    mb[i] = -INFINITY; lb[i] = 0.f;
+  for (int q = 0; q < kScanRows; ++q) {
+    on[q] = row0 + q < rows;
+    row[q] = on[q] ? row0 + q : row0;              // a row past the end repeats row0's loads and stores nothing
+    m[q] = -INFINITY; l[q] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) ab[i][j] = 0.f;
-    if (i < n_chunks) fetch(i, mb[i], lb[i], ab[i]);
+    for (int i = 0; i < NPL; ++i) acc[q][i] = 0.f;
+    if (state_in) {
+      m[q] = state_in[row[q] * W + D]; l[q] = state_in[row[q] * W + D + 1];
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) acc[q][i] = state_in[row[q] * W + lane + 32 * i];
+    }
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      mb[q][u] = -INFINITY; lb[q][u] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NPL; ++j) ab[q][u][j] = 0.f;
+      if (u < n_chunks) fetch(row[q], u, mb[q][u], lb[q][u], ab[q][u]);
+    }
   }
   for (int c0 = 0; c0 < n_chunks; c0 += kAhead) {
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
       const int c = c0 + u;
       if (c < n_chunks) {
-        float* r = rec + c * cs + row * W;
-        const float mc = mb[u], lc = lb[u];
-        float ac[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) ac[i] = ab[u][i];
-        if (c + kAhead < n_chunks) fetch(c + kAhead, mb[u], lb[u], ab[u]);
-        __syncwarp();
-        // the record of everything before chunk c
+        for (int q = 0; q < kScanRows; ++q) {
+          float* r = rec + c * cs + row[q] * W;
+          const float mc = mb[q][u], lc = lb[q][u];
+          float ac[NPL];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[i];
-        if (lane == 0) { r[D] = m; r[D + 1] = l; }
-        const float mn = fmaxf(m, mc);
-        const float wa = (m == -INFINITY) ? 0.f : __expf(m - mn);
-        const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
-        l = wa * l + wc * lc;
+          for (int i = 0; i < NPL; ++i) ac[i] = ab[q][u][i];
+          if (c + kAhead < n_chunks) fetch(row[q], c + kAhead, mb[q][u], lb[q][u], ab[q][u]);
+          __syncwarp();
+          if (on[q]) {                             // the record of everything before chunk c
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] = wa * acc[i] + wc * ac[i];
-        m = mn;
+            for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[q][i];
+            if (lane == 0) { r[D] = m[q]; r[D + 1] = l[q]; }
+          }
+          const float mn = fmaxf(m[q], mc);
+          const float wa = (m[q] == -INFINITY) ? 0.f : __expf(m[q] - mn);
+          const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
+          l[q] = wa * l[q] + wc * lc;
+#pragma unroll
+          for (int i = 0; i < NPL; ++i) acc[q][i] = wa * acc[q][i] + wc * ac[i];
+          m[q] = mn;
+        }
       }
     }
   }
   if (state_out) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) if (lane + 32 * i < D) state_out[row * W + lane + 32 * i] = acc[i];
-    if (lane == 0) { state_out[row * W + D] = m; state_out[row * W + D + 1] = l; }
+    for (int q = 0; q < kScanRows; ++q) {
+      if (on[q]) {
+#pragma unroll
+        for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) state_out[row[q] * W + lane + 32 * i] = acc[q][i];
+        if (lane == 0) { state_out[row[q] * W + D] = m[q]; state_out[row[q] * W + D + 1] = l[q]; }
+      }
+    }
   }
+}
+
+void launch_scan(bool dependent, float* rec, int n_chunks, long long rows, int D, const float* state_in, float* state_out,
+                 cudaStream_t st) {
+  const int rpb = kScanThreads / 32 * kScanRows;
+  const dim3 grid((unsigned)((rows + rpb - 1) / rpb)), block(kScanThreads);
+  auto go = [&](auto kernel) {
+    if (dependent) launch_dep(kernel, grid, block, 0, st, rec, n_chunks, rows, D, state_in, state_out);
+    else kernel<<<grid, block, 0, st>>>(rec, n_chunks, rows, D, state_in, state_out);
+  };
+  if (D <= 32) go(k_causal_scan<1>);
+  else if (D <= 64) go(k_causal_scan<2>);
+  else go(k_causal_scan<4>);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -382,8 +417,7 @@ namespace flare {
 // pass 2 for the backward (flare_causal_bwd.cu), which needs the same chunk-start records
 int launch_causal_scan(float* rec, int n_chunks, long long rows, int D, const float* state_in, float* state_out,
                        cudaStream_t st) {
-  const int rpb = kThreads / 32;
-  k_causal_scan<<<(unsigned)((rows + rpb - 1) / rpb), kThreads, 0, st>>>(rec, n_chunks, rows, D, state_in, state_out);
+  launch_scan(false, rec, n_chunks, rows, D, state_in, state_out, st);
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal scan: %s", cudaGetErrorString(e));
   return FLARE_OK;
@@ -419,9 +453,7 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   }
   // pass 2: exclusive prefix along the chunk axis
   const long long rows = (long long)p->B * p->H * p->M;
-  const int rpb = kThreads / 32;
-  launch_dep(k_causal_scan, dim3((unsigned)((rows + rpb - 1) / rpb)), dim3(kThreads), 0, st, workspace, chunks, rows, p->D,
-             state_in, state_out);
+  launch_scan(true, workspace, chunks, rows, p->D, state_in, state_out, st);
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;
   a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;
