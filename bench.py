@@ -664,6 +664,44 @@ def run_triple(args):
                           config=dict(workload=f"triple: B={B} H={H} N={N} D={D} fp16"))), flush=True)
 
 
+def run_causal_linear(args):
+    """Secondary workload (not the headline line): causal linear attention forward at the shape of the reference's
+    benchmark (lra/models/triton/causal_linear.py:589-650: B=8, H=8, N=2048, Dk=128, Dv=32), bf16, device-resident."""
+    import flare_b200 as fb
+    dev = torch.device("cuda:0")
+    B, H, Dk, Dv = 8, 8, 128, 32
+    N = args.tokens or 2048
+    g = torch.Generator().manual_seed(0)
+    # one call's tensors (84 MB at the default N) fit in L2: the calls rotate over enough input sets to exceed it
+    n_sets = max(2, -(-3 * 126_000_000 // (2 * B * H * N * (2 * Dk + 2 * Dv))))
+    sets = [((torch.randn(B, H, N, Dk, generator=g) * Dk ** -0.5).bfloat16().to(dev),
+             torch.randn(B, H, N, Dk, generator=g).bfloat16().to(dev),
+             torch.randn(B, H, N, Dv, generator=g).bfloat16().to(dev)) for _ in range(n_sets)]
+    for i in range(max(args.warmup, 3)):
+        fb.causal_linear(*sets[i % n_sets])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(200_000 * args.steps)          # the host enqueues ahead of the device: device time per call
+    e0.record()
+    for i in range(args.steps):
+        fb.causal_linear(*sets[i % n_sets])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    # q, k, v read and y written once (2 bytes each): the bound; the passes read k and v twice
+    pk = peaks()
+    alg_bytes = 2 * B * H * N * (2 * Dk + 2 * Dv)
+    alg_flops = 2.0 * B * H * N * (128 * Dk + 128 * Dv + 2 * Dk * Dv)      # per token: S row, S V, K^T V and Q P
+    roof = dict(bound="hbm", achieved=alg_bytes / (ms * 1e-3) / 1e9, peak=pk["hbm_gbs"], unit="GB/s",
+                frac=alg_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], traffic=None, peaks_source=pk["source"],
+                tensor_frac=alg_flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], kernel="k_cl_tc_sums / k_cl_tc_walk (tcgen05)")
+    print(json.dumps(dict(metric="causal linear attention fwd Mtokens/s", value=B * N / ms / 1e3, unit="Mtokens/s",
+                          n_gpus=1, steps=args.steps, warmup=max(args.warmup, 3), ms_per_step=ms, higher_is_better=True,
+                          dtype="bf16", data="synthetic", roofline=roof,
+                          config=dict(workload=f"causal_linear: B={B} H={H} N={N} Dk={Dk} Dv={Dv} bf16",
+                                      l2=f"calls rotate over {n_sets} input sets, more than L2 together"))), flush=True)
+
+
 def run_sdpa_gpu(args):
     """Secondary line (not the headline): the kernels the reference dispatches for this path on this GPU, i.e.
     its two F.scaled_dot_product_attention calls (README.md:49-50) and their autograd in bf16 through the
@@ -792,15 +830,17 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-sustained", action="store_true", help="skip the two-second sustained leg")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch every step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "triple", "sdpa_gpu", "cp_encoder"],
+    ap.add_argument("--workload", default="mixer", choices=["mixer", "causal", "triple", "causal_linear", "sdpa_gpu", "cp_encoder"],
                     help="mixer: the headline line; causal: a secondary line for causal prefill/decode/training; triple: a "
-                         "secondary line for triple attention; sdpa_gpu: "
+                         "secondary line for triple attention; causal_linear: a secondary line for causal linear attention; sdpa_gpu: "
                          "a secondary line timing the reference's own two SDPA calls + autograd on this GPU")
     args = ap.parse_args()
     if args.workload == "causal":
         run_causal(args)
     elif args.workload == "triple":
         run_triple(args)
+    elif args.workload == "causal_linear":
+        run_causal_linear(args)
     elif args.workload == "sdpa_gpu":
         run_sdpa_gpu(args)
     elif args.workload == "cp_encoder":

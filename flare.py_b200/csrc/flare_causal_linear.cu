@@ -10,6 +10,7 @@
 #include <cstdio>
 #include <cuda_runtime.h>
 #include "common.cuh"
+#include "launch.h"
 
 namespace flare { void set_last_error(const char* msg); }
 
@@ -170,7 +171,9 @@ extern "C" {
 
 size_t flare_causal_linear_workspace_bytes(int B, int H, int N, int Dk, int Dv) {
   if (B < 1 || H < 1 || N < 1 || Dk < 1 || Dv < 1) return 0;
-  return (size_t)B * H * pick_segments(B, H, N) * Dk * Dv * sizeof(float) + 256;
+  const size_t simt = (size_t)B * H * pick_segments(B, H, N) * Dk * Dv * sizeof(float) + 256;
+  const size_t tc = (Dk == 128 && (Dv == 32 || Dv == 64)) ? flare::causal_linear_tc_workspace(B, H, N, Dk, Dv) : 0;
+  return simt > tc ? simt : tc;
 }
 
 int flare_causal_linear(int B, int H, int N, int Dk, int Dv, int dtype, const void* q, const int64_t* q_stride,
@@ -181,6 +184,14 @@ int flare_causal_linear(int B, int H, int N, int Dk, int Dv, int dtype, const vo
   if ((long long)B * H > 65535) return refuse(FLARE_EUNSUPPORTED, "causal_linear: B*H > 65535");
   if (!q || !k || !v || !y || !workspace || !q_stride || !k_stride || !v_stride || !y_stride)
     return refuse(FLARE_EINVAL, "causal_linear: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (flare::causal_linear_tc_supported(B, H, N, Dk, Dv, dtype, q, q_stride, k, k_stride, v, v_stride, y, y_stride)) {
+    const int rc = flare::causal_linear_tc(B, H, N, Dv, dtype, q, q_stride, k, k_stride, v, v_stride, y, y_stride, workspace, st);
+    if (rc != FLARE_OK) return refuse(rc, "causal_linear: the tensor-core passes could not be launched");
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal_linear: %s", cudaGetErrorString(e));
+    return FLARE_OK;
+  }
   ClArgs a;
   a.B = B; a.H = H; a.N = N; a.Dk = Dk; a.Dv = Dv;
   a.n_seg = pick_segments(B, H, N);
@@ -188,7 +199,6 @@ int flare_causal_linear(int B, int H, int N, int Dk, int Dv, int dtype, const vo
   a.n_seg = (N + a.seg_len - 1) / a.seg_len;
   for (int i = 0; i < 3; ++i) { a.qs[i] = q_stride[i]; a.ks[i] = k_stride[i]; a.vs[i] = v_stride[i]; a.ys[i] = y_stride[i]; }
   a.q = q; a.k = k; a.v = v; a.y = y; a.segsum = workspace;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case FLARE_F32: return run<float>(a, st);
     case FLARE_F16: return run<__half>(a, st);

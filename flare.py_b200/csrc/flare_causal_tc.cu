@@ -54,40 +54,6 @@ __device__ __forceinline__ void row_sync() {       // the 128 row threads
   asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
-// The wait for outstanding tensor-memory loads, written as a dependency of the registers they fill, so that no use
-// of them can be scheduled ahead of it.
-__device__ __forceinline__ void tmem_wait_ld_on(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :: "memory");
-}
-// One pass over a thread's 128-column row in four blocks of 32: block c + 1 is in flight while f works on block c.
-template <typename F>
-__device__ __forceinline__ void row_pass(uint32_t taddr, F&& f) {
-  uint32_t v[2][32];
-  tmem_ld32(taddr, v[0]);
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    tmem_wait_ld_on(v[c & 1]);
-    if (c + 1 < 4) tmem_ld32(taddr + 32 * (c + 1), v[(c + 1) & 1]);
-    f(c, v[c & 1]);
-  }
-}
-
-// Half a row (64 columns) in two blocks of 32.
-template <typename F>
-__device__ __forceinline__ void row_half_pass(uint32_t taddr, F&& f) {
-  uint32_t v[2][32];
-  tmem_ld32(taddr, v[0]);
-  tmem_wait_ld_on(v[0]);
-  tmem_ld32(taddr + 32, v[1]);
-  f(0, v[0]);
-  tmem_wait_ld_on(v[1]);
-  f(1, v[1]);
-}
 __device__ __forceinline__ void rows_sync() {      // the 256 row threads
   asm volatile("bar.sync 1, 256;" ::: "memory");
 }

@@ -80,6 +80,15 @@ int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const 
 int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
                    int* redo, int chunks, cudaStream_t st);
 
+// Causal linear attention on the tensor cores (flare_causal_linear_tc.cu): 16-bit inputs, Dk = 128, Dv in {32, 64}.
+bool causal_linear_tc_supported(int B, int H, int N, int Dk, int Dv, int dtype, const void* q, const int64_t* qs,
+                                const void* k, const int64_t* ks, const void* v, const int64_t* vs, const void* y,
+                                const int64_t* ys);
+size_t causal_linear_tc_workspace(int B, int H, int N, int Dk, int Dv);
+int causal_linear_tc(int B, int H, int N, int Dv, int dtype, const void* q, const int64_t* qs, const void* k,
+                     const int64_t* ks, const void* v, const int64_t* vs, void* y, const int64_t* ys, float* workspace,
+                     cudaStream_t st);
+
 // Triple attention on the tensor cores (flare_triple_tc.cu): 16-bit inputs, every feature dimension 32.
 bool triple_tc_supported(int N, int D0, int D1, int D2, int dtype);
 bool triple_tc_strides_ok(long long sx, long long sy, long long sz);

@@ -45,4 +45,25 @@ inline bool make_tile_map(CUtensorMap* map, const void* base, int dtype16, int D
   return r == CUDA_SUCCESS;
 }
 
+// Same tensor, but a box of `box_cols` of its D columns (a multiple of 8; 2 * box_cols bytes per tile row, which picks the
+// swizzle): rows wider than one 128-byte swizzle span are fetched as several column blocks, each a tile of its own.
+inline bool make_tile_map_cols(CUtensorMap* map, const void* base, int dtype16, int D, int box_cols, uint64_t rows,
+                               uint64_t d2, uint64_t d3, uint64_t stride_row_b, uint64_t stride_d2_b,
+                               uint64_t stride_d3_b, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (!enc) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, rows, d2, d3};
+  cuuint64_t strides[3] = {stride_row_b, stride_d2_b, stride_d3_b};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  const int rowb = 2 * box_cols;
+  if (rowb != 32 && rowb != 64 && rowb != 128) return false;
+  CUtensorMapSwizzle sw = rowb == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                          : rowb == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B;
+  CUresult r = enc(map, dtype16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace flare

@@ -268,7 +268,8 @@ int flare_causal_bwd(const FlareProblem* p, const void* q, const void* k, const 
 /* Causal linear attention, Y_t = Q_t . sum_{n<=t} K_n^T V_n / N (lra/models/triton/causal_linear.py:23-145;
  * reference form :317-336; forward only, as there).  q, k: [B,H,N,Dk]; v, y: [B,H,N,Dv]; strides in
  * elements for dims (b, h, n), unit stride on the last dim.  workspace:
- * flare_causal_linear_workspace_bytes bytes.  Dk, Dv up to 256. */
+ * flare_causal_linear_workspace_bytes bytes.  Dk, Dv up to 256.  16-bit inputs with Dk = 128, Dv in {32, 64}
+ * and 16-byte aligned rows run as three tensor-core passes over 128-token chunks; the rest on fp32 kernels. */
 size_t flare_causal_linear_workspace_bytes(int B, int H, int N, int Dk, int Dv);
 int flare_causal_linear(int B, int H, int N, int Dk, int Dv, int dtype, const void* q, const int64_t* q_stride,
                         const void* k, const int64_t* k_stride, const void* v, const int64_t* v_stride,

@@ -122,6 +122,28 @@ def test_causal_linear(cuda_dev, B, H, N, Dk, Dv, dtype):
     assert O.rel_l2(y.double().cpu(), y_ref.double()) <= TOL[dtype]
 
 
+@pytest.mark.parametrize("B,H,N,Dv,dtype", [
+    (2, 2, 1000, 64, torch.float16),          # ragged last chunk
+    (1, 2, 130, 32, torch.bfloat16),
+    (8, 8, 2048, 32, torch.bfloat16),         # the shape of the reference's main()
+    (1, 1, 7, 32, torch.float16),
+])
+def test_causal_linear_tensor_core_shapes(cuda_dev, B, H, N, Dv, dtype):
+    """16-bit inputs with Dk = 128 and Dv in {32, 64} run on the tensor cores; q, k, v as head-interleaved views."""
+    import flare_b200 as fb
+    Dk = 128
+    qf = _rand((B, N, H * Dk), dtype, 0, Dk ** -0.5).to(cuda_dev)
+    kf = _rand((B, N, H * Dk), dtype, 1).to(cuda_dev)
+    vf = _rand((B, N, H * Dv), dtype, 2).to(cuda_dev)
+    q, k = (t.view(B, N, H, Dk).permute(0, 2, 1, 3) for t in (qf, kf))
+    v = vf.view(B, N, H, Dv).permute(0, 2, 1, 3)
+    y = fb.causal_linear(q, k, v)
+    torch.cuda.synchronize()
+    assert fb.device_status() == 0
+    y_ref = O.causal_linear(q.double().cpu(), k.double().cpu(), v.double().cpu())
+    assert O.rel_l2(y.double().cpu(), y_ref.double()) <= TOL[dtype]
+
+
 def test_causal_linear_strided_views(cuda_dev):
     """q, k, v as 'b n (h d) -> b h n d' views, as the lra blocks make them."""
     import flare_b200 as fb
