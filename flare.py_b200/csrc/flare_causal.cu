@@ -160,7 +160,8 @@ struct CausalArgs {
   const float* prefix;         // [n_chunks][B][H][M][D+2]: the record before each chunk
   float* state;                // decode: [B][H][M][D+2], updated in place (prefix == nullptr)
   int tokens_per_cta;          // kChunk in prefill, N (usually 1) in decode
-  const int* redo;             // prefill behind the tensor-core walk: [chunks][B*H], CTAs whose flag is 0 return
+  const int* redo;             // prefill behind the tensor-core walk: [chunks][B*H], only the flagged units are walked
+  int n_units;                 // chunks * B * H (redo mode)
 };
 
 template <typename T, int D>
@@ -187,8 +188,24 @@ k_causal_walk(CausalArgs a) {
   const int tid = threadIdx.x;
   const int d = tid % D, g = tid / D;
   const int nlat = M / G;                          // latents of this thread: g * nlat ... g * nlat + nlat - 1
-  const int chunk = blockIdx.x, bh = blockIdx.y;
-  if (a.redo && a.redo[chunk * gridDim.y + bh] == 0) return;
+  // Redo mode (behind the tensor-core walk): a small one-dimensional grid strides over the (chunk, b*h) units and
+  // takes the flagged ones; otherwise one CTA per unit.
+  const int n_bh = a.B * a.H;
+  int next_base = blockIdx.x, cur_base = 0;
+  unsigned flagged = 0;                            // of the units cur_base + lane * gridDim.x: the same in every warp
+  for (;;) {
+  int chunk = blockIdx.x, bh = blockIdx.y;
+  if (a.redo) {
+    while (flagged == 0 && next_base < a.n_units) {                    // 32 flags per round, read side by side
+      cur_base = next_base; next_base += 32 * (int)gridDim.x;
+      const int u = cur_base + (tid & 31) * (int)gridDim.x;
+      flagged = __ballot_sync(0xffffffffu, u < a.n_units && a.redo[u] != 0);
+    }
+    if (flagged == 0) break;
+    const int unit = cur_base + (__ffs(flagged) - 1) * (int)gridDim.x;
+    flagged &= flagged - 1;
+    chunk = unit / n_bh; bh = unit % n_bh;
+  }
   const int b = bh / a.H, h = bh % a.H;
   const int n0 = chunk * a.tokens_per_cta, n1 = min(a.N, n0 + a.tokens_per_cta);
   const int W = D + 2;
@@ -357,6 +374,9 @@ k_causal_walk(CausalArgs a) {
     for (int j = 0; j < kMaxLat; ++j) if (j < nlat) st[(g * nlat + j) * W + d] = acc[j];
     for (int m = tid; m < M; m += kThreads) { st[m * W + D] = sMu[m]; st[m * W + D + 1] = sL[m]; }
   }
+  if (!a.redo) break;
+  __syncthreads();                                 // the next unit reuses the shared arrays
+  }
 }
 
 size_t walk_smem(int M, int D) {
@@ -369,7 +389,9 @@ int launch_walk(const CausalArgs& a, int n_cta_x, cudaStream_t st) {
   if (smem > 227 * 1024) return refuse(FLARE_EUNSUPPORTED, "causal: M=%d D=%d needs %zu bytes of shared memory", a.M, D, smem);
   cudaError_t e = cudaFuncSetAttribute(k_causal_walk<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
-  launch_dep(k_causal_walk<T, D>, dim3((unsigned)n_cta_x, (unsigned)(a.B * a.H)), dim3(kThreads), smem, st, a);
+  const dim3 grid = a.redo ? dim3((unsigned)(a.n_units < 2 * 148 ? a.n_units : 2 * 148))
+                           : dim3((unsigned)n_cta_x, (unsigned)(a.B * a.H));
+  launch_dep(k_causal_walk<T, D>, grid, dim3(kThreads), smem, st, a);
   e = cudaPeekAtLastError();
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal: %s", cudaGetErrorString(e));
   return FLARE_OK;
@@ -397,7 +419,7 @@ int fill_args(const FlareProblem* p, CausalArgs* a) {
   if (p->M % G != 0 || p->M / G > kMaxLat)
     return refuse(FLARE_EUNSUPPORTED, "causal: M=%d must be a multiple of %d and at most %d for D=%d", p->M, G, G * kMaxLat, D);
   a->B = p->B; a->H = p->H; a->N = p->N; a->M = p->M; a->D = D; a->scale = p->scale;
-  a->redo = nullptr;
+  a->redo = nullptr; a->n_units = 0;
   for (int i = 0; i < 3; ++i) { a->qs[i] = p->q_stride[i]; a->ks[i] = p->k_stride[i]; a->vs[i] = p->v_stride[i]; a->ys[i] = p->y_stride[i]; }
   return FLARE_OK;
 }
@@ -465,7 +487,7 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
     if (rc != FLARE_OK) return refuse(rc, "causal_prefill: tensor-core walk could not be launched");
     const cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal_prefill: %s", cudaGetErrorString(e));
-    a.redo = redo;
+    a.redo = redo; a.n_units = chunks * p->B * p->H;
   }
   return run_walk(p, a, chunks, st);
 }

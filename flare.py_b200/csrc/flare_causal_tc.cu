@@ -22,6 +22,7 @@
 // of fp32 before that maximum is reached.  A chunk whose scores climb by more than 64 octaves is flagged and
 // redone by the fp32 walk, which carries a running maximum.  Two CTAs per SM (256 tensor-memory columns and
 // under 100 KB of shared memory each) so that one chunk's products and loads overlap another's arithmetic.
+#include <type_traits>
 #include "common.cuh"
 #include "launch.h"
 #include "tc_common.cuh"
@@ -177,16 +178,19 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
     mbar_wait(bar_s, 0, a.status, abort_flag);
     tc_fence_after();
+    // Steps 2 to 5, compiled twice: a full chunk with all 128 latents needs none of the per-score bounds tests.
+    auto steps = [&](auto full_chunk) {
+    constexpr bool FULL = decltype(full_chunk)::value;
     // ---- step 2: token r over the latents 64 hb ... 64 hb + 63: maximum and sum relative to it ----
     {
       float mx = -INFINITY, su = 0.f;
       row_half_pass(lane_base + cST + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < M) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
+        for (int j = 0; j < 32; ++j) if (FULL || 64 * hb + 32 * c + j < M) mx = fmaxf(mx, __uint_as_float(v[j]) * sl);
       });
       row_half_pass(lane_base + cST + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < M) su += ex2(fmaf(__uint_as_float(v[j]), sl, -mx));
+        for (int j = 0; j < 32; ++j) if (FULL || 64 * hb + 32 * c + j < M) su += ex2(fmaf(__uint_as_float(v[j]), sl, -mx));
       });
       sPart[hb * 128 + r] = make_float2(mx, su);
     }
@@ -196,7 +200,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       float mp = -INFINITY;
       row_half_pass(lane_base + cS + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) if (64 * hb + 32 * c + j < cnt) mp = fmaxf(mp, __uint_as_float(v[j]) * sl);
+        for (int j = 0; j < 32; ++j) if (FULL || 64 * hb + 32 * c + j < cnt) mp = fmaxf(mp, __uint_as_float(v[j]) * sl);
         if (c == 0) first = fmaxf(first, __uint_as_float(v[0]) * sl);
       });
       sMuP[hb * 128 + r] = mp;
@@ -224,7 +228,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         row_half_pass(lane_base + cS, [&](int c, const uint32_t (&v)[32]) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            l += (live && 32 * c + j < cnt) ? ex2(fmaf(__uint_as_float(v[j]), sl, -mu)) : 0.f;
+            l += (FULL || (live && 32 * c + j < cnt)) ? ex2(fmaf(__uint_as_float(v[j]), sl, -mu)) : 0.f;
         });
       }
       uint8_t* eh = sE + hb * kHalf;
@@ -238,12 +242,12 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           for (int u = 0; u < 2; ++u) {
             const int t = 64 * hb + 32 * c + j + u;
             const float x = __uint_as_float(v[j + u]);
-            const bool in = live && t < cnt;
+            const bool in = FULL || (live && t < cnt);
             const float e = in ? ex2(fmaf(x, sl, -mu)) : 0.f;
             l += e;
             const float A = in ? ex2(fmaf(x, sl, -sCmax[t])) * sCinv[t] : 0.f;
             e2[u] = e;
-            g2[u] = l > 0.f ? __fdividef(A, l) : 0.f;
+            g2[u] = (FULL || l > 0.f) ? __fdividef(A, l) : 0.f;   // l = 0 only in a chunk that is flagged and redone
           }
           pe[j >> 1] = pack_bf16(e2[0], e2[1]);
           pg[j >> 1] = pack_bf16(g2[0], g2[1]);
@@ -261,7 +265,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int cc = 0; cc < CPR / 2; ++cc) {
         const int c = hb * (CPR / 2) + cc;
         uint4 o = make_uint4(0, 0, 0, 0);
-        if (live) {
+        if (FULL || live) {
           const float2* x = reinterpret_cast<const float2*>(rec + 8 * c);   // records are D + 2 floats: 8-byte aligned
           const float2 x0 = x[0], x1 = x[1], x2 = x[2], x3 = x[3];
           o = make_uint4(pack_bf16(x0.x * aa, x0.y * aa), pack_bf16(x1.x * aa, x1.y * aa), pack_bf16(x2.x * aa, x2.y * aa),
@@ -287,12 +291,21 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     } else {
       row_half_pass(lane_base + cW + 64 * hb, [&](int c, const uint32_t (&v)[32]) {
         uint32_t pw[16];
+        const int cb = 2 * hb + c, rb = warp & 3;  // column block against this warp's row block: the same for all lanes
+        if (FULL && cb < rb) {                     // below the diagonal: nothing to mask
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const int n = 64 * hb + 32 * c + j;
-          const float w0 = (n <= r && n < cnt) ? __uint_as_float(v[j]) : 0.f;
-          const float w1 = (n + 1 <= r && n + 1 < cnt) ? __uint_as_float(v[j + 1]) : 0.f;
-          pw[j >> 1] = pack_bf16(w0, w1);
+          for (int j = 0; j < 32; j += 2) pw[j >> 1] = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+        } else if (cb > rb) {                      // above it: nothing to keep
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pw[j] = 0u;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int n = 64 * hb + 32 * c + j;
+            const float w0 = (n <= r && (FULL || n < cnt)) ? __uint_as_float(v[j]) : 0.f;
+            const float w1 = (n + 1 <= r && (FULL || n + 1 < cnt)) ? __uint_as_float(v[j + 1]) : 0.f;
+            pw[j >> 1] = pack_bf16(w0, w1);
+          }
         }
         tmem_st16(lane_base + cWp + 32 * hb + 16 * c, pw);
       });
@@ -300,6 +313,9 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tmem_wait_st();
     tc_fence_before();
     arrive_w(bar_wp);
+    };                                             // steps
+    if (cnt == 128 && M == 128) steps(std::true_type{});
+    else steps(std::false_type{});
 
     // ---- step 7: Y of token r, half of its D values -> y ----
     mbar_wait(bar_y, 0, a.status, abort_flag);
