@@ -62,18 +62,17 @@ k_cl_tc_sums(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
     abort_flag[0] = 0;
     fence_barrier_init();
     prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+    // the loads start before tensor memory is allocated and the CTA has met
+    mbar_expect_tx(bar_load, 2 * kHalf + kTileV);
+    tma_load_4d(sK, &tmK, bar_load, 0, chunk * 128, h, b);              // rows past N arrive as zeros
+    tma_load_4d(sK + kHalf, &tmK, bar_load, 64, chunk * 128, h, b);
+    tma_load_4d(sV, &tmV, bar_load, 0, chunk * 128, h, b);
   }
   if (warp == 0) tmem_alloc<64>(tmem_slot);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 2 * kHalf + kTileV);
-    tma_load_4d(sK, &tmK, bar_load, 0, chunk * 128, h, b);              // rows past N arrive as zeros
-    tma_load_4d(sK + kHalf, &tmK, bar_load, 64, chunk * 128, h, b);
-    tma_load_4d(sV, &tmV, bar_load, 0, chunk * 128, h, b);
-  }
   if (warp == 4) {
     // A = K^T: contraction over the tokens (rows), Dk across two 64-column blocks; B = V rows, contiguous along Dv
     const uint32_t id = idesc_f16(128, DV, F, F, 1, 1);
@@ -163,14 +162,7 @@ k_cl_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     abort_flag[0] = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmP);
-  }
-  if (warp == 0) tmem_alloc<256>(tmem_slot);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  constexpr uint32_t cS = 0, cY = 128, cSp = 192;  // S fp32, Y, S masked and packed
-  if (tid == 0) {
+    // the loads start before tensor memory is allocated and the CTA has met
     mbar_expect_tx(bar_load, 4 * kHalf + 2 * kTileV);
     tma_load_4d(sQ, &tmQ, bar_load, 0, n0, h, b);
     tma_load_4d(sQ + kHalf, &tmQ, bar_load, 64, n0, h, b);
@@ -179,6 +171,12 @@ k_cl_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
     tma_load_4d(sP, &tmP, bar_load, 0, 0, chunk, bh);
   }
+  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  constexpr uint32_t cS = 0, cY = 128, cSp = 192;  // S fp32, Y, S masked and packed
   if (warp == kRowT / 32) {
     const uint32_t id_s = idesc_f16(128, 128, F, F, 0, 0);            // S: A = Q, B = K, both K-major
     const uint32_t id_y0 = idesc_f16(128, DV, F, F, 0, 1);            // Y = Q P: B rows are the contraction index

@@ -110,6 +110,11 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     abort_flag[1] = 0;                             // range flag of this chunk
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+    // the loads start before tensor memory is allocated and the CTA has met
+    mbar_expect_tx(bar_load, 3 * kTile);
+    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);      // rows past M arrive as zeros
+    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);                       // rows past N arrive as zeros
+    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
   }
   if (warp == 0) tmem_alloc<256>(tmem_slot);
   tc_fence_before();
@@ -118,12 +123,6 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem = *tmem_slot;
   // W takes the columns of S once every latent thread has read its row, Y those of S^T; the packed W sits behind Y
   constexpr uint32_t cS = 0, cST = 128, cW = 0, cY = 128, cWp = 192;
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 3 * kTile);
-    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);      // rows past M arrive as zeros
-    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);                       // rows past N arrive as zeros
-    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
-  }
 
   if (warp == kRowT / 32) {
     // ================= issuing warp =================
@@ -381,6 +380,11 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     abort_flag[0] = 0;
     fence_barrier_init();
     prefetch_tmap(&tmQ); prefetch_tmap(&tmK); prefetch_tmap(&tmV);
+    // the loads start before tensor memory is allocated and the CTA has met
+    mbar_expect_tx(bar_load, 3 * kTile);
+    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);
+    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);
+    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
   }
   if (warp == 0) tmem_alloc<128>(tmem_slot);
   tc_fence_before();
@@ -388,12 +392,6 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   constexpr uint32_t cS = 0, cAcc = 64;            // E packed occupies columns [0, 64) when acc is written
-  if (tid == 0) {
-    mbar_expect_tx(bar_load, 3 * kTile);
-    tma_load_4d(sQ, &tmQ, bar_load, 0, 0, h, a.q_batched ? b : 0);
-    tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);
-    tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
-  }
 
   const int r = tid;
   const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
