@@ -9,9 +9,10 @@
 //   1. S [latent lanes x token columns] and S^T [token lanes x latent columns]: two tcgen05 products, so that
 //      the softmax over the latents (per token) and the running sum over the tokens (per latent) are both walks
 //      along a thread's own tensor-memory row
-//   2. token threads: column maximum and sum of S^T -> shared memory (128 + 128 floats)
-//   3. latent threads: mu, a, E, l (running sum), G; E and G rows as bf16 into shared memory, laid out as the
-//      MN-major operands of the next product (contraction over the latents); a * acc0 as bf16 beside them
+//   2. token threads: column maximum and sum of S^T -> one factor w_t per token in shared memory
+//   3. latent threads: mu, a, E, l (running sum), A = E u_m w_t, G = A / l; E and G rows as bf16 into shared
+//      memory, laid out as the MN-major operands of the next product (contraction over the latents); a * acc0
+//      as bf16 beside them
 //   4. W = G^T E (token lanes x token columns) and Y = G^T (a acc0): products from shared memory
 //   5. token threads: W masked to n <= t, packed to bf16 in place in tensor memory
 //   6. Y += W V: A operand from tensor memory, V tile as loaded by TMA
@@ -82,8 +83,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sV = sE + 2 * kHalf;
   uint8_t* sA0 = sV + kTile;                       // a_m acc0_m as bf16: [latent][D]
   static_assert(2 * kTile <= 2 * kHalf, "Q and K must fit in the G tile");
-  float* sCmax = reinterpret_cast<float*>(sA0 + kTile);      // [128] column maximum (log2 units)
-  float* sCinv = sCmax + 128;                      // [128] 1 / column sum (0 past the end of the sequence)
+  float* sCinv = reinterpret_cast<float*>(sA0 + kTile);      // [128] w_t (0 past the end of the sequence)
   float2* sPart = reinterpret_cast<float2*>(sCinv + 128);    // [2][128] (maximum, sum) of a token over half the latents
   float* sMuP = reinterpret_cast<float*>(sPart + 256);       // [2][128] maximum of a latent over half the tokens
   uint64_t* bars = reinterpret_cast<uint64_t*>(sMuP + 256);
@@ -127,13 +127,13 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == kRowT / 32) {
     // ================= issuing warp =================
     const uint32_t id_s = idesc_f16(128, 128, 1, 1, 0, 0);          // S, S^T: A, B K-major
-    const uint32_t id_w = idesc_f16(128, 64, 1, 1, 1, 1);           // W halves: A = G, B = E, both MN-major
+    const uint32_t id_w = idesc_f16(128, 128, 1, 1, 1, 1);          // W: A = G, B = E, both MN-major over two 64-token blocks
     const uint32_t id_y0 = idesc_f16(128, D, 1, 1, 1, 1);           // Y = G^T (a acc0): A, B MN-major
     const uint32_t id_y1 = idesc_f16(128, D, 1, 1, 0, 1);           // Y += W V: A in tensor memory, B MN-major
     const uint64_t dQ = smem_desc<ROWB>(smem_u32(sQ)), dK = smem_desc<ROWB>(smem_u32(sK)), dV = smem_desc<ROWB>(smem_u32(sV)),
                    dA0 = smem_desc<ROWB>(smem_u32(sA0));
     const uint64_t dG = smem_desc_mn128(smem_u32(sG), kHalf, 1024);
-    const uint64_t dE0 = smem_desc<128>(smem_u32(sE)), dE1 = smem_desc<128>(smem_u32(sE + kHalf));
+    const uint64_t dE = smem_desc_mn128(smem_u32(sE), kHalf, 1024);
     mbar_wait(bar_load, 0, a.status, abort_flag);
     tc_fence_after();
     if (elect_one()) {
@@ -149,8 +149,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (elect_one()) {
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {             // contraction over the latents, 16 per product
-        mma_ss(tmem + cW, dG + 128 * kk, dE0 + 128 * kk, id_w, kk > 0);
-        mma_ss(tmem + cW + 64, dG + 128 * kk, dE1 + 128 * kk, id_w, kk > 0);
+        mma_ss(tmem + cW, dG + 128 * kk, dE + 128 * kk, id_w, kk > 0);
         mma_ss(tmem + cY, dG + 128 * kk, dA0 + (uint64_t)(kk * ROWB), id_y0, kk > 0);
       }
       mma_commit(bar_w);
@@ -174,6 +173,9 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float* rec = a.prefix + ((((long long)chunk * a.B + b) * a.H + h) * M + min(r, M - 1)) * W;
     const float m0 = rec[D], l0 = rec[D + 1];
     const bool live = r < M;
+    // its acc0 half is read at the end of step 3: bring the two lines it spans close now
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(rec + hb * (D / 2)));
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(rec + hb * (D / 2) + D / 2 - 1));
 
     mbar_wait(bar_s, 0, a.status, abort_flag);
     tc_fence_after();
@@ -205,13 +207,19 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       sMuP[hb * 128 + r] = mp;
     }
     rows_sync();
+    // A_mt = 2^(S_mt - cmax_t) / csum_t is formed from the exponential that E needs anyway:
+    //   A_mt = E_mt * u_m * w_t,   u_m = 2^(mu_m - c0),   w_t = 2^(c0 - cmax_t) / csum_t,
+    // with c0 the column maximum of the chunk's first token (every thread reads it from the same two words).
+    // |mu_m - c0| and |cmax_t - c0| are kept within 50 octaves, so that no factor leaves fp32's range while A_mt
+    // still matters; a chunk outside that is flagged and redone like one whose scores climb too far.
+    const float c0 = fmaxf(sPart[0].x, sPart[128].x);
     if (hb == 0) {                                 // the two halves of token r's statistics
       const float2 p0 = sPart[r], p1 = sPart[128 + r];
       const float cm = fmaxf(p0.x, p1.x);
       const float cs = p0.y * ex2(p0.x - cm) + (p1.x == -INFINITY ? 0.f : p1.y * ex2(p1.x - cm));
       const bool in = r < cnt;
-      sCmax[r] = in ? cm : 0.f;
-      sCinv[r] = in ? 1.f / cs : 0.f;
+      sCinv[r] = in ? __fdividef(ex2(c0 - cm), cs) : 0.f;
+      if (in && fabsf(c0 - cm) > 50.f) abort_flag[1] = 1;
     }
     const float mu = fmaxf(m0 * kLog2e, fmaxf(sMuP[r], sMuP[128 + r]));   // the record keeps m in natural-log units
     rows_sync();
@@ -220,7 +228,8 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     {
       // E and l are relative to the chunk's final maximum: l_mt >= 2^(first - mu).  Past 64 octaves the chunk is
       // handed to the walk that carries a running maximum (flagged; its y overwrites this kernel's).
-      if (hb == 0 && live && mu - first > 64.f) abort_flag[1] = 1;
+      if (hb == 0 && live && (mu - first > 64.f || fabsf(mu - c0) > 50.f)) abort_flag[1] = 1;
+      const float um = live ? ex2(fminf(fmaxf(mu - c0, -60.f), 60.f)) : 0.f;
       const float aa = (m0 == -INFINITY) ? 0.f : ex2(m0 * kLog2e - mu);
       float l = aa * l0;
       if (hb == 1) {                               // the sum over the first half, in the order its owner adds it
@@ -244,7 +253,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const bool in = FULL || (live && t < cnt);
             const float e = in ? ex2(fmaf(x, sl, -mu)) : 0.f;
             l += e;
-            const float A = in ? ex2(fmaf(x, sl, -sCmax[t])) * sCinv[t] : 0.f;
+            const float A = e * (um * sCinv[t]);
             e2[u] = e;
             g2[u] = (FULL || l > 0.f) ? __fdividef(A, l) : 0.f;   // l = 0 only in a chunk that is flagged and redone
           }
