@@ -313,9 +313,14 @@ def _mixer_setup(ctx, inputs, output):
     y, z32, lse_m, lse_n = output
     ctx.save_for_backward(q, k, v, y, z32, lse_m, lse_n, key_mask)
     ctx.scale, ctx.dropout = scale, (dropout_p, dropout_seed)
+    # z32, lse_m, lse_n are the backward's operands, not results anyone differentiates: without this the engine
+    # fills a zero tensor for each of them on every backward (one of them B*H*N floats)
+    ctx.set_materialize_grads(False)
 
 
 def _mixer_backward(ctx, dy, _dz32, _dlm, _dln):
+    if dy is None:
+        return None, None, None, None, None, None, None
     q, k, v, y, z32, lse_m, lse_n, key_mask = ctx.saved_tensors
     dq, dk, dv = _op_mixer_bwd(q, k, v, dy, y, z32, lse_m, lse_n, ctx.scale, key_mask, *ctx.dropout)
     return dq.to(q.dtype), dk, dv, None, None, None, None
@@ -353,9 +358,12 @@ def _gather_setup(ctx, inputs, output):
     _z, z32, lse_m = output
     ctx.save_for_backward(q, k, v, z32, lse_m, key_mask)
     ctx.scale = scale
+    ctx.set_materialize_grads(False)
 
 
 def _gather_backward(ctx, dz, _dz32, _dlse):
+    if dz is None:
+        return None, None, None, None, None
     q, k, v, z32, lse_m, key_mask = ctx.saved_tensors
     dq, dk, dv = _op_gather_bwd(q, k, v, dz.contiguous(), z32, lse_m, ctx.scale, key_mask)
     return dq.to(q.dtype), dk, dv, None, None
@@ -391,9 +399,12 @@ def _scatter_setup(ctx, inputs, output):
     y, lse_n = output
     ctx.save_for_backward(q, k, z, y, lse_n, key_mask)
     ctx.scale = scale
+    ctx.set_materialize_grads(False)
 
 
 def _scatter_backward(ctx, dy, _dlse):
+    if dy is None:
+        return None, None, None, None, None
     q, k, z, y, lse_n, key_mask = ctx.saved_tensors
     dq, dk, dz32 = _op_scatter_bwd(q, k, z, dy, y, lse_n, ctx.scale, key_mask)
     return dq.to(q.dtype), dk, dz32.to(z.dtype), None, None
