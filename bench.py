@@ -590,6 +590,19 @@ def run_causal(args):
     k1, v1 = k[:, :, :1].contiguous(), v[:, :, :1].contiguous()
     fb.flare_causal_decode(q, k1, v1, st, 1.0)
     us = timed(lambda: fb.flare_causal_decode(q, k1, v1, st, 1.0), max(args.steps, 20)) * 1e3
+    # the serving loop as it would run: 16 decode steps recorded once in a CUDA graph over static buffers and the
+    # in-place state, replayed; device time per step without the host's launch cost
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        fb.flare_causal_decode(q, k1, v1, st, 1.0)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(16):
+            fb.flare_causal_decode(q, k1, v1, st, 1.0)
+    graph.replay()
+    us_graph = timed(graph.replay, max(args.steps, 20)) * 1e3 / 16
     # training step of the same layer: forward + backward through flare_causal_mixer
     qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
     dy = torch.randn(B, H, N, D, generator=g).bfloat16().to(dev)
@@ -611,7 +624,8 @@ def run_causal(args):
                 tensor_frac=alg_flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], kernel="k_causal_tc_walk (tcgen05)")
     print(json.dumps(dict(metric="causal FLARE prefill Mtokens/s", value=B * N / ms / 1e3, unit="Mtokens/s", n_gpus=1,
                           steps=args.steps, warmup=max(args.warmup, 1), ms_per_step=ms, higher_is_better=True,
-                          dtype="bf16", data="synthetic", decode_step_us=us, fwd_bwd_ms=train_ms, roofline=roof,
+                          dtype="bf16", data="synthetic", decode_step_us=us, decode_step_graph_us=us_graph, fwd_bwd_ms=train_ms,
+                          roofline=roof,
                           config=dict(workload=f"causal_prefill: B={B} H={H} N={N} M={M} D={D} bf16, one layer's mixer"))),
           flush=True)
 
