@@ -49,47 +49,80 @@ int refuse(int code, const char* fmt, ...) {
 constexpr int kScanThreads = 128;
 constexpr int kScanRows = 2;      // rows per warp, walked side by side
 
-template <int NPL>                // columns per lane: D <= 32 * NPL
-__global__ void __launch_bounds__(kScanThreads, NPL == 4 ? 5 : 8)
-k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, const float* __restrict__ state_in,
+// The head dimension is a template parameter and a lane owns pairs of adjacent columns (one 8-byte access per 64
+// columns; rows are D + 2 floats, so 8-byte aligned): about 25 instructions per row and chunk.  With D a run-time
+// value, 4-byte accesses and 64-bit index arithmetic per access it was 109, and the kernel issue bound at a third of
+// the memory bandwidth.
+template <int D>
+__global__ void __launch_bounds__(kScanThreads, D == 128 ? 5 : 8)
+k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float* __restrict__ state_in,
               float* __restrict__ state_out) {
   grid_dep_sync();
+  constexpr int W = D + 2;
+  constexpr int VEC = D >= 64 ? 2 : 1;             // floats per access
+  constexpr int NLD = D >= 64 ? D / 64 : 1;        // accesses per row: columns 64 i + 2 lane (+1), or column lane
   const int lane = threadIdx.x % 32;
+  const bool lane_on = D >= 32 || lane < D;
+  const int col = VEC * lane;
   const long long row0 = ((long long)blockIdx.x * (kScanThreads / 32) + threadIdx.x / 32) * kScanRows;
   if (row0 >= rows) return;
-  const int W = D + 2;
   const long long cs = rows * W;
   // A warp's chain is latency bound and a record is only (D + 2) floats: two rows per warp and kAhead records of each
   // in flight keep the memory system busy, and half as many warps fit the GPU in one wave.
   constexpr int kAhead = 4;
-  long long row[kScanRows];
   bool on[kScanRows];
-  float m[kScanRows], l[kScanRows], acc[kScanRows][NPL];
-  float mb[kScanRows][kAhead], lb[kScanRows][kAhead], ab[kScanRows][kAhead][NPL];
-  auto fetch = [&](long long rw, int c, float& mo, float& lo, float (&ao)[NPL]) {
-    const float* r = rec + c * cs + rw * W;
-    mo = r[D]; lo = r[D + 1];
+  float* wp[kScanRows];                            // the record this row writes next
+  const float* fp[kScanRows];                      // the record it fetches next
+  float m[kScanRows], l[kScanRows], acc[kScanRows][NLD][VEC];
+  float2 mlb[kScanRows][kAhead];
+  float ab[kScanRows][kAhead][NLD][VEC];
+  auto load_acc = [&](const float* r, float (&ao)[NLD][VEC]) {
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) ao[i] = (lane + 32 * i < D) ? r[lane + 32 * i] : 0.f;
+    for (int i = 0; i < NLD; ++i) {
+      if constexpr (VEC == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(r + 64 * i + col);
+        ao[i][0] = t.x; ao[i][1] = t.y;
+      } else {
+        ao[i][0] = lane_on ? r[col] : 0.f;
+      }
+    }
+  };
+  auto store_acc = [&](float* r, const float (&ao)[NLD][VEC]) {
+#pragma unroll
+    for (int i = 0; i < NLD; ++i) {
+      if constexpr (VEC == 2) *reinterpret_cast<float2*>(r + 64 * i + col) = make_float2(ao[i][0], ao[i][1]);
+      else if (lane_on) r[col] = ao[i][0];
+    }
   };
 #pragma unroll
   for (int q = 0; q < kScanRows; ++q) {
     on[q] = row0 + q < rows;
-    row[q] = on[q] ? row0 + q : row0;              // a row past the end repeats row0's loads and stores nothing
+    const long long rw = on[q] ? row0 + q : row0;  // a row past the end repeats row0's loads and stores nothing
+    wp[q] = rec + rw * W;
+    fp[q] = wp[q];
     m[q] = -INFINITY; l[q] = 0.f;
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) acc[q][i] = 0.f;
-    if (state_in) {
-      m[q] = state_in[row[q] * W + D]; l[q] = state_in[row[q] * W + D + 1];
+    for (int i = 0; i < NLD; ++i)
 #pragma unroll
-      for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) acc[q][i] = state_in[row[q] * W + lane + 32 * i];
+      for (int j = 0; j < VEC; ++j) acc[q][i][j] = 0.f;
+    if (state_in) {
+      const float* si = state_in + rw * W;
+      const float2 ml = *reinterpret_cast<const float2*>(si + D);
+      m[q] = ml.x; l[q] = ml.y;
+      load_acc(si, acc[q]);
     }
 #pragma unroll
     for (int u = 0; u < kAhead; ++u) {
-      mb[q][u] = -INFINITY; lb[q][u] = 0.f;
+      mlb[q][u] = make_float2(-INFINITY, 0.f);
 #pragma unroll
-      for (int j = 0; j < NPL; ++j) ab[q][u][j] = 0.f;
-      if (u < n_chunks) fetch(row[q], u, mb[q][u], lb[q][u], ab[q][u]);
+      for (int i = 0; i < NLD; ++i)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) ab[q][u][i][j] = 0.f;
+      if (u < n_chunks) {
+        mlb[q][u] = *reinterpret_cast<const float2*>(fp[q] + D);
+        load_acc(fp[q], ab[q][u]);
+        fp[q] += cs;
+      }
     }
   }
   for (int c0 = 0; c0 < n_chunks; c0 += kAhead) {
@@ -99,24 +132,31 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, cons
       if (c < n_chunks) {
 #pragma unroll
         for (int q = 0; q < kScanRows; ++q) {
-          float* r = rec + c * cs + row[q] * W;
-          const float mc = mb[q][u], lc = lb[q][u];
-          float ac[NPL];
+          const float mc = mlb[q][u].x, lc = mlb[q][u].y;
+          float ac[NLD][VEC];
 #pragma unroll
-          for (int i = 0; i < NPL; ++i) ac[i] = ab[q][u][i];
-          if (c + kAhead < n_chunks) fetch(row[q], c + kAhead, mb[q][u], lb[q][u], ab[q][u]);
+          for (int i = 0; i < NLD; ++i)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) ac[i][j] = ab[q][u][i][j];
+          if (c + kAhead < n_chunks) {
+            mlb[q][u] = *reinterpret_cast<const float2*>(fp[q] + D);
+            load_acc(fp[q], ab[q][u]);
+            fp[q] += cs;
+          }
           __syncwarp();
           if (on[q]) {                             // the record of everything before chunk c
-#pragma unroll
-            for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) r[lane + 32 * i] = acc[q][i];
-            if (lane == 0) { r[D] = m[q]; r[D + 1] = l[q]; }
+            store_acc(wp[q], acc[q]);
+            if (lane == 0) *reinterpret_cast<float2*>(wp[q] + D) = make_float2(m[q], l[q]);
           }
+          wp[q] += cs;
           const float mn = fmaxf(m[q], mc);
           const float wa = (m[q] == -INFINITY) ? 0.f : __expf(m[q] - mn);
           const float wc = (mc == -INFINITY) ? 0.f : __expf(mc - mn);
           l[q] = wa * l[q] + wc * lc;
 #pragma unroll
-          for (int i = 0; i < NPL; ++i) acc[q][i] = wa * acc[q][i] + wc * ac[i];
+          for (int i = 0; i < NLD; ++i)
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) acc[q][i][j] = wa * acc[q][i][j] + wc * ac[i][j];
           m[q] = mn;
         }
       }
@@ -126,9 +166,9 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, int D, cons
 #pragma unroll
     for (int q = 0; q < kScanRows; ++q) {
       if (on[q]) {
-#pragma unroll
-        for (int i = 0; i < NPL; ++i) if (lane + 32 * i < D) state_out[row[q] * W + lane + 32 * i] = acc[q][i];
-        if (lane == 0) { state_out[row[q] * W + D] = m[q]; state_out[row[q] * W + D + 1] = l[q]; }
+        float* so = state_out + (row0 + q) * W;
+        store_acc(so, acc[q]);
+        if (lane == 0) *reinterpret_cast<float2*>(so + D) = make_float2(m[q], l[q]);
       }
     }
   }
@@ -139,12 +179,15 @@ void launch_scan(bool dependent, float* rec, int n_chunks, long long rows, int D
   const int rpb = kScanThreads / 32 * kScanRows;
   const dim3 grid((unsigned)((rows + rpb - 1) / rpb)), block(kScanThreads);
   auto go = [&](auto kernel) {
-    if (dependent) launch_dep(kernel, grid, block, 0, st, rec, n_chunks, rows, D, state_in, state_out);
-    else kernel<<<grid, block, 0, st>>>(rec, n_chunks, rows, D, state_in, state_out);
+    if (dependent) launch_dep(kernel, grid, block, 0, st, rec, n_chunks, rows, state_in, state_out);
+    else kernel<<<grid, block, 0, st>>>(rec, n_chunks, rows, state_in, state_out);
   };
-  if (D <= 32) go(k_causal_scan<1>);
-  else if (D <= 64) go(k_causal_scan<2>);
-  else go(k_causal_scan<4>);
+  switch (D) {                                     // fill_args admits exactly these
+    case 16: go(k_causal_scan<16>); break;
+    case 32: go(k_causal_scan<32>); break;
+    case 64: go(k_causal_scan<64>); break;
+    default: go(k_causal_scan<128>); break;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -52,9 +52,6 @@ struct CausalTcArgs {
 __device__ __forceinline__ void arrive_w(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void row_sync() {       // the 128 row threads
-  asm volatile("bar.sync 1, 128;" ::: "memory");
-}
 
 __device__ __forceinline__ void rows_sync() {      // the 256 row threads
   asm volatile("bar.sync 1, 256;" ::: "memory");
