@@ -10,13 +10,13 @@
 //      the softmax over the latents (per token) and the running sum over the tokens (per latent) are both walks
 //      along a thread's own tensor-memory row
 //   2. token threads: column maximum and sum of S^T -> one factor w_t per token in shared memory
-//   3. latent threads: mu, a, E, l (running sum), A = E u_m w_t, G = A / l; E and G rows as bf16 into shared
-//      memory, laid out as the MN-major operands of the next product (contraction over the latents); a * acc0
-//      as bf16 beside them
+//   3. latent threads: mu, a, E, l (running sum), G' = E u_m / l (G = G' w_t: the token factor is common to row t
+//      of W and Y and is applied to y at the end); E and G' rows as bf16 into shared memory, laid out as the
+//      MN-major operands of the next product (contraction over the latents); a * acc0 as bf16 beside them
 //   4. W = G^T E (token lanes x token columns) and Y = G^T (a acc0): products from shared memory
 //   5. token threads: W masked to n <= t, packed to bf16 in place in tensor memory
 //   6. Y += W V: A operand from tensor memory, V tile as loaded by TMA
-//   7. token threads: Y -> y
+//   7. token threads: w_t Y -> y
 //
 // 128 row threads (a thread is latent m in steps 3 and token t in steps 2, 5, 7) and one issuing warp; every
 // wait is bounded.  bf16 only: E and G are relative to the chunk's final maximum and need the exponent range
@@ -205,7 +205,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     rows_sync();
     // A_mt = 2^(S_mt - cmax_t) / csum_t is formed from the exponential that E needs anyway:
-    //   A_mt = E_mt * u_m * w_t,   u_m = 2^(mu_m - c0),   w_t = 2^(c0 - cmax_t) / csum_t,
+    //   A_mt = E_mt * u_m * w_t,   u_m = 2^(mu_m - c0),   w_t = 2^(c0 - cmax_t) / csum_t   (w_t applied in step 7),
     // with c0 the column maximum of the chunk's first token (every thread reads it from the same two words).
     // |mu_m - c0| and |cmax_t - c0| are kept within 50 octaves, so that no factor leaves fp32's range while A_mt
     // still matters; a chunk outside that is flagged and redone like one whose scores climb too far.
@@ -250,9 +250,9 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const bool in = FULL || (live && t < cnt);
             const float e = in ? ex2(fmaf(x, sl, -mu)) : 0.f;
             l += e;
-            const float A = e * (um * sCinv[t]);
             e2[u] = e;
-            g2[u] = (FULL || l > 0.f) ? __fdividef(A, l) : 0.f;   // l = 0 only in a chunk that is flagged and redone
+            // G without its token factor w_t, which is common to row t of W and Y and applied to y in step 7
+            g2[u] = (FULL || l > 0.f) ? e * __fdividef(um, l) : 0.f;   // l = 0 only in a chunk that is flagged and redone
           }
           pe[j >> 1] = pack_bf16(e2[0], e2[1]);
           pg[j >> 1] = pack_bf16(g2[0], g2[1]);
@@ -332,13 +332,14 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       else tmem_ld16(lane_base + cY + 16 * hb, v);
       tmem_wait_ld();
       if (r < cnt) {
+        const float wt = sCinv[r];                 // the token factor left out of G
 #pragma unroll
         for (int q4 = 0; q4 < D / 16; ++q4) {
           uint4 o;
-          o.x = pack_bf16(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
-          o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
-          o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
-          o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+          o.x = pack_bf16(__uint_as_float(v[8 * q4]) * wt, __uint_as_float(v[8 * q4 + 1]) * wt);
+          o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]) * wt, __uint_as_float(v[8 * q4 + 3]) * wt);
+          o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]) * wt, __uint_as_float(v[8 * q4 + 5]) * wt);
+          o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]) * wt, __uint_as_float(v[8 * q4 + 7]) * wt);
           reinterpret_cast<uint4*>(yp)[q4] = o;
         }
       }
