@@ -170,9 +170,26 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float* rec = a.prefix + ((((long long)chunk * a.B + b) * a.H + h) * M + min(r, M - 1)) * W;
     const float m0 = rec[D], l0 = rec[D + 1];
     const bool live = r < M;
-    // its acc0 half is read at the end of step 3: bring the two lines it spans close now
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(rec + hb * (D / 2)));
-    asm volatile("prefetch.global.L1 [%0];" ::"l"(rec + hb * (D / 2) + D / 2 - 1));
+    // The acc0 rows of the chunk's prefix record.  A thread reading its own 264-byte row touches one 32-byte sector
+    // per 8 bytes it uses, 4096 sector requests per CTA in the middle of step 3.  The block is contiguous: the row
+    // threads copy it side by side with asynchronous 8-byte copies now, while the tiles and the score products are on
+    // their way, into the bytes E takes later (16-byte chunks xor-ed with the row: a warp's rows do not share banks).
+    constexpr int kStageChunks = D / 4;            // 16-byte chunks per staged row
+    {
+      constexpr int HW = W / 2, NIT = (128 * HW + kRowT - 1) / kRowT;
+      const float2* blk = reinterpret_cast<const float2*>(a.prefix + (((long long)chunk * a.B + b) * a.H + h) * M * W);
+      const int total = M * HW;
+#pragma unroll
+      for (int it = 0; it < NIT; ++it) {
+        const int i2 = tid + kRowT * it;
+        const int row = i2 / HW, c2 = i2 - row * HW;
+        if (i2 < total && c2 < D / 2) {
+          const uint32_t dst = smem_u32(sE + row * (D * 4) + ((((c2 >> 1) ^ row) & (kStageChunks - 1)) << 4) + ((c2 & 1) << 3));
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(blk + i2) : "memory");
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
 
     mbar_wait(bar_s, 0, a.status, abort_flag);
     tc_fence_after();
@@ -203,6 +220,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       });
       sMuP[hb * 128 + r] = mp;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");       // this thread's part of the staged rows has landed
     rows_sync();
     // A_mt = 2^(S_mt - cmax_t) / csum_t is formed from the exponential that E needs anyway:
     //   A_mt = E_mt * u_m * w_t,   u_m = 2^(mu_m - c0),   w_t = 2^(c0 - cmax_t) / csum_t   (w_t applied in step 7),
@@ -219,6 +237,21 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (in && fabsf(c0 - cm) > 50.f) abort_flag[1] = 1;
     }
     const float mu = fmaxf(m0 * kLog2e, fmaxf(sMuP[r], sMuP[128 + r]));   // the record keeps m in natural-log units
+    const float aa = (m0 == -INFINITY) ? 0.f : ex2(m0 * kLog2e - mu);
+    // a * acc0 of this latent, half of its D values, from the staged rows (E overwrites them after the barrier)
+#pragma unroll
+    for (int cc = 0; cc < CPR / 2; ++cc) {
+      const int c = hb * (CPR / 2) + cc;           // 16 bytes of bf16 = 8 columns = staged chunks 2c, 2c + 1
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (FULL || live) {
+        const uint8_t* srow = sE + r * (D * 4);
+        const float4 x0 = *reinterpret_cast<const float4*>(srow + ((((2 * c) ^ r) & (kStageChunks - 1)) << 4));
+        const float4 x1 = *reinterpret_cast<const float4*>(srow + ((((2 * c + 1) ^ r) & (kStageChunks - 1)) << 4));
+        o = make_uint4(pack_bf16(x0.x * aa, x0.y * aa), pack_bf16(x0.z * aa, x0.w * aa), pack_bf16(x1.x * aa, x1.y * aa),
+                       pack_bf16(x1.z * aa, x1.w * aa));
+      }
+      *reinterpret_cast<uint4*>(sA0 + swz_off<ROWB>(r, c)) = o;
+    }
     rows_sync();
 
     // ---- step 3: latent r: a, E, running l, G over its half of the tokens; a * acc0 over its half of D ----
@@ -227,7 +260,6 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // handed to the walk that carries a running maximum (flagged; its y overwrites this kernel's).
       if (hb == 0 && live && (mu - first > 64.f || fabsf(mu - c0) > 50.f)) abort_flag[1] = 1;
       const float um = live ? ex2(fminf(fmaxf(mu - c0, -60.f), 60.f)) : 0.f;
-      const float aa = (m0 == -INFINITY) ? 0.f : ex2(m0 * kLog2e - mu);
       float l = aa * l0;
       if (hb == 1) {                               // the sum over the first half, in the order its owner adds it
         row_half_pass(lane_base + cS, [&](int c, const uint32_t (&v)[32]) {
@@ -265,19 +297,6 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           *reinterpret_cast<uint4*>(gh + off) = make_uint4(pg[4 * q4], pg[4 * q4 + 1], pg[4 * q4 + 2], pg[4 * q4 + 3]);
         }
       });
-      // a * acc0 of this latent, half of its D values
-#pragma unroll
-      for (int cc = 0; cc < CPR / 2; ++cc) {
-        const int c = hb * (CPR / 2) + cc;
-        uint4 o = make_uint4(0, 0, 0, 0);
-        if (FULL || live) {
-          const float2* x = reinterpret_cast<const float2*>(rec + 8 * c);   // records are D + 2 floats: 8-byte aligned
-          const float2 x0 = x[0], x1 = x[1], x2 = x[2], x3 = x[3];
-          o = make_uint4(pack_bf16(x0.x * aa, x0.y * aa), pack_bf16(x1.x * aa, x1.y * aa), pack_bf16(x2.x * aa, x2.y * aa),
-                         pack_bf16(x3.x * aa, x3.y * aa));
-        }
-        *reinterpret_cast<uint4*>(sA0 + swz_off<ROWB>(r, c)) = o;
-      }
       fence_proxy_async();
       tc_fence_before();
       arrive_w(bar_ge);
