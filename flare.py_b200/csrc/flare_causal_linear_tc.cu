@@ -68,7 +68,7 @@ k_cl_tc_sums(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
     tma_load_4d(sK + kHalf, &tmK, bar_load, 64, chunk * 128, h, b);
     tma_load_4d(sV, &tmV, bar_load, 0, chunk * 128, h, b);
   }
-  if (warp == 0) tmem_alloc<64>(tmem_slot);
+  if (warp == 1) tmem_alloc<64>(tmem_slot);       // beside warp 0, whose first thread is issuing the loads
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -106,7 +106,7 @@ k_cl_tc_sums(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<64>(tmem);
+  if (warp == 1) tmem_dealloc<64>(tmem);
 }
 
 // ---- pass 2: exclusive running sum over the chunks, scaled and rounded ---------------------------------------------
@@ -171,7 +171,7 @@ k_cl_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
     tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
     tma_load_4d(sP, &tmP, bar_load, 0, 0, chunk, bh);
   }
-  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  if (warp == 1) tmem_alloc<256>(tmem_slot);       // beside warp 0, whose first thread is issuing the loads
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -255,7 +255,7 @@ k_cl_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CU
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<256>(tmem);
+  if (warp == 1) tmem_dealloc<256>(tmem);
 }
 
 template <typename T, int DV>

@@ -113,7 +113,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);                       // rows past N arrive as zeros
     tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
   }
-  if (warp == 0) tmem_alloc<256>(tmem_slot);
+  if (warp == 1) tmem_alloc<256>(tmem_slot);     // beside warp 0, whose first thread is issuing the loads
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -366,7 +366,7 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<256>(tmem);
+  if (warp == 1) tmem_dealloc<256>(tmem);
 }
 
 // Pass 1 for the same shapes: the record (acc, m, l) of every 128-token chunk on its own.  S = scale q k^T,
@@ -412,7 +412,7 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tma_load_4d(sK, &tmK, bar_load, 0, n0, h, b);
     tma_load_4d(sV, &tmV, bar_load, 0, n0, h, b);
   }
-  if (warp == 0) tmem_alloc<128>(tmem_slot);
+  if (warp == 1) tmem_alloc<128>(tmem_slot);     // beside warp 0, whose first thread is issuing the loads
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -493,7 +493,7 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc<128>(tmem);
+  if (warp == 1) tmem_dealloc<128>(tmem);
 }
 
 struct TcLaunch {
