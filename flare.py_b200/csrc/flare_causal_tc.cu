@@ -179,10 +179,14 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr int HW = W / 2, NIT = (128 * HW + kRowT - 1) / kRowT;
       const float2* blk = reinterpret_cast<const float2*>(a.prefix + (((long long)chunk * a.B + b) * a.H + h) * M * W);
       const int total = M * HW;
+      int row = tid / HW, c2 = tid - row * HW;     // 8-byte element i2 = tid + 256 it is column pair c2 of row `row`
 #pragma unroll
       for (int it = 0; it < NIT; ++it) {
         const int i2 = tid + kRowT * it;
-        const int row = i2 / HW, c2 = i2 - row * HW;
+        if (it > 0) {
+          row += kRowT / HW; c2 += kRowT % HW;
+          if (c2 >= HW) { c2 -= HW; ++row; }
+        }
         if (i2 < total && c2 < D / 2) {
           const uint32_t dst = smem_u32(sE + row * (D * 4) + ((((c2 >> 1) ^ row) & (kStageChunks - 1)) << 4) + ((c2 & 1) << 3));
           asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(blk + i2) : "memory");
