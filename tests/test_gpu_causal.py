@@ -146,6 +146,31 @@ def test_prefill_tensor_core_walk_shapes(cuda_dev, B, H, N, M, D, shared):
         assert O.rel_l2(torch.cat([y0, y1], 2).double().cpu(), y_ref) <= 2e-2
 
 
+def test_prefill_replays_from_a_cuda_graph(cuda_dev):
+    """The four chained launches of the tensor-core prefill (records, scan, walk, redo pass) recorded once and replayed
+    on new inputs written into the same buffers."""
+    import flare_b200 as fb
+    B, H, N, M, D = 2, 2, 700, 128, 64
+    q, k, v = _inputs(B, H, N, M, D, torch.bfloat16, seed=17)
+    q2, k2, v2 = _inputs(B, H, N, M, D, torch.bfloat16, seed=18)
+    qd, kd, vd = q.to(cuda_dev), k.to(cuda_dev), v.to(cuda_dev)
+    side = torch.cuda.Stream(device=cuda_dev)
+    side.wait_stream(torch.cuda.current_stream(cuda_dev))
+    with torch.cuda.stream(side):
+        fb.flare_causal_prefill(qd, kd, vd, 1.0)                     # warm-up outside the recording
+    torch.cuda.current_stream(cuda_dev).wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y, st = fb.flare_causal_prefill(qd, kd, vd, 1.0)
+    for qq, kk, vv in ((q, k, v), (q2, k2, v2)):
+        qd.copy_(qq.to(cuda_dev)); kd.copy_(kk.to(cuda_dev)); vd.copy_(vv.to(cuda_dev))
+        graph.replay()
+        torch.cuda.synchronize()
+        y_ref, _ = O.causal_recurrent(qq.double(), kk.double(), vv.double(), 1.0)
+        assert O.rel_l2(y.double().cpu(), y_ref) <= 2e-2
+    assert fb.device_status() == 0
+
+
 def test_prefill_tensor_core_walk_hands_wide_chunks_to_the_fp32_walk(cuda_dev):
     """Scores that climb by hundreds of octaves inside one chunk: the tensor-core walk keeps one reference
     maximum per chunk, flags such chunks, and the fp32 walk with a running maximum redoes them."""
