@@ -53,10 +53,13 @@ constexpr int kScanRows = 2;      // rows per warp, walked side by side
 // columns; rows are D + 2 floats, so 8-byte aligned): about 25 instructions per row and chunk.  With D a run-time
 // value, 4-byte accesses and 64-bit index arithmetic per access it was 109, and the kernel issue bound at a third of
 // the memory bandwidth.
-template <int D>
+// COMPACT: the prefix of chunk c goes to pacc[c][row][D] (16-bit, what the tensor-core walk multiplies with anyway)
+// and pml[c][row] = (m, l) instead of back over the fp32 record: a third of the bytes written, half of the bytes the
+// walk reads, and rows it can fetch in 16-byte pieces.
+template <int D, bool COMPACT>
 __global__ void __launch_bounds__(kScanThreads, D == 128 ? 5 : 8)
 k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float* __restrict__ state_in,
-              float* __restrict__ state_out) {
+              float* __restrict__ state_out, __nv_bfloat16* __restrict__ pacc, float2* __restrict__ pml) {
   grid_dep_sync();
   constexpr int W = D + 2;
   constexpr int VEC = D >= 64 ? 2 : 1;             // floats per access
@@ -71,6 +74,7 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
   // in flight keep the memory system busy, and half as many warps fit the GPU in one wave.
   constexpr int kAhead = 4;
   bool on[kScanRows];
+  long long rw_[kScanRows];
   float* wp[kScanRows];                            // the record this row writes next
   const float* fp[kScanRows];                      // the record it fetches next
   float m[kScanRows], l[kScanRows], acc[kScanRows][NLD][VEC];
@@ -98,6 +102,7 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
   for (int q = 0; q < kScanRows; ++q) {
     on[q] = row0 + q < rows;
     const long long rw = on[q] ? row0 + q : row0;  // a row past the end repeats row0's loads and stores nothing
+    rw_[q] = rw;
     wp[q] = rec + rw * W;
     fp[q] = wp[q];
     m[q] = -INFINITY; l[q] = 0.f;
@@ -145,8 +150,19 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
           }
           __syncwarp();
           if (on[q]) {                             // the record of everything before chunk c
-            store_acc(wp[q], acc[q]);
-            if (lane == 0) *reinterpret_cast<float2*>(wp[q] + D) = make_float2(m[q], l[q]);
+            if constexpr (COMPACT) {
+              __nv_bfloat16* pr = pacc + ((long long)c * rows + rw_[q]) * D;
+#pragma unroll
+              for (int i = 0; i < NLD; ++i) {
+                if constexpr (VEC == 2)
+                  *reinterpret_cast<__nv_bfloat162*>(pr + 64 * i + col) = __floats2bfloat162_rn(acc[q][i][0], acc[q][i][1]);
+                else if (lane_on) pr[col] = __float2bfloat16_rn(acc[q][i][0]);
+              }
+              if (lane == 0) pml[(long long)c * rows + rw_[q]] = make_float2(m[q], l[q]);
+            } else {
+              store_acc(wp[q], acc[q]);
+              if (lane == 0) *reinterpret_cast<float2*>(wp[q] + D) = make_float2(m[q], l[q]);
+            }
           }
           wp[q] += cs;
           const float mn = fmaxf(m[q], mc);
@@ -175,18 +191,22 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
 }
 
 void launch_scan(bool dependent, float* rec, int n_chunks, long long rows, int D, const float* state_in, float* state_out,
-                 cudaStream_t st) {
+                 __nv_bfloat16* pacc, float2* pml, cudaStream_t st) {
   const int rpb = kScanThreads / 32 * kScanRows;
   const dim3 grid((unsigned)((rows + rpb - 1) / rpb)), block(kScanThreads);
   auto go = [&](auto kernel) {
-    if (dependent) launch_dep(kernel, grid, block, 0, st, rec, n_chunks, rows, state_in, state_out);
-    else kernel<<<grid, block, 0, st>>>(rec, n_chunks, rows, state_in, state_out);
+    if (dependent) launch_dep(kernel, grid, block, 0, st, rec, n_chunks, rows, state_in, state_out, pacc, pml);
+    else kernel<<<grid, block, 0, st>>>(rec, n_chunks, rows, state_in, state_out, pacc, pml);
   };
+  if (pacc) {                                      // behind the tensor-core record pass: D is 32 or 64
+    if (D == 32) go(k_causal_scan<32, true>); else go(k_causal_scan<64, true>);
+    return;
+  }
   switch (D) {                                     // fill_args admits exactly these
-    case 16: go(k_causal_scan<16>); break;
-    case 32: go(k_causal_scan<32>); break;
-    case 64: go(k_causal_scan<64>); break;
-    default: go(k_causal_scan<128>); break;
+    case 16: go(k_causal_scan<16, false>); break;
+    case 32: go(k_causal_scan<32, false>); break;
+    case 64: go(k_causal_scan<64, false>); break;
+    default: go(k_causal_scan<128, false>); break;
   }
 }
 
@@ -205,6 +225,8 @@ struct CausalArgs {
   int tokens_per_cta;          // kChunk in prefill, N (usually 1) in decode
   const int* redo;             // prefill behind the tensor-core walk: [chunks][B*H], only the flagged units are walked
   int n_units;                 // chunks * B * H (redo mode)
+  const __nv_bfloat16* pacc;   // redo mode: the prefix as the scan wrote it for the tensor-core walk,
+  const float2* pml;           //   acc [chunks][B][H][M][D] in 16 bits and (m, l) [chunks][B][H][M]
 };
 
 template <typename T, int D>
@@ -261,10 +283,15 @@ k_causal_walk(CausalArgs a) {
                               : a.state + ((long long)b * a.H + h) * M * W;
 
   for (int i = tid; i < M * D; i += kThreads) sQ[(i / D) * DP + i % D] = to_f32(qp[(i / D) * a.qs[2] + i % D]);
-  for (int m = tid; m < M; m += kThreads) { sMu[m] = rec[m * W + D]; sL[m] = rec[m * W + D + 1]; }
+  const long long prow = (((long long)chunk * a.B + b) * a.H + h) * M;      // first row of this unit in pacc / pml
+  for (int m = tid; m < M; m += kThreads) {
+    if (a.pacc) { const float2 ml = a.pml[prow + m]; sMu[m] = ml.x; sL[m] = ml.y; }
+    else { sMu[m] = rec[m * W + D]; sL[m] = rec[m * W + D + 1]; }
+  }
   float acc[kMaxLat];
 #pragma unroll
-  for (int j = 0; j < kMaxLat; ++j) acc[j] = (j < nlat) ? rec[(g * nlat + j) * W + d] : 0.f;
+  for (int j = 0; j < kMaxLat; ++j)
+    acc[j] = (j < nlat) ? (a.pacc ? __bfloat162float(a.pacc[(prow + g * nlat + j) * D + d]) : rec[(g * nlat + j) * W + d]) : 0.f;
   __syncthreads();
 
   // E, l and acc of a sub-chunk are relative to the running maximum at its end, so l_mt >= e^{first - mu} with
@@ -462,7 +489,7 @@ int fill_args(const FlareProblem* p, CausalArgs* a) {
   if (p->M % G != 0 || p->M / G > kMaxLat)
     return refuse(FLARE_EUNSUPPORTED, "causal: M=%d must be a multiple of %d and at most %d for D=%d", p->M, G, G * kMaxLat, D);
   a->B = p->B; a->H = p->H; a->N = p->N; a->M = p->M; a->D = D; a->scale = p->scale;
-  a->redo = nullptr; a->n_units = 0;
+  a->redo = nullptr; a->n_units = 0; a->pacc = nullptr; a->pml = nullptr;
   for (int i = 0; i < 3; ++i) { a->qs[i] = p->q_stride[i]; a->ks[i] = p->k_stride[i]; a->vs[i] = p->v_stride[i]; a->ys[i] = p->y_stride[i]; }
   return FLARE_OK;
 }
@@ -482,7 +509,7 @@ namespace flare {
 // pass 2 for the backward (flare_causal_bwd.cu), which needs the same chunk-start records
 int launch_causal_scan(float* rec, int n_chunks, long long rows, int D, const float* state_in, float* state_out,
                        cudaStream_t st) {
-  launch_scan(false, rec, n_chunks, rows, D, state_in, state_out, st);
+  launch_scan(false, rec, n_chunks, rows, D, state_in, state_out, nullptr, nullptr, st);
   const cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal scan: %s", cudaGetErrorString(e));
   return FLARE_OK;
@@ -494,7 +521,10 @@ extern "C" {
 size_t flare_causal_workspace_bytes(const FlareProblem* p) {
   if (!p || p->N < 1) return 0;
   const size_t chunks = ((size_t)p->N + kChunk - 1) / kChunk;
-  return chunks * p->B * p->H * p->M * (p->D + 2) * sizeof(float) + chunks * p->B * p->H * sizeof(int) + 256;
+  const size_t rows = (size_t)p->B * p->H * p->M;
+  // records, redo flags, and the compact prefix of the tensor-core path (16-byte aligned pieces)
+  return chunks * rows * (p->D + 2) * sizeof(float) + ((chunks * p->B * p->H * sizeof(int) + 15) & ~size_t(15)) +
+         chunks * rows * (p->D * 2 + sizeof(float2)) + 256;
 }
 
 int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
@@ -518,19 +548,25 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   }
   // pass 2: exclusive prefix along the chunk axis
   const long long rows = (long long)p->B * p->H * p->M;
-  launch_scan(true, workspace, chunks, rows, p->D, state_in, state_out, st);
+  // workspace: records | redo flags | pml | pacc   (every piece a multiple of 16 bytes)
+  char* wsb = reinterpret_cast<char*>(workspace) + (size_t)chunks * rows * (p->D + 2) * sizeof(float);
+  int* redo = reinterpret_cast<int*>(wsb);
+  wsb += ((size_t)chunks * p->B * p->H * sizeof(int) + 15) & ~size_t(15);
+  float2* pml = reinterpret_cast<float2*>(wsb);
+  wsb += (size_t)chunks * rows * sizeof(float2);
+  __nv_bfloat16* pacc = reinterpret_cast<__nv_bfloat16*>(wsb);
+  launch_scan(true, workspace, chunks, rows, p->D, state_in, state_out, on_tc ? pacc : nullptr, on_tc ? pml : nullptr, st);
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;
   a.prefix = workspace; a.state = nullptr; a.tokens_per_cta = kChunk;
   if (on_tc) {
     // the tensor-core walk flags the chunks whose scores span too many octaves for its fixed reference
     // maximum; the fp32 walk, launched behind it, redoes exactly those (every other CTA returns at once)
-    int* redo = reinterpret_cast<int*>(workspace + (size_t)chunks * rows * (p->D + 2));
-    rc = flare::causal_tc_walk(p, q, k, v, y, workspace, redo, chunks, st);
+    rc = flare::causal_tc_walk(p, q, k, v, y, pacc, pml, redo, chunks, st);
     if (rc != FLARE_OK) return refuse(rc, "causal_prefill: tensor-core walk could not be launched");
     const cudaError_t e = cudaPeekAtLastError();
     if (e != cudaSuccess) return refuse(FLARE_ECUDA, "causal_prefill: %s", cudaGetErrorString(e));
-    a.redo = redo; a.n_units = chunks * p->B * p->H;
+    a.redo = redo; a.n_units = chunks * p->B * p->H; a.pacc = pacc; a.pml = pml;
   }
   return run_walk(p, a, chunks, st);
 }

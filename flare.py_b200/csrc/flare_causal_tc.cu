@@ -1,6 +1,6 @@
 // Causal FLARE prefill, pass 3 on the tensor cores (bf16, M <= 128, D in {32, 64}).
 //
-// One CTA per (b, h, 128-token chunk) starts from the chunk's prefix record (m0, l0, acc0) and writes the
+// One CTA per (b, h, 128-token chunk) starts from the chunk's prefix (m0, l0 per latent, acc0 in 16 bits) and writes the
 // chunk's y.  In the chunked form every contraction is a product (S = scale q k^T, mu = max(m0, rowmax S),
 // a = e^{m0 - mu}, E = e^{S - mu}, l_mt = a l0 + cumsum_t E, A = softmax_M(S), G = A / l):
 //
@@ -42,7 +42,8 @@ struct CausalTcArgs {
   int B, H, N, M;
   float scale_log2;
   int q_batched;
-  const float* prefix;                             // [chunks][B][H][M][D+2]
+  const __nv_bfloat16* pacc;                       // [chunks][B][H][M][D]: acc of the prefix before every chunk
+  const float2* pml;                               // [chunks][B][H][M]: its (m, l)
   __nv_bfloat16* y;
   long long ys[3];
   int* redo;                                       // [chunks][B*H]: 1 = this chunk's scores span too many octaves
@@ -166,30 +167,25 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int r = 32 * (warp & 3) + lane, hb = warp >> 2;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float sl = a.scale_log2;
-    // the prefix record of latent r (needed in step 3; fetched now)
-    const float* rec = a.prefix + ((((long long)chunk * a.B + b) * a.H + h) * M + min(r, M - 1)) * W;
-    const float m0 = rec[D], l0 = rec[D + 1];
+    // the prefix of this chunk as the scan left it: (m, l) per latent, acc0 rows in 16 bits
+    const long long prow = (((long long)chunk * a.B + b) * a.H + h) * M;
+    const float2 ml0 = a.pml[prow + min(r, M - 1)];
+    const float m0 = ml0.x, l0 = ml0.y;
     const bool live = r < M;
-    // The acc0 rows of the chunk's prefix record.  A thread reading its own 264-byte row touches one 32-byte sector
-    // per 8 bytes it uses, 4096 sector requests per CTA in the middle of step 3.  The block is contiguous: the row
-    // threads copy it side by side with asynchronous 8-byte copies now, while the tiles and the score products are on
-    // their way, into the bytes E takes later (16-byte chunks xor-ed with the row: a warp's rows do not share banks).
-    constexpr int kStageChunks = D / 4;            // 16-byte chunks per staged row
+    // The acc0 rows are one contiguous block of M x D 16-bit values: the row threads fetch it with asynchronous
+    // 16-byte copies now, while the tiles and the score products are on their way, into the bytes E takes later, in
+    // the layout of the operand tile they become once scaled by a_m.  (A thread reading its own row of an fp32
+    // record in the middle of step 3 cost 2600-4800 clocks per chunk.)
     {
-      constexpr int HW = W / 2, NIT = (128 * HW + kRowT - 1) / kRowT;
-      const float2* blk = reinterpret_cast<const float2*>(a.prefix + (((long long)chunk * a.B + b) * a.H + h) * M * W);
-      const int total = M * HW;
-      int row = tid / HW, c2 = tid - row * HW;     // 8-byte element i2 = tid + 256 it is column pair c2 of row `row`
+      constexpr int NIT = 128 * CPR / kRowT;       // 16-byte pieces per thread: 4 (D = 64), 2 (D = 32)
+      const uint4* blk = reinterpret_cast<const uint4*>(a.pacc + prow * D);
 #pragma unroll
       for (int it = 0; it < NIT; ++it) {
-        const int i2 = tid + kRowT * it;
-        if (it > 0) {
-          row += kRowT / HW; c2 += kRowT % HW;
-          if (c2 >= HW) { c2 -= HW; ++row; }
-        }
-        if (i2 < total && c2 < D / 2) {
-          const uint32_t dst = smem_u32(sE + row * (D * 4) + ((((c2 >> 1) ^ row) & (kStageChunks - 1)) << 4) + ((c2 & 1) << 3));
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(blk + i2) : "memory");
+        const int i16 = tid + kRowT * it;
+        const int row = i16 / CPR, ch = i16 % CPR;
+        if (row < M) {
+          const uint32_t dst = smem_u32(sE + swz_off<ROWB>(row, ch));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(blk + i16) : "memory");
         }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -245,14 +241,18 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     // a * acc0 of this latent, half of its D values, from the staged rows (E overwrites them after the barrier)
 #pragma unroll
     for (int cc = 0; cc < CPR / 2; ++cc) {
-      const int c = hb * (CPR / 2) + cc;           // 16 bytes of bf16 = 8 columns = staged chunks 2c, 2c + 1
+      const int c = hb * (CPR / 2) + cc;
       uint4 o = make_uint4(0, 0, 0, 0);
       if (FULL || live) {
-        const uint8_t* srow = sE + r * (D * 4);
-        const float4 x0 = *reinterpret_cast<const float4*>(srow + ((((2 * c) ^ r) & (kStageChunks - 1)) << 4));
-        const float4 x1 = *reinterpret_cast<const float4*>(srow + ((((2 * c + 1) ^ r) & (kStageChunks - 1)) << 4));
-        o = make_uint4(pack_bf16(x0.x * aa, x0.y * aa), pack_bf16(x0.z * aa, x0.w * aa), pack_bf16(x1.x * aa, x1.y * aa),
-                       pack_bf16(x1.z * aa, x1.w * aa));
+        const uint4 x = *reinterpret_cast<const uint4*>(sE + swz_off<ROWB>(r, c));
+        const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Op16<__nv_bfloat16>::unpack(xw[j]);
+          ow[j] = pack_bf16(f.x * aa, f.y * aa);
+        }
+        o = make_uint4(ow[0], ow[1], ow[2], ow[3]);
       }
       *reinterpret_cast<uint4*>(sA0 + swz_off<ROWB>(r, c)) = o;
     }
@@ -521,21 +521,21 @@ int fill_launch(const FlareProblem* p, const void* q, const void* k, const void*
   a.B = p->B; a.H = p->H; a.N = p->N; a.M = p->M;
   a.scale_log2 = p->scale * kLog2e;
   a.q_batched = qb ? 1 : 0;
-  a.prefix = nullptr; a.y = nullptr; a.redo = nullptr;
+  a.pacc = nullptr; a.pml = nullptr; a.y = nullptr; a.redo = nullptr;
   for (int i = 0; i < 3; ++i) a.ys[i] = p->y_stride[i];
   a.status = tc_status_ptr();
   return FLARE_OK;
 }
 
 template <int D>
-int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
-                   int* redo, int chunks, cudaStream_t st) {
+int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const __nv_bfloat16* pacc,
+                   const float2* pml, int* redo, int chunks, cudaStream_t st) {
   TcLaunch L;
   const int rc = fill_launch<D>(p, q, k, v, &L);
   if (rc != FLARE_OK) return rc;
   CausalTcArgs& a = L.a;
   const CUtensorMap &tmQ = L.tmQ, &tmK = L.tmK, &tmV = L.tmV;
-  a.prefix = prefix;
+  a.pacc = pacc; a.pml = pml;
   a.y = reinterpret_cast<__nv_bfloat16*>(y);
   a.redo = redo;
   constexpr int smem = 2 * 128 * 2 * D + 4 * 128 * 128 + 4096 + 256 + 1024;
@@ -571,10 +571,10 @@ bool causal_tc_walk_supported(const FlareProblem* p, const void* q, const void* 
   return ok(q, p->q_stride) && ok(k, p->k_stride) && ok(v, p->v_stride) && ok(y, p->y_stride);
 }
 
-int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
-                   int* redo, int chunks, cudaStream_t st) {
-  return p->D == 32 ? launch_walk_tc<32>(p, q, k, v, y, prefix, redo, chunks, st)
-                    : launch_walk_tc<64>(p, q, k, v, y, prefix, redo, chunks, st);
+int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const __nv_bfloat16* pacc,
+                   const float2* pml, int* redo, int chunks, cudaStream_t st) {
+  return p->D == 32 ? launch_walk_tc<32>(p, q, k, v, y, pacc, pml, redo, chunks, st)
+                    : launch_walk_tc<64>(p, q, k, v, y, pacc, pml, redo, chunks, st);
 }
 
 }  // namespace flare

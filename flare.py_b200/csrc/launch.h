@@ -77,8 +77,9 @@ bool causal_tc_walk_supported(const FlareProblem* p, const void* q, const void* 
 int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
                      cudaStream_t st);
 // redo: int [chunks][B*H], written by every CTA: 1 where the chunk must be redone by the fp32 walk.
-int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const float* prefix,
-                   int* redo, int chunks, cudaStream_t st);
+// pacc [chunks][B][H][M][D] bf16 and pml [chunks][B][H][M] (m, l): the prefix of every chunk as the scan wrote it.
+int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const __nv_bfloat16* pacc,
+                   const float2* pml, int* redo, int chunks, cudaStream_t st);
 
 // Causal linear attention on the tensor cores (flare_causal_linear_tc.cu): 16-bit inputs, Dk = 128, Dv in {32, 64}.
 bool causal_linear_tc_supported(int B, int H, int N, int Dk, int Dv, int dtype, const void* q, const int64_t* qs,
