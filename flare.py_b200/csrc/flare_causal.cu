@@ -53,9 +53,9 @@ constexpr int kScanRows = 2;      // rows per warp, walked side by side
 // columns; rows are D + 2 floats, so 8-byte aligned): about 25 instructions per row and chunk.  With D a run-time
 // value, 4-byte accesses and 64-bit index arithmetic per access it was 109, and the kernel issue bound at a third of
 // the memory bandwidth.
-// COMPACT: the prefix of chunk c goes to pacc[c][row][D] (16-bit, what the tensor-core walk multiplies with anyway)
-// and pml[c][row] = (m, l) instead of back over the fp32 record: a third of the bytes written, half of the bytes the
-// walk reads, and rows it can fetch in 16-byte pieces.
+// COMPACT (behind the tensor-core record pass): the records are pacc[c][row][D] in 16 bits (what the tensor-core walk
+// multiplies with anyway) and pml[c][row] = (m, l), scanned in place like the fp32 ones: half the bytes in every
+// pass, and rows the walk can fetch in 16-byte pieces.  The sums themselves stay in fp32 registers.
 template <int D, bool COMPACT>
 __global__ void __launch_bounds__(kScanThreads, D == 128 ? 5 : 8)
 k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float* __restrict__ state_in,
@@ -98,6 +98,27 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
       else if (lane_on) r[col] = ao[i][0];
     }
   };
+  // record c of row q into slot u
+  auto fetch = [&](int q, int u, int c) {
+    if constexpr (COMPACT) {
+      const long long i = (long long)c * rows + rw_[q];
+      mlb[q][u] = pml[i];
+      const __nv_bfloat16* pr = pacc + i * D;
+#pragma unroll
+      for (int k = 0; k < NLD; ++k) {
+        if constexpr (VEC == 2) {
+          const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(pr + 64 * k + col));
+          ab[q][u][k][0] = t.x; ab[q][u][k][1] = t.y;
+        } else {
+          ab[q][u][k][0] = lane_on ? __bfloat162float(pr[col]) : 0.f;
+        }
+      }
+    } else {
+      mlb[q][u] = *reinterpret_cast<const float2*>(fp[q] + D);
+      load_acc(fp[q], ab[q][u]);
+      fp[q] += cs;
+    }
+  };
 #pragma unroll
   for (int q = 0; q < kScanRows; ++q) {
     on[q] = row0 + q < rows;
@@ -124,9 +145,7 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
 #pragma unroll
         for (int j = 0; j < VEC; ++j) ab[q][u][i][j] = 0.f;
       if (u < n_chunks) {
-        mlb[q][u] = *reinterpret_cast<const float2*>(fp[q] + D);
-        load_acc(fp[q], ab[q][u]);
-        fp[q] += cs;
+        fetch(q, u, u);
       }
     }
   }
@@ -144,9 +163,7 @@ k_causal_scan(float* __restrict__ rec, int n_chunks, long long rows, const float
 #pragma unroll
             for (int j = 0; j < VEC; ++j) ac[i][j] = ab[q][u][i][j];
           if (c + kAhead < n_chunks) {
-            mlb[q][u] = *reinterpret_cast<const float2*>(fp[q] + D);
-            load_acc(fp[q], ab[q][u]);
-            fp[q] += cs;
+            fetch(q, u, c + kAhead);
           }
           __syncwarp();
           if (on[q]) {                             // the record of everything before chunk c
@@ -537,8 +554,17 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   const int chunks = (p->N + kChunk - 1) / kChunk;
   // pass 1: one record per 128-token chunk
   const bool on_tc = flare::causal_tc_walk_supported(p, q, k, v, y);
+  const long long rows = (long long)p->B * p->H * p->M;
+  // workspace: fp32 records | redo flags | pml | pacc   (every piece a multiple of 16 bytes; the tensor-core path
+  // keeps its records and prefixes in the last two, the others in the first)
+  char* wsb = reinterpret_cast<char*>(workspace) + (size_t)chunks * rows * (p->D + 2) * sizeof(float);
+  int* redo = reinterpret_cast<int*>(wsb);
+  wsb += ((size_t)chunks * p->B * p->H * sizeof(int) + 15) & ~size_t(15);
+  float2* pml = reinterpret_cast<float2*>(wsb);
+  wsb += (size_t)chunks * rows * sizeof(float2);
+  __nv_bfloat16* pacc = reinterpret_cast<__nv_bfloat16*>(wsb);
   if (on_tc) {
-    rc = flare::causal_tc_record(p, q, k, v, workspace, chunks, st);
+    rc = flare::causal_tc_record(p, q, k, v, pacc, pml, chunks, st);
     if (rc != FLARE_OK) return refuse(rc, "causal_prefill: tensor-core record pass could not be launched");
   } else {
     FlareProblem pp = *p;
@@ -547,14 +573,6 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
     if (rc != FLARE_OK) return rc;
   }
   // pass 2: exclusive prefix along the chunk axis
-  const long long rows = (long long)p->B * p->H * p->M;
-  // workspace: records | redo flags | pml | pacc   (every piece a multiple of 16 bytes)
-  char* wsb = reinterpret_cast<char*>(workspace) + (size_t)chunks * rows * (p->D + 2) * sizeof(float);
-  int* redo = reinterpret_cast<int*>(wsb);
-  wsb += ((size_t)chunks * p->B * p->H * sizeof(int) + 15) & ~size_t(15);
-  float2* pml = reinterpret_cast<float2*>(wsb);
-  wsb += (size_t)chunks * rows * sizeof(float2);
-  __nv_bfloat16* pacc = reinterpret_cast<__nv_bfloat16*>(wsb);
   launch_scan(true, workspace, chunks, rows, p->D, state_in, state_out, on_tc ? pacc : nullptr, on_tc ? pml : nullptr, st);
   // pass 3: the tokens of every chunk
   a.q = q; a.k = k; a.v = v; a.y = y;

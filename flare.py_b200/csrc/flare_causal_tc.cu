@@ -375,21 +375,22 @@ k_causal_tc_walk(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
 // Pass 1 for the same shapes: the record (acc, m, l) of every 128-token chunk on its own.  S = scale q k^T,
 // m = rowmax, E = e^{S - m} packed to bf16 in place in tensor memory, acc = E V.  128 tensor-memory columns and
-// three operand tiles per CTA: four CTAs per SM.  The record leaves through shared memory in one contiguous block.
+// three operand tiles per CTA: four CTAs per SM.  acc leaves in 16 bits through shared memory as one contiguous block
+// (the scan adds the records up in fp32; the walk multiplies 16-bit operands anyway), (m, l) as one pair per latent.
 template <int D>
 __global__ void __launch_bounds__(kThreadsW, 4)
 k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, CausalTcArgs a, float* __restrict__ rec_out) {
+                   const __grid_constant__ CUtensorMap tmV, CausalTcArgs a, __nv_bfloat16* __restrict__ racc,
+                   float2* __restrict__ rml) {
   grid_dep_sync();
-  constexpr int ROWB = 2 * D, W = D + 2;
+  constexpr int ROWB = 2 * D;
   constexpr int kTile = 128 * ROWB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kTile;
   uint8_t* sV = sK + kTile;
-  float* sOut = reinterpret_cast<float*>(smem);    // [M][D + 2], over the operand tiles once the products are done
-  static_assert(128 * W * 4 <= 3 * kTile, "the record must fit over the operand tiles");
+  uint8_t* sOut = smem;                            // [128][D] in 16 bits (swizzled rows), over the operand tiles once the products are done
   uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kTile);
   uint64_t* bar_load = bars;
   uint64_t* bar_s = bars + 1;
@@ -473,27 +474,31 @@ k_causal_tc_record(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     tc_fence_after();
   }
   __syncthreads();                                 // the products are complete: the operand tiles are free
+  const long long prow = (((long long)chunk * a.B + b) * a.H + h) * M;      // first row of this record
   if (warp < kRows / 32) {                         // whole warps: rows past M are staged and not copied out
-    {
-      float* orow = sOut + r * W;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(lane_base + cAcc + 32 * c, v);
-        tmem_wait_ld();
+    for (int c = 0; c < D / 32; ++c) {
+      uint32_t v[32];
+      tmem_ld32(lane_base + cAcc + 32 * c, v);
+      tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; j += 2)
-          *reinterpret_cast<float2*>(orow + 32 * c + j) = make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 o;
+        o.x = pack_bf16(__uint_as_float(v[8 * q4]), __uint_as_float(v[8 * q4 + 1]));
+        o.y = pack_bf16(__uint_as_float(v[8 * q4 + 2]), __uint_as_float(v[8 * q4 + 3]));
+        o.z = pack_bf16(__uint_as_float(v[8 * q4 + 4]), __uint_as_float(v[8 * q4 + 5]));
+        o.w = pack_bf16(__uint_as_float(v[8 * q4 + 6]), __uint_as_float(v[8 * q4 + 7]));
+        *reinterpret_cast<uint4*>(sOut + swz_off<ROWB>(r, 4 * c + q4)) = o;
       }
-      *reinterpret_cast<float2*>(orow + D) = make_float2(mx * kLn2, l);
     }
+    if (r < M && !*reinterpret_cast<volatile int*>(abort_flag)) rml[prow + r] = make_float2(mx * kLn2, l);
   }
   __syncthreads();
-  // the record of this (chunk, b, h): M * (D + 2) contiguous floats
+  // acc of this (chunk, b, h): M x D contiguous 16-bit values
   if (!*reinterpret_cast<volatile int*>(abort_flag)) {
-    float2* dst = reinterpret_cast<float2*>(rec_out + (((long long)chunk * a.B + b) * a.H + h) * M * W);
-    const float2* src = reinterpret_cast<const float2*>(sOut);
-    for (int i = tid; i < M * W / 2; i += kThreadsW) dst[i] = src[i];
+    uint4* dst = reinterpret_cast<uint4*>(racc + prow * D);
+    constexpr int CPR = ROWB / 16;
+    for (int i = tid; i < M * CPR; i += kThreadsW) dst[i] = *reinterpret_cast<const uint4*>(sOut + swz_off<ROWB>(i / CPR, i % CPR));
   }
   tc_fence_before();
   __syncthreads();
@@ -545,15 +550,15 @@ int launch_walk_tc(const FlareProblem* p, const void* q, const void* k, const vo
 }
 
 template <int D>
-int launch_record_tc(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
-                     cudaStream_t st) {
+int launch_record_tc(const FlareProblem* p, const void* q, const void* k, const void* v, __nv_bfloat16* racc, float2* rml,
+                     int chunks, cudaStream_t st) {
   TcLaunch L;
   const int rc = fill_launch<D>(p, q, k, v, &L);
   if (rc != FLARE_OK) return rc;
   constexpr int smem = 3 * 128 * 2 * D + 256 + 1024;
   if (tc_set_dyn_smem(reinterpret_cast<const void*>(&k_causal_tc_record<D>), smem) != FLARE_OK) return FLARE_ECUDA;
   launch_dep(k_causal_tc_record<D>, dim3((unsigned)chunks, (unsigned)(p->B * p->H)), dim3(kThreadsW), smem, st, L.tmQ, L.tmK,
-             L.tmV, L.a, rec);
+             L.tmV, L.a, racc, rml);
   return FLARE_OK;
 }
 
@@ -580,8 +585,9 @@ int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const vo
 }  // namespace flare
 
 namespace flare {
-int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
-                     cudaStream_t st) {
-  return p->D == 32 ? launch_record_tc<32>(p, q, k, v, rec, chunks, st) : launch_record_tc<64>(p, q, k, v, rec, chunks, st);
+int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, __nv_bfloat16* racc, float2* rml,
+                     int chunks, cudaStream_t st) {
+  return p->D == 32 ? launch_record_tc<32>(p, q, k, v, racc, rml, chunks, st)
+                    : launch_record_tc<64>(p, q, k, v, racc, rml, chunks, st);
 }
 }  // namespace flare

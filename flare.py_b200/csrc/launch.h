@@ -73,9 +73,10 @@ int tc_set_dyn_smem(const void* kernel, int bytes);
 
 // Causal prefill, pass 3 on the tensor cores (flare_causal_tc.cu): bf16, M <= 128, D in {32, 64}.
 bool causal_tc_walk_supported(const FlareProblem* p, const void* q, const void* k, const void* v, const void* y);
-// pass 1 for the same shapes: rec = [chunks][B][H][M][D+2], the record of every 128-token chunk on its own
-int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, float* rec, int chunks,
-                     cudaStream_t st);
+// pass 1 for the same shapes: the record of every 128-token chunk on its own, racc [chunks][B][H][M][D] in 16 bits and
+// rml [chunks][B][H][M] = (m, l); the scan turns them into the prefixes in place
+int causal_tc_record(const FlareProblem* p, const void* q, const void* k, const void* v, __nv_bfloat16* racc, float2* rml,
+                     int chunks, cudaStream_t st);
 // redo: int [chunks][B*H], written by every CTA: 1 where the chunk must be redone by the fp32 walk.
 // pacc [chunks][B][H][M][D] bf16 and pml [chunks][B][H][M] (m, l): the prefix of every chunk as the scan wrote it.
 int causal_tc_walk(const FlareProblem* p, const void* q, const void* k, const void* v, void* y, const __nv_bfloat16* pacc,
