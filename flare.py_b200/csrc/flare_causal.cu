@@ -550,6 +550,7 @@ int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, co
   int rc = fill_args(p, &a);
   if (rc != FLARE_OK) return rc;
   if (!q || !k || !v || !y || !workspace) return refuse(FLARE_EINVAL, "causal_prefill: null pointer");
+  if (reinterpret_cast<uintptr_t>(workspace) % 16) return refuse(FLARE_EINVAL, "causal_prefill: workspace must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int chunks = (p->N + kChunk - 1) / kChunk;
   // pass 1: one record per 128-token chunk

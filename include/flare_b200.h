@@ -247,7 +247,9 @@ int flare_gather_noalloc(const FlareProblem* p, const void* q, const void* k, co
  * Requires D in {16,32,64,128}, M a multiple of 256/D and at most 32*256/D; dtype as p->dtype.
  * bf16 with M <= 128, D in {32,64} and 16-byte aligned rows runs the prefill's chunk records and chunk
  * walk on the tensor cores (five tcgen05 products per 128-token chunk); a chunk whose scores climb by
- * more than 64 octaves is redone, inside the same call, by the fp32 walk. */
+ * more than 64 octaves is redone, inside the same call, by the fp32 walk.  On that path the chunk records
+ * travel between the passes as 16-bit acc rows (summed in fp32), so state_out carries bf16 rounding of the
+ * chunk sums; `workspace` must be 16-byte aligned. */
 size_t flare_causal_workspace_bytes(const FlareProblem* p);
 int flare_causal_prefill(const FlareProblem* p, const void* q, const void* k, const void* v, void* y,
                          const float* state_in, float* state_out, float* workspace,
