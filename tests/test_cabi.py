@@ -98,6 +98,18 @@ def test_rejects_misaligned_and_null(cabi):
         cabi.check(-2, "x")
 
 
+def test_causal_prefill_workspace_size_and_alignment_are_host_checks(cabi):
+    """The causal prefill's workspace holds fp32 records, the redo flags and the 16-bit records with their (m, l)
+    pairs; a workspace that is not 16-byte aligned is refused before any launch."""
+    p = _problem(cabi, B=2, H=4, N=1000, M=64, D=32)
+    chunks, rows = 8, 2 * 4 * 64
+    need = chunks * rows * (32 + 2) * 4 + chunks * 2 * 4 * 4 + chunks * rows * (32 * 2 + 8)
+    assert cabi.lib.flare_causal_workspace_bytes(C.byref(p)) >= need
+    rc = cabi.lib.flare_causal_prefill(C.byref(p), 16, 16, 16, 16, None, None, 24, None)
+    assert rc == -1
+    assert b"aligned" in cabi.lib.flare_last_error()
+
+
 def test_whole_pass_checks_workspace(cabi):
     p = _problem(cabi)
     rc = cabi.lib.flare_mixer_fwd(C.byref(p), 16, 16, 16, None, 16, 16, 16, 16, 256, 8, None)
